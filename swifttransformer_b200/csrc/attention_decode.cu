@@ -1,0 +1,222 @@
+// Paged attention for queries that stand alone (decode tokens and very short
+// portions), bfloat16 storage, float arithmetic: a bandwidth-bound kernel.
+//
+// One thread block per (query token, head, split of the key range).  Eight
+// lanes share a key: each loads 16 bytes of the key row (and later of the
+// value row) per 64 dims, so a warp reads four full rows per instruction and
+// every byte of the cache is read once.  Each 8-lane group runs its own online
+// softmax over the keys it visits; the sixteen groups of a block, and then the
+// splits of a token, are merged with the usual max / sum rescaling in float.
+// With one split the block writes the normalised output itself; otherwise it
+// leaves (max, sum, weighted values) in `partial` and st_attention_combine
+// finishes.
+//
+// Same mathematics as src/csrc/kernel/fused_decoding_stage_attention_mha.cu:159-318
+// in the reference (which keeps the value sum in the storage type and
+// handles one fixed set of head sizes); the K/V write that the reference does
+// in that kernel is done beforehand by st_qkv_to_cache.
+#include "common.cuh"
+
+#define DEC_THREADS 128
+#define DEC_GROUPS (DEC_THREADS / 8)
+#define LOG2E 1.4426950408889634f
+
+struct __align__(16) bf16x8 { __nv_bfloat162 v[4]; };
+
+__device__ __forceinline__ bf16x8 ldg16(const bf16* p) {
+    bf16x8 r;
+    *reinterpret_cast<uint4*>(&r) = __ldg(reinterpret_cast<const uint4*>(p));
+    return r;
+}
+
+template <int NCHUNK>   // head_dim <= 64 * NCHUNK, a multiple of 8
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
+                        float* __restrict__ partial, const int* __restrict__ items,
+                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
+                        int n_layers, int layer, int nh, int nkv, int d, int page_size, float scale_log2,
+                        int window, int n_splits) {
+    __shared__ float s_m[DEC_GROUPS], s_l[DEC_GROUPS];
+    extern __shared__ float s_acc[];   // [DEC_GROUPS][d]
+    const int t = items ? items[blockIdx.x] : blockIdx.x;
+    const int h = blockIdx.y, split = blockIdx.z;
+    const int kvh = h / (nh / nkv);
+    const int pos = positions[t];
+    if (pos < 0) return;   // padding entry of a fixed-shape launch
+    const int slot = slots[seq_of_token[t]];
+    const int* bt = block_table + (size_t)slot * max_pages;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int hi = pos + 1;
+    int per = (hi - lo + n_splits - 1) / n_splits;
+    per = (per + 15) / 16 * 16;
+    const int k_lo = lo + split * per;
+    const int k_hi = min(hi, k_lo + per);
+
+    const int g = threadIdx.x >> 3, l8 = threadIdx.x & 7;
+    float qf[NCHUNK][8];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+        const int dim0 = (c * 8 + l8) * 8;
+        if (dim0 < d) {
+            const bf16x8 v = ldg16(q + ((size_t)t * nh + h) * d + dim0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(v.v[i]);
+                qf[c][2 * i] = f.x * scale_log2;
+                qf[c][2 * i + 1] = f.y * scale_log2;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qf[c][i] = 0.f;
+        }
+    }
+    float acc[NCHUNK][8];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const size_t head_stride = (size_t)page_size * d;
+    const size_t kv_stride = (size_t)nkv * head_stride;
+
+    // every lane of the block runs the same number of rounds (the shuffles need
+    // all 32 lanes); a group whose key lies past the end re-reads the last key
+    // and drops the result.
+    for (int key0 = k_lo; key0 < k_hi; key0 += DEC_GROUPS) {
+        const bool valid = key0 + g < k_hi;
+        const int key = valid ? key0 + g : k_hi - 1;
+        const int page = bt[key / page_size];
+        const bf16* krow = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
+                           + (size_t)(key % page_size) * d;
+        const bf16* vrow = krow + kv_stride;
+        bf16x8 kreg[NCHUNK], vreg[NCHUNK];
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) {
+            const int dim0 = (c * 8 + l8) * 8;
+            if (dim0 < d) { kreg[c] = ldg16(krow + dim0); vreg[c] = ldg16(vrow + dim0); }
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) {
+            const int dim0 = (c * 8 + l8) * 8;
+            if (dim0 < d) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(kreg[c].v[i]);
+                    s = fmaf(qf[c][2 * i], f.x, s);
+                    s = fmaf(qf[c][2 * i + 1], f.y, s);
+                }
+            }
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (!valid) continue;
+        const float m_new = fmaxf(m, s);
+        const float corr = exp2f(m - m_new);   // m = -inf on the first key: exp2f(-inf) = 0
+        const float p = exp2f(s - m_new);
+        l = l * corr + p;
+        m = m_new;
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) {
+            const int dim0 = (c * 8 + l8) * 8;
+            if (dim0 < d) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(vreg[c].v[i]);
+                    acc[c][2 * i] = fmaf(p, f.x, acc[c][2 * i] * corr);
+                    acc[c][2 * i + 1] = fmaf(p, f.y, acc[c][2 * i + 1] * corr);
+                }
+            }
+        }
+    }
+    if (l8 == 0) { s_m[g] = m; s_l[g] = l; }
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+        const int dim0 = (c * 8 + l8) * 8;
+        if (dim0 < d) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s_acc[g * d + dim0 + i] = acc[c][i];
+        }
+    }
+    __syncthreads();
+    float mm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < DEC_GROUPS; ++i) mm = fmaxf(mm, s_m[i]);
+    float ll = 0.f;
+#pragma unroll
+    for (int i = 0; i < DEC_GROUPS; ++i) ll += (s_m[i] == -INFINITY) ? 0.f : s_l[i] * exp2f(s_m[i] - mm);
+    float* part = partial ? partial + (((size_t)blockIdx.x * nh + h) * n_splits + split) * (d + 2) : nullptr;
+    for (int e = threadIdx.x; e < d; e += DEC_THREADS) {
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < DEC_GROUPS; ++i)
+            a += (s_m[i] == -INFINITY) ? 0.f : s_acc[i * d + e] * exp2f(s_m[i] - mm);
+        if (n_splits == 1) out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / ll);
+        else part[2 + e] = a;
+    }
+    if (n_splits > 1 && threadIdx.x == 0) { part[0] = mm; part[1] = ll; }
+}
+
+// merge the splits of every (item, head)
+__global__ void attention_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
+                                         const int* __restrict__ items, const int* __restrict__ positions,
+                                         int nh, int d, int n_splits) {
+    const int t = items ? items[blockIdx.x] : blockIdx.x;
+    if (positions[t] < 0) return;
+    const int h = blockIdx.y;
+    const float* part = partial + ((size_t)blockIdx.x * nh + h) * n_splits * (d + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part[(size_t)s * (d + 2)]);
+    float ll = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part[(size_t)s * (d + 2)];
+        ll += (ms == -INFINITY) ? 0.f : part[(size_t)s * (d + 2) + 1] * exp2f(ms - mm);
+    }
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part[(size_t)s * (d + 2)];
+            a += (ms == -INFINITY) ? 0.f : part[(size_t)s * (d + 2) + 2 + e] * exp2f(ms - mm);
+        }
+        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / ll);
+    }
+}
+
+// Number of floats of scratch that st_attention_decode needs for n_splits > 1.
+ST_EXPORT long long st_attention_decode_scratch_floats(int n_items, int nh, int d, int n_splits) {
+    return n_splits > 1 ? (long long)n_items * nh * n_splits * (d + 2) : 0;
+}
+
+ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, float* partial, const int* items,
+                                  int n_items, const int* positions, const int* seq_of_token, const int* slots,
+                                  const int* block_table, int max_pages, int n_layers, int layer, int nh, int nkv,
+                                  int d, int page_size, float scale, int window, int n_splits, void* stream) {
+    if (n_items <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
+    if (d % 8 || d <= 0) return ST_ERR_BAD_SIZE;
+    if (d > 256) return ST_ERR_TOO_LARGE;
+    if (n_splits > 1 && !partial) return ST_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_items, nh, n_splits);
+    const size_t smem = (size_t)DEC_GROUPS * d * sizeof(float);
+    const float sl2 = scale * LOG2E;
+#define LAUNCH_DEC(NC)                                                                                         \
+    attention_decode_kernel<NC><<<grid, DEC_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,  \
+        n_splits > 1 ? partial : nullptr, items, positions, seq_of_token, slots, block_table, max_pages,        \
+        n_layers, layer, nh, nkv, d, page_size, sl2, window, n_splits)
+    if (d <= 64) LAUNCH_DEC(1);
+    else if (d <= 128) LAUNCH_DEC(2);
+    else if (d <= 192) LAUNCH_DEC(3);
+    else LAUNCH_DEC(4);
+#undef LAUNCH_DEC
+    int rc = st_launch_status();
+    if (rc) return rc;
+    if (n_splits > 1) {
+        dim3 g2(n_items, nh);
+        attention_combine_kernel<<<g2, 64, 0, s>>>(partial, (bf16*)out, items, positions, nh, d, n_splits);
+        rc = st_launch_status();
+    }
+    return rc;
+}

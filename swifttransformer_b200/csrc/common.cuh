@@ -1,0 +1,72 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+//
+// Conventions of every exported launcher (extern "C", called through ctypes):
+//   * pointers are device pointers, `stream` is a cudaStream_t passed as void*;
+//   * `dtype` selects the storage type of activations / matrices: 0 = float,
+//     1 = __nv_bfloat16.  Vectors (biases, norm weights) are always float;
+//   * the return value is 0 on success, a positive cudaError_t from the launch,
+//     or a negative ST_ERR_* code for arguments the kernel refuses.  Nothing is
+//     ever computed wrongly for an unsupported size: it is refused.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define ST_ERR_BAD_DTYPE (-1)
+#define ST_ERR_BAD_SIZE (-2)
+#define ST_ERR_TOO_LARGE (-3)
+#define ST_ERR_BAD_ARG (-4)
+
+#define ST_EXPORT extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide reductions with a fixed order (xor butterflies inside a warp, then
+// the warp partials combined in warp-index order by every thread), so the
+// result is the same bit pattern in every thread and on every launch.
+// `scratch` holds at least 32 floats; the call ends with the scratch free for reuse.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int i = 0; i < nwarp; ++i) r += scratch[i];
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = scratch[0];
+    for (int i = 1; i < nwarp; ++i) r = fmaxf(r, scratch[i]);
+    return r;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == 1) return v > 0.f ? v : 0.f;                                // relu
+    if (act == 2) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));  // gelu (erf form)
+    return v;
+}
+
+static inline int st_launch_status() { return (int)cudaGetLastError(); }

@@ -1,0 +1,286 @@
+"""The engine's device operations.
+
+Every function here launches hand-written sm_100a kernels from ``csrc/``
+through the C entry points of ``libst_b200.so`` (loaded with ctypes; built on
+first use by ``ops.build``), on torch's current CUDA stream, on tensors the
+caller owns.  The only library calls are the bfloat16 matrix products, which
+go to cuBLAS through ``torch`` (the reference uses cuBLAS for the same five
+products, src/csrc/util/cublas_wrapper.cc:29-53).
+
+There is no CPU path: a tensor that is not on a CUDA device is an error, and
+so is a missing or unbuildable library.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import build as _build
+
+_LIB = None
+
+ACT_CODES = {"none": 0, "relu": 1, "gelu": 2}
+NORM_CODES = {"layernorm": 0, "rmsnorm": 1, "none": 2}
+
+_ERRORS = {-1: "unsupported dtype", -2: "unsupported size", -3: "size beyond the kernel's limit",
+           -4: "invalid argument"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded kernel library (built on first use)."""
+    global _LIB
+    if _LIB is None:
+        path = _build.ensure_built()
+        try:
+            _LIB = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load {path}: {e}") from None
+        _LIB.st_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        _LIB.st_uniform_host.restype = ctypes.c_float
+        _LIB.st_uniform_host.argtypes = [ctypes.c_longlong, ctypes.c_longlong]
+    return _LIB
+
+
+def library_path() -> str:
+    return _build.ensure_built()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{what}: refused ({_ERRORS.get(rc, rc)})")
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"unsupported tensor type {t.dtype} (float32 or bfloat16)")
+
+
+def _p(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("this engine runs on a CUDA device only; got a CPU tensor")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f(x: float):
+    return ctypes.c_float(x)
+
+
+# ------------------------------------------------------------------ embedding
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, positions: Optional[torch.Tensor] = None,
+          pos_table: Optional[torch.Tensor] = None, pos_offset: int = 0) -> torch.Tensor:
+    """out[t] = table[ids[t]] (+ pos_table[positions[t] + pos_offset]); out is float32 or table's type."""
+    n, width = ids.numel(), table.shape[1]
+    assert out.shape == (n, width) and out.is_contiguous() and table.is_contiguous()
+    if pos_table is not None:
+        assert pos_table.shape[1] == width and pos_table.dtype == table.dtype
+    _check(lib().st_embed(_p(ids), _p(table), n, width, _p(positions) if pos_table is not None else None,
+                          _p(pos_table), pos_offset, _p(out), _dt(table), int(out.dtype == torch.float32),
+                          _stream()), "embed")
+    return out
+
+
+def add_positions(x: torch.Tensor, positions: torch.Tensor, pos_table: torch.Tensor, pos_offset: int,
+                  out: torch.Tensor) -> torch.Tensor:
+    """out[t] = x[t] + pos_table[positions[t] + pos_offset]."""
+    n, width = x.shape
+    assert pos_table.shape[1] == width and x.dtype == pos_table.dtype and out.shape == x.shape
+    _check(lib().st_add_positions(_p(x), n, width, _p(positions), _p(pos_table), pos_offset, _p(out),
+                                  _dt(x), int(out.dtype == torch.float32), _stream()), "add_positions")
+    return out
+
+
+# ------------------------------------------------------------ residual + norm
+def add_norm(x: torch.Tensor, *, delta: Optional[torch.Tensor] = None, delta_bias: Optional[torch.Tensor] = None,
+             resid_out: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None,
+             beta: Optional[torch.Tensor] = None, eps: float = 1e-5, kind: str = "layernorm",
+             rows: Optional[torch.Tensor] = None, out_act: Optional[torch.Tensor] = None,
+             out_f32: Optional[torch.Tensor] = None, act_dtype: Optional[torch.dtype] = None) -> None:
+    """s = x[i] + delta[i] + delta_bias; resid_out[i] = s; y = norm(s); out_act[r] = y; out_f32[r] = y.
+
+    ``x`` is the float32 residual stream; ``i = rows[r]`` when ``rows`` is given, else ``r``.
+    """
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    width = x.shape[1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if out_act is not None:
+        code = _dt(out_act)
+    elif delta is not None:
+        code = _dt(delta)
+    else:
+        code = 0 if act_dtype in (None, torch.float32) else 1
+    if delta is not None and out_act is not None:
+        assert delta.dtype == out_act.dtype
+    _check(lib().st_add_norm(_p(x), _p(rows), _p(delta), _p(delta_bias), _p(resid_out), _p(gamma), _p(beta),
+                             _f(eps), NORM_CODES[kind], n, width, _p(out_act), _p(out_f32), code, _stream()),
+           "add_norm")
+
+
+def bias_act(y: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> torch.Tensor:
+    """y = act(y + bias) in place."""
+    if bias is None and act == "none":
+        return y
+    assert y.is_contiguous()
+    _check(lib().st_bias_act(_p(y), _p(bias), ACT_CODES[act], y.shape[0], y.shape[1], _dt(y), _stream()), "bias_act")
+    return y
+
+
+def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, count: torch.Tensor, max_count: int) -> None:
+    """dst.flatten()[idx[i]] = val[i] for i < count[0] (count lives on the device)."""
+    _check(lib().st_scatter_i32(_p(dst), _p(idx), _p(val), _p(count), max_count, _stream()), "scatter_i32")
+
+
+# ------------------------------------------------------------ matrix products
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(a @ w.T + bias); w is [out, in].  float32: the plain fused-multiply-add kernel (true 32-bit).
+    bfloat16: cuBLAS with float accumulation, then the bias/activation kernel."""
+    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1] and a.dtype == w.dtype
+    out_dtype = out_dtype or a.dtype
+    n, m = a.shape[0], w.shape[0]
+    if a.dtype == torch.float32:
+        return gemm_plain(a, w, bias, act, out_dtype)
+    if not a.is_cuda:
+        raise KernelError("this engine runs on a CUDA device only; got a CPU tensor")
+    if n == 0:
+        return torch.empty((0, m), dtype=out_dtype, device=a.device)
+    if out_dtype == torch.float32:
+        y = torch.mm(a, w.t(), out_dtype=torch.float32)
+    else:
+        y = torch.mm(a, w.t())
+    return bias_act(y, bias, act)
+
+
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The plain kernel for either storage type (float arithmetic, fixed summation order)."""
+    out_dtype = out_dtype or a.dtype
+    a = a.contiguous()
+    assert w.is_contiguous()
+    n, k = a.shape
+    m = w.shape[0]
+    out = torch.empty((n, m), dtype=out_dtype, device=a.device)
+    _check(lib().st_gemm_plain(_p(a), _p(w), _p(bias), _p(out), n, m, k, ACT_CODES[act], _dt(a),
+                               int(out_dtype == torch.float32), _stream()), "gemm_plain")
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def qkv_to_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, pool: torch.Tensor,
+                 layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor,
+                 block_table: torch.Tensor, nh: int, nkv: int, d: int, status: torch.Tensor,
+                 write_kv: bool = True) -> None:
+    """q_out = q + bias; pool[page, layer, 0/1, head, pos % page, :] = k/v + bias.
+
+    pool: [pages, layers, 2, nkv, page_size, d]; block_table: [slots, max_pages] int32."""
+    n = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * d and pool.dtype == qkv.dtype
+    num_pages, n_layers, _, pnkv, page_size, pd = pool.shape
+    assert pnkv == nkv and pd == d
+    _check(lib().st_qkv_to_cache(_p(qkv), _p(bias), _p(q_out), _p(pool), _p(positions), _p(seq_of_token),
+                                 _p(slots), _p(block_table), block_table.shape[1], num_pages, n_layers, layer,
+                                 n, nh, nkv, d, page_size, int(write_kv), _p(status), _dt(qkv), _stream()),
+           "qkv_to_cache")
+
+
+def attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                    seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
+                    scale: float, window: int = 0) -> torch.Tensor:
+    """Paged causal attention, one block per (token, head), float arithmetic, any sizes."""
+    n = q.shape[0]
+    _, n_layers, _, nkv, page_size, d = pool.shape
+    _check(lib().st_attention_plain(_p(q), _p(pool), _p(out), _p(positions), _p(seq_of_token), _p(slots),
+                                    _p(block_table), block_table.shape[1], n_layers, layer, n, nh, nkv, d,
+                                    page_size, _f(scale), window, _dt(q), _stream()), "attention_plain")
+    return out
+
+
+def attention_decode_scratch(n_items: int, nh: int, d: int, n_splits: int) -> int:
+    return int(lib().st_attention_decode_scratch_floats(n_items, nh, d, n_splits))
+
+
+def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor,
+                     items: Optional[torch.Tensor], n_items: int, positions: torch.Tensor,
+                     seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
+                     scale: float, window: int = 0, n_splits: int = 1,
+                     partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bfloat16 paged attention for single query tokens; ``items`` lists the token indices it serves
+    (None: tokens 0..n_items-1).  A token whose position is negative is skipped."""
+    _, n_layers, _, nkv, page_size, d = pool.shape
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode is a bfloat16 kernel")
+    if n_splits > 1:
+        need = attention_decode_scratch(n_items, nh, d, n_splits)
+        if partial is None or partial.numel() < need or partial.dtype != torch.float32:
+            raise KernelError(f"attention_decode: needs {need} floats of scratch for {n_splits} splits")
+    _check(lib().st_attention_decode(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items, _p(positions),
+                                     _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
+                                     n_layers, layer, nh, nkv, d, page_size, _f(scale), window, n_splits,
+                                     _stream()), "attention_decode")
+    return out
+
+
+def attention_prefill_tile_rows() -> int:
+    return int(lib().st_attention_prefill_tile_rows())
+
+
+def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,
+                      n_tiles: int, q_start: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
+                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
+    """bfloat16 tensor-core paged attention over tiles of 64 query tokens; tiles: int32 [n_tiles, 2] =
+    (request index in the step, offset of the tile among the request's new tokens)."""
+    _, n_layers, _, nkv, page_size, d = pool.shape
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill is a bfloat16 kernel")
+    _check(lib().st_attention_prefill(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start), _p(start_pos),
+                                      _p(slots), _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv,
+                                      d, page_size, _f(scale), window, _stream()), "attention_prefill")
+    return out
+
+
+# ------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Lowest index of the largest value of each row of float32 logits -> int32 [rows]."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    n, v = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(lib().st_argmax(_p(logits), n, v, _p(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperatures: torch.Tensor, top_k: torch.Tensor, seeds: torch.Tensor,
+           counters: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row r: temperature <= 0 -> greedy; else draw from softmax(logits/temperature) restricted to the
+    top_k[r] largest (<= 0: all) with the uniform number ``uniform(seeds[r], counters[r])``."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    assert temperatures.dtype == torch.float32 and top_k.dtype == torch.int32
+    assert seeds.dtype == torch.int64 and counters.dtype == torch.int64
+    n, v = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(lib().st_sample(_p(logits), n, v, _p(temperatures), _p(top_k), _p(seeds), _p(counters), _p(out),
+                           _stream()), "sample")
+    return out
+
+
+def uniform(seed: int, counter: int) -> float:
+    """The uniform number in [0,1) that `sample` uses for (seed, counter); computed on the host."""
+    return float(lib().st_uniform_host(seed, counter))

@@ -1,0 +1,122 @@
+"""Interfaces of the parts a model is put together from.
+
+A model is: an embedding, a position encoding, a list of blocks, an order in
+which the blocks run, a final norm and an output head.  A block is put
+together from a mixer (attention here), a feed-forward and norms.  Every part
+takes its sizes and constants as constructor arguments, declares the tensors
+it wants from the checkpoint (``param_specs``) and receives them in ``bind``.
+No part knows which model it is in; which parts a layer has is decided by the
+architecture's builder, layer by layer, from the configuration.
+
+The reference's counterpart is procedural: ``st::layer::attention`` and
+``st::layer::ffn`` take raw pointers and their sizes as parameters
+(src/csrc/layer/attention.h:8-53, src/csrc/layer/ffn.h:11-31) and the block
+order is written out in src/csrc/model/gpt/gpt.cc:304-503.
+
+Interfaces
+----------
+Mixer.cache_spec()        -> PagedKVSpec | StateSpec | None
+Mixer.forward(h, ctx, cache) -> Delta         h: [N, width] activations
+FeedForward.forward(h, ctx)  -> Delta
+Norm.apply(x, delta, ...)    -> see parts.norm
+PositionEncoding.table()     -> (table, offset) for encodings added to the hidden state
+Block.forward(stream, ctx, cache) -> None (updates the residual stream)
+
+``Delta`` is what a sub-layer hands back: ``value + bias`` (bias broadcast over
+rows) is to be added to the residual stream.  Leaving the sum to the consumer
+lets the next norm kernel do residual add, bias add and normalisation in one
+pass over the row.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..weights.spec import ParamSpec
+
+
+@dataclasses.dataclass
+class Delta:
+    value: torch.Tensor                 # [N, width], activation dtype
+    bias: Optional[torch.Tensor] = None  # [width] float32
+
+
+@dataclasses.dataclass(frozen=True)
+class PagedKVSpec:
+    """Keys and values per token, kept in pages.  ``window`` None: all keys stay."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclasses.dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size (``shape`` per request), zero when a request starts."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    """Base of all parts."""
+
+    def param_specs(self) -> List[ParamSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take this part's tensors out of ``tensors`` (name -> device tensor)."""
+
+    def children(self) -> List["Part"]:
+        return []
+
+    # bytes of parameters this part reads in one step (for roofline accounting)
+    def param_bytes(self) -> int:
+        return 0
+
+
+class Mixer(Part):
+    # False for mixers whose forward does host-side work that cannot be
+    # recorded into a CUDA graph (the engine then runs them eagerly).
+    graph_safe = True
+
+    def cache_spec(self):
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
+        raise NotImplementedError
+
+
+class Registry:
+    """Name -> constructor for one kind of part."""
+
+    def __init__(self, kind: str):
+        self.kind = kind
+        self._items: Dict[str, Callable[..., Any]] = {}
+
+    def register(self, name: str, ctor: Optional[Callable[..., Any]] = None):
+        def deco(c):
+            self._items[name] = c
+            return c
+        return deco(ctor) if ctor is not None else deco
+
+    def build(self, kind_name: str, /, **kwargs):
+        if kind_name not in self._items:
+            raise KeyError(f"unknown {self.kind} '{kind_name}'; registered: "
+                           f"{', '.join(sorted(self._items)) or '(none)'}")
+        return self._items[kind_name](**kwargs)
+
+    def names(self) -> List[str]:
+        return sorted(self._items)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")

@@ -1,0 +1,45 @@
+"""The dense feed-forward: z = act(h fc1^T + b1) fc2^T + b2.
+
+Reference: ``st::layer::ffn`` (src/csrc/layer/ffn.cc:49-126): fc1 product (71-80),
+fused bias + activation (85-92), fc2 product (96-105), bias (124).  The second
+bias travels with the result so the next norm kernel adds it with the residual.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List
+
+import torch
+
+from .. import ops
+from ..weights.spec import MATRIX, VECTOR, ParamSpec
+from .base import FEED_FORWARDS, Delta, FeedForward
+
+
+@FEED_FORWARDS.register("dense")
+class DenseFFN(FeedForward):
+    def __init__(self, hidden: int, inner: int, activation: str, fc1_name: str, fc2_name: str, bias: bool = True):
+        if activation not in ops.ACT_CODES:
+            raise ValueError(f"activation '{activation}' is not supported ({', '.join(ops.ACT_CODES)})")
+        self.hidden, self.inner, self.activation, self.bias = hidden, inner, activation, bias
+        self.fc1_name, self.fc2_name = fc1_name, fc2_name
+        self.w1 = self.b1 = self.w2 = self.b2 = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        specs = [ParamSpec(self.fc1_name + ".weight", (self.inner, self.hidden), MATRIX),
+                 ParamSpec(self.fc2_name + ".weight", (self.hidden, self.inner), MATRIX)]
+        if self.bias:
+            specs += [ParamSpec(self.fc1_name + ".bias", (self.inner,), VECTOR),
+                      ParamSpec(self.fc2_name + ".bias", (self.hidden,), VECTOR)]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w1, self.w2 = tensors[self.fc1_name + ".weight"], tensors[self.fc2_name + ".weight"]
+        if self.bias:
+            self.b1, self.b2 = tensors[self.fc1_name + ".bias"], tensors[self.fc2_name + ".bias"]
+
+    def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
+        u = ops.linear(h, self.w1, self.b1, self.activation)
+        return Delta(ops.linear(u, self.w2), self.b2)
+
+    def param_bytes(self) -> int:
+        return (self.w1.numel() + self.w2.numel()) * self.w1.element_size()

@@ -1,0 +1,230 @@
+"""The plain reference of every device operation, in torch on the CPU.
+
+Each function has the signature of its namesake in ``swifttransformer_b200.ops``
+and computes the same thing the slow, obvious way (float64 inside where that
+is free).  The kernel tests compare each CUDA kernel with its function here;
+the CPU tests patch these over ``ops`` to exercise the engine's host logic
+(step building, cache manager, scheduler) where there is no GPU.  Nothing in
+the package imports this file.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+def _act(y, act):
+    if act == "relu":
+        return torch.relu(y)
+    if act == "gelu":
+        return 0.5 * y * (1 + torch.erf(y / math.sqrt(2.0)))
+    return y
+
+
+def embed(ids, table, out, positions=None, pos_table=None, pos_offset=0):
+    v = table[ids.long()].double()
+    if pos_table is not None:
+        v = v + pos_table[positions.long() + pos_offset].double()
+    out.copy_(v.to(out.dtype))
+    return out
+
+
+def add_positions(x, positions, pos_table, pos_offset, out):
+    out.copy_((x.double() + pos_table[positions.long() + pos_offset].double()).to(out.dtype))
+    return out
+
+
+def add_norm(x, *, delta=None, delta_bias=None, resid_out=None, gamma=None, beta=None, eps=1e-5,
+             kind="layernorm", rows=None, out_act=None, out_f32=None, act_dtype=None):
+    idx = rows.long() if rows is not None else torch.arange(x.shape[0])
+    s = x[idx].float()
+    if delta is not None:
+        s = s + delta[idx].float()
+    if delta_bias is not None:
+        s = s + delta_bias.float()
+    if resid_out is not None:
+        resid_out[idx] = s
+    sd = s.double()
+    if kind == "layernorm":
+        mean = sd.mean(-1, keepdim=True)
+        var = ((sd - mean) ** 2).mean(-1, keepdim=True)
+        y = (sd - mean) / torch.sqrt(var + eps)
+    elif kind == "rmsnorm":
+        y = sd / torch.sqrt((sd ** 2).mean(-1, keepdim=True) + eps)
+    else:
+        y = sd
+    if kind != "none":
+        if gamma is not None:
+            y = y * gamma.double()
+        if beta is not None:
+            y = y + beta.double()
+    if out_act is not None:
+        out_act.copy_(y.to(out_act.dtype))
+    if out_f32 is not None:
+        out_f32.copy_(y.float())
+
+
+def bias_act(y, bias, act):
+    v = y.float()
+    if bias is not None:
+        v = v + bias
+    y.copy_(_act(v, act).to(y.dtype))
+    return y
+
+
+def scatter_i32(dst, idx, val, count, max_count):
+    n = int(count[0])
+    dst.view(-1)[idx[:n].long()] = val[:n]
+
+
+def linear(a, w, bias=None, act="none", out_dtype=None):
+    y = a.double() @ w.double().t()
+    if bias is not None:
+        y = y + bias.double()
+    return _act(y, act).to(out_dtype or a.dtype)
+
+
+gemm_plain = linear
+
+
+def qkv_to_cache(qkv, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d,
+                 status, write_kv=True):
+    n = qkv.shape[0]
+    v = qkv.float()
+    if bias is not None:
+        v = v + bias
+    q_out.copy_(v[:, :nh * d].to(q_out.dtype))
+    if not write_kv:
+        return
+    ps = pool.shape[4]
+    for t in range(n):
+        pos = int(positions[t])
+        if pos < 0:
+            continue
+        slot = int(slots[int(seq_of_token[t])])
+        page = int(block_table[slot, pos // ps])
+        if page < 0 or page >= pool.shape[0]:
+            status[0] = 1
+            continue
+        pool[page, layer, 0, :, pos % ps, :] = v[t, nh * d:(nh + nkv) * d].view(nkv, d).to(pool.dtype)
+        pool[page, layer, 1, :, pos % ps, :] = v[t, (nh + nkv) * d:].view(nkv, d).to(pool.dtype)
+
+
+def attention_plain(q, pool, layer, out, positions, seq_of_token, slots, block_table, nh, scale, window=0):
+    n = q.shape[0]
+    _, _, _, nkv, ps, d = pool.shape
+    g = nh // nkv
+    for t in range(n):
+        pos = int(positions[t])
+        if pos < 0:
+            continue
+        slot = int(slots[int(seq_of_token[t])])
+        lo = max(0, pos - window + 1) if window > 0 else 0
+        keys = torch.arange(lo, pos + 1)
+        pages = block_table[slot, (keys // ps).long()].long()
+        k = pool[pages, layer, 0, :, (keys % ps).long(), :].double()    # [keys, nkv, d]
+        v = pool[pages, layer, 1, :, (keys % ps).long(), :].double()
+        qt = q[t].double().view(nh, d)
+        for h in range(nh):
+            s = (k[:, h // g, :] @ qt[h]) * scale
+            p = torch.softmax(s, 0)
+            out[t, h * d:(h + 1) * d] = (p @ v[:, h // g, :]).to(out.dtype)
+    return out
+
+
+def attention_decode_scratch(n_items, nh, d, n_splits):
+    return n_items * nh * n_splits * (d + 2) if n_splits > 1 else 0
+
+
+def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_token, slots, block_table, nh,
+                     scale, window=0, n_splits=1, partial=None):
+    idx = items[:n_items].long() if items is not None else torch.arange(n_items)
+    tmp = torch.zeros_like(out)
+    pos = torch.full_like(positions, -1)
+    pos[idx] = positions[idx]
+    attention_plain(q, pool, layer, tmp, pos, seq_of_token, slots, block_table, nh, scale, window)
+    keep = idx[positions[idx] >= 0]
+    out[keep] = tmp[keep]
+    return out
+
+
+def attention_prefill_tile_rows():
+    return 64
+
+
+def attention_prefill(q, pool, layer, out, tiles, n_tiles, q_start, start_pos, slots, block_table, nh, scale,
+                      window=0):
+    n = q.shape[0]
+    pos = torch.full((n,), -1, dtype=torch.int32)
+    seq_of = torch.zeros(n, dtype=torch.int32)
+    for i in range(n_tiles):
+        seq, off = int(tiles[2 * i]), int(tiles[2 * i + 1])
+        a = int(q_start[seq]) + off
+        b = min(a + 64, int(q_start[seq + 1]))
+        pos[a:b] = torch.arange(int(start_pos[seq]) + off, int(start_pos[seq]) + off + (b - a), dtype=torch.int32)
+        seq_of[a:b] = seq
+    tmp = torch.zeros_like(out)
+    attention_plain(q, pool, layer, tmp, pos, seq_of, slots, block_table, nh, scale, window)
+    out[pos >= 0] = tmp[pos >= 0]
+    return out
+
+
+def argmax(logits, out=None):
+    r = torch.argmax(logits, dim=-1).to(torch.int32)   # torch returns the first maximal index
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
+
+
+def _uniform(seed, counter):
+    m = (1 << 64) - 1
+    z = (seed * 0x9E3779B97F4A7C15 + (counter + 1) * 0xBF58476D1CE4E5B9) & m
+    z ^= z >> 30
+    z = (z * 0xBF58476D1CE4E5B9) & m
+    z ^= z >> 27
+    z = (z * 0x94D049BB133111EB) & m
+    z ^= z >> 31
+    return float(z >> 40) / 16777216.0
+
+
+def uniform(seed, counter):
+    return _uniform(int(seed) & ((1 << 64) - 1), int(counter) & ((1 << 64) - 1))
+
+
+def sample(logits, temperatures, top_k, seeds, counters, out=None):
+    n, v = logits.shape
+    res = torch.empty(n, dtype=torch.int32)
+    for r in range(n):
+        z = logits[r].double()
+        t = float(temperatures[r])
+        if t <= 0:
+            res[r] = int(torch.argmax(z))
+            continue
+        k = int(top_k[r])
+        if 0 < k < v:
+            kth = torch.sort(z, descending=True).values[k - 1]
+            z = torch.where(z >= kth, z, torch.full_like(z, -float("inf")))
+        p = torch.exp((z - z.max()) / t)
+        c = torch.cumsum(p, 0)
+        u = uniform(int(seeds[r]), int(counters[r]))
+        res[r] = min(int(torch.searchsorted(c, torch.tensor(u * float(c[-1]), dtype=c.dtype), right=True)), v - 1)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "linear", "gemm_plain", "qkv_to_cache",
+       "attention_plain", "attention_decode_scratch", "attention_decode", "attention_prefill_tile_rows",
+       "attention_prefill", "argmax", "sample", "uniform"]
+
+
+def install(monkeypatch):
+    """Patch every operation of the package with its CPU reference (tests only)."""
+    import sys
+    from swifttransformer_b200 import ops
+    this = sys.modules[__name__]
+    for name in ALL:
+        monkeypatch.setattr(ops, name, getattr(this, name))
