@@ -76,7 +76,8 @@ class PagedGroup:
         self.block_table = torch.full((max_seqs, max_pages_per_seq), -1, dtype=torch.int32, device=device)
         # per slot: logical page index -> page id, and the first logical page still held
         self.pages: List[Dict[int, int]] = [dict() for _ in range(max_seqs)]
-        self.updates: List[Tuple[int, int]] = []     # (flat index into block_table, value)
+        # flat index into block_table -> newest value (one entry per index: the device applies them in parallel)
+        self.updates: Dict[int, int] = {}
 
     @property
     def bytes_per_token(self) -> int:
@@ -105,7 +106,7 @@ class PagedGroup:
             return False
         for j, p in zip(need, got):
             self.pages[slot][j] = p
-            self.updates.append((slot * self.max_pages_per_seq + j, p))
+            self.updates[slot * self.max_pages_per_seq + j] = p
         return True
 
     def _release(self, slot: int, logical: Sequence[int]) -> None:
@@ -113,7 +114,7 @@ class PagedGroup:
         self.pool.free([held[j] for j in logical])
         for j in logical:
             del held[j]
-            self.updates.append((slot * self.max_pages_per_seq + j, -1))
+            self.updates[slot * self.max_pages_per_seq + j] = -1
 
     def trim(self, slot: int, length: int) -> int:
         """Give back the pages that no query at a position >= length can read (window groups)."""
@@ -128,8 +129,8 @@ class PagedGroup:
         self._release(slot, list(self.pages[slot]))
 
     def take_updates(self) -> List[Tuple[int, int]]:
-        u, self.updates = self.updates, []
-        return u
+        u, self.updates = self.updates, {}
+        return list(u.items())
 
 
 class CacheManager:

@@ -94,7 +94,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
         for (int idx = threadIdx.x; idx < PF_BN * chunks; idx += PF_THREADS) {
             const int r = idx / chunks, c = idx - r * chunks;
             const int key = kt * PF_BN + r;
-            const bool ok = key < kv_hi;
+            const bool ok = key >= key_lo && key < kv_hi;   // outside: never read (its page may be gone)
             const int page = ok ? bt[key / page_size] : 0;
             const bf16* src = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
                               + (size_t)(ok ? key % page_size : 0) * d + c * 8;

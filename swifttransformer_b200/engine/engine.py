@@ -1,0 +1,139 @@
+"""The Python entry point: requests in, tokens out.
+
+``LLMEngine`` ties the model, the cache manager, the step function, the
+scheduler and the sampler together.  ``generate`` is the call a user makes;
+``step`` runs one scheduler decision through the GPU.
+
+The reference's counterpart is the static-batch loop ``run_batched_inference``
+(src/examples/lib/inference_batch.cc:15-232) and, from Python,
+``torch.classes.gpt_ops.OptOp.forward`` (src/csrc/pybinding.cc:53-62), which
+leaves batching, block allocation and stopping to its caller.
+"""
+from __future__ import annotations
+
+import dataclasses
+import itertools
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..models.base import CausalLM
+from ..models.registry import load_model
+from ..sampling.sampler import Sampler, SamplingParams
+from .scheduler import Request, Scheduled, Scheduler
+from .step import ModelRunner, StepEntry
+
+
+@dataclasses.dataclass
+class EngineConfig:
+    page_size: int = 16                 # the reference's block_size (src/examples/run_gpt.cc:93-96)
+    num_pages: Optional[int] = None     # None: sized from free device memory
+    memory_fraction: float = 0.85       # share of the free device memory the cache may take
+    max_batch_tokens: int = 2048        # token budget of one step
+    chunk_size: int = 512               # longest prompt portion
+    max_num_seqs: int = 256             # most requests running at a time
+    use_cuda_graphs: bool = True        # record decode-only steps once per batch size and replay them
+
+
+class LLMEngine:
+    def __init__(self, model: Union[str, CausalLM], dtype="bfloat16", device="cuda",
+                 config: Optional[EngineConfig] = None, **overrides):
+        cfg = dataclasses.replace(config or EngineConfig(), **overrides)
+        self.config = cfg
+        self.model = load_model(model, dtype, device) if isinstance(model, str) else model
+        self.device = self.model.device
+        specs = self.model.definition.cache_specs()
+        max_len = self.model.max_positions or 1 << 20
+        num_pages = cfg.num_pages
+        if num_pages is None:
+            num_pages = self._pages_that_fit(specs, cfg, max_len)
+        self.cache = CacheManager(specs, self.model.dtype, self.device, cfg.page_size, num_pages,
+                                  cfg.max_num_seqs, max_len)
+        self.runner = ModelRunner(self.model, self.cache, cfg.max_batch_tokens,
+                                  use_cuda_graphs=cfg.use_cuda_graphs)
+        self.scheduler = Scheduler(self.cache, cfg.max_batch_tokens, cfg.chunk_size, cfg.max_num_seqs,
+                                   self.model.max_positions)
+        self.sampler = Sampler(self.device)
+        self._ids = itertools.count()
+        self.requests: Dict[Any, Request] = {}
+        self.stats = dict(steps=0, prompt_tokens=0, decode_tokens=0)
+
+    def _pages_that_fit(self, specs, cfg: EngineConfig, max_len: int) -> int:
+        from ..parts.base import PagedKVSpec
+        esize = torch.empty((), dtype=self.model.dtype).element_size()
+        per_page = sum(2 * s.num_kv_heads * s.head_dim * cfg.page_size * esize
+                       for s in specs if isinstance(s, PagedKVSpec))
+        if per_page == 0:
+            return 1
+        if self.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.device)
+        else:
+            free = 1 << 30
+        want = cfg.max_num_seqs * ((max_len + cfg.page_size - 1) // cfg.page_size)
+        return max(1, min(want, int(free * cfg.memory_fraction) // per_page))
+
+    # ------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None):
+        rid = request_id if request_id is not None else next(self._ids)
+        if rid in self.requests:
+            raise ValueError(f"request id {rid!r} is already in use")
+        prompt = [int(t) for t in prompt]
+        vocab = self.model.vocab_size
+        for t in prompt:
+            if t < 0 or t >= vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        req = Request(rid, prompt, params or SamplingParams())
+        self.scheduler.add(req)
+        self.requests[rid] = req
+        return rid
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ---------------------------------------------------------------- step
+    def step(self) -> List[Request]:
+        """One scheduler decision through the GPU; returns the requests that finished in it."""
+        plan = self.scheduler.schedule()
+        if not plan:
+            return self._drain_finished([])
+        entries, samplers, counters = [], [], []
+        for s in plan:
+            r = s.request
+            toks = r.tokens[r.n_computed:r.n_computed + s.n]
+            entries.append(StepEntry(r.slot, toks, r.n_computed, [s.n - 1] if s.samples else []))
+            if s.samples:
+                samplers.append(r.params)
+                counters.append(len(r.output))
+            if s.n == 1 and r.n_computed >= len(r.prompt):
+                self.stats["decode_tokens"] += 1
+            else:
+                self.stats["prompt_tokens"] += s.n
+        logits = self.runner.step(entries)
+        sampled = self.sampler.sample(logits, samplers, counters) if samplers else []
+        self.stats["steps"] += 1
+        return self._drain_finished(self.scheduler.update(plan, sampled))
+
+    def _drain_finished(self, done: List[Request]) -> List[Request]:
+        # requests the scheduler gave up on (cache_full) finish without a step of their own
+        seen = {id(r) for r in done}
+        for r in self.scheduler.finished:
+            if id(r) not in seen and r.id in self.requests and not getattr(r, "_reported", False):
+                done.append(r)
+        for r in done:
+            r._reported = True
+        return done
+
+    # ------------------------------------------------------------ generate
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[List[int]]:
+        """Generate for every prompt (token ids in, token ids out), batching them continuously."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, dataclasses.replace(sp)) for p, sp in zip(prompts, params)]
+        while self.has_work():
+            self.step()
+        out = [self.requests[i].output for i in ids]
+        for i in ids:
+            del self.requests[i]
+        return out

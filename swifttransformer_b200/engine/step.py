@@ -97,14 +97,16 @@ class StepContext:
 class ModelRunner:
     """Owns the model, its cache and the staging buffers; runs steps."""
 
-    def __init__(self, model: CausalLM, cache: CacheManager, max_batch_tokens: int = 8192):
+    def __init__(self, model: CausalLM, cache: CacheManager, max_batch_tokens: int = 8192,
+                 use_cuda_graphs: bool = False):
         self.model, self.cache = model, cache
         self.device = model.device
         self.max_batch_tokens = max_batch_tokens
+        self.use_cuda_graphs = use_cuda_graphs and self.device.type == "cuda" and model.graph_safe()
         self.max_seqs = cache.max_seqs
         self.tile_rows = 64
         cap = self._layout(max_batch_tokens, self.max_seqs, max_batch_tokens,
-                           [max_batch_tokens + self.max_seqs * 4] * len(cache.groups))["total"]
+                           [self.max_seqs * cache.max_pages_per_seq + 16] * len(cache.groups))["total"]
         pin = self.device.type == "cuda"
         # two pinned staging buffers used in turn: a buffer is rewritten only after
         # the copy that last read it has finished (the host may run ahead of the GPU)

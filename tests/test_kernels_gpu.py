@@ -1,0 +1,308 @@
+"""Each CUDA kernel alone against its plain reference (tests/cpu_ops.py), at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import cpu_ops
+from swifttransformer_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def close(got, ref, dtype, what, rel=None):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    rel = rel if rel is not None else (2e-6 if dtype == torch.float32 else 1e-2)
+    tol = rel * max(ref.abs().max().item(), 1e-6)
+    err = (got - ref).abs().max().item()
+    assert err <= tol, f"{what}: max error {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [24, 1000, 2048])
+def test_embed(dtype, width):
+    vocab, n, off = 301, 37, 2
+    table, ptab = rnd((vocab, width), dtype, 1), rnd((50 + off, width), dtype, 2)
+    ids = torch.randint(0, vocab, (n,), dtype=torch.int32)
+    pos = torch.randint(0, 50, (n,), dtype=torch.int32)
+    for out_dtype in {torch.float32, dtype}:
+        ref = cpu_ops.embed(ids, table, torch.empty(n, width, dtype=out_dtype), pos, ptab, off)
+        got = ops.embed(ids.to(DEV), table.to(DEV), torch.empty(n, width, dtype=out_dtype, device=DEV),
+                        pos.to(DEV), ptab.to(DEV), off)
+        close(got, ref, out_dtype, "embed+pos", rel=1e-6 if out_dtype == torch.float32 else 4e-3)
+        ref = cpu_ops.embed(ids, table, torch.empty(n, width, dtype=out_dtype))
+        got = ops.embed(ids.to(DEV), table.to(DEV), torch.empty(n, width, dtype=out_dtype, device=DEV))
+        assert torch.equal(got.cpu(), ref)
+    x = rnd((n, width), dtype, 3)
+    ref = cpu_ops.add_positions(x, pos, ptab, off, torch.empty(n, width))
+    got = ops.add_positions(x.to(DEV), pos.to(DEV), ptab.to(DEV), off, torch.empty(n, width, device=DEV))
+    close(got, ref, torch.float32, "add_positions", rel=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm", "none"])
+@pytest.mark.parametrize("width", [40, 777, 7168])
+def test_add_norm(dtype, kind, width):
+    n = 19
+    # a row offset far from zero shows a one-pass variance; the two-pass one must not care
+    x = rnd((n, width), torch.float32, 4) + 30.0
+    delta, dbias = rnd((n, width), dtype, 5), rnd((width,), torch.float32, 6)
+    gamma, beta = 1 + rnd((width,), torch.float32, 7, 0.1), rnd((width,), torch.float32, 8, 0.1)
+    eps = 3e-4
+    # pre-norm use: residual updated, normalised copy out
+    xr = x.clone()
+    ref_out = torch.empty(n, width, dtype=dtype)
+    cpu_ops.add_norm(xr, delta=delta, delta_bias=dbias, resid_out=xr, gamma=gamma, beta=beta, eps=eps, kind=kind,
+                     out_act=ref_out)
+    xg = x.to(DEV)
+    got_out = torch.empty(n, width, dtype=dtype, device=DEV)
+    ops.add_norm(xg, delta=delta.to(DEV), delta_bias=dbias.to(DEV), resid_out=xg, gamma=gamma.to(DEV),
+                 beta=beta.to(DEV), eps=eps, kind=kind, out_act=got_out)
+    close(xg, xr, torch.float32, "residual", rel=1e-6)
+    close(got_out, ref_out, dtype, f"{kind} out", rel=5e-5 if dtype == torch.float32 else 8e-3)
+    # post-norm use: residual replaced by the normalised row; and a gather of rows without affine
+    xr = x.clone()
+    cpu_ops.add_norm(xr, delta=delta, eps=eps, kind=kind, out_act=ref_out, out_f32=xr)
+    xg = x.to(DEV)
+    ops.add_norm(xg, delta=delta.to(DEV), eps=eps, kind=kind, out_act=got_out, out_f32=xg)
+    close(xg, xr, torch.float32, "normalised residual", rel=5e-5)
+    rows = torch.tensor([3, 0, 18, 3], dtype=torch.int32)
+    ref_g = torch.empty(4, width, dtype=dtype)
+    cpu_ops.add_norm(x, delta=delta, delta_bias=dbias, gamma=gamma, beta=beta, eps=eps, kind=kind, rows=rows,
+                     out_act=ref_g)
+    got_g = torch.empty(4, width, dtype=dtype, device=DEV)
+    xg = x.to(DEV)
+    ops.add_norm(xg, delta=delta.to(DEV), delta_bias=dbias.to(DEV), gamma=gamma.to(DEV), beta=beta.to(DEV),
+                 eps=eps, kind=kind, rows=rows.to(DEV), out_act=got_g)
+    close(got_g, ref_g, dtype, "gathered rows", rel=5e-5 if dtype == torch.float32 else 8e-3)
+    assert torch.equal(xg.cpu(), x), "a gathered norm must not touch the residual stream"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["none", "relu", "gelu"])
+def test_bias_act(dtype, act):
+    y, b = rnd((33, 530), dtype, 9), rnd((530,), torch.float32, 10)
+    ref = cpu_ops.bias_act(y.clone(), b, act)
+    got = ops.bias_act(y.to(DEV), b.to(DEV), act)
+    close(got, ref, dtype, "bias_act", rel=1e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 50, 24), (5, 130, 77), (70, 333, 520), (129, 64, 2048)])
+def test_gemm_plain(dtype, shape):
+    n, m, k = shape
+    a, w, b = rnd((n, k), dtype, 11), rnd((m, k), dtype, 12, 0.1), rnd((m,), torch.float32, 13)
+    for act in ("none", "relu"):
+        ref = cpu_ops.linear(a, w, b, act, torch.float32)
+        got = ops.gemm_plain(a.to(DEV), w.to(DEV), b.to(DEV), act, torch.float32)
+        close(got, ref, torch.float32, "gemm_plain", rel=3e-6)
+    got = ops.linear(a.to(DEV), w.to(DEV), b.to(DEV), "relu")
+    ref = cpu_ops.linear(a, w, b, "relu")
+    close(got, ref, dtype, "linear", rel=3e-6 if dtype == torch.float32 else 1e-2)
+    # float32 logits out of bfloat16 operands (the output head)
+    got = ops.linear(a.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    close(got, cpu_ops.linear(a, w, out_dtype=torch.float32), torch.float32, "linear f32 out",
+          rel=3e-6 if dtype == torch.float32 else 1e-5)
+
+
+def test_gemm_plain_rows_do_not_depend_on_the_batch():
+    a, w = rnd((70, 200), torch.float32, 14).to(DEV), rnd((90, 200), torch.float32, 15).to(DEV)
+    full = ops.gemm_plain(a, w)
+    one = ops.gemm_plain(a[37:38].contiguous(), w)
+    assert torch.equal(full[37:38], one)
+
+
+def make_cache(dtype, n_seqs, lens, nkv, d, page_size, n_layers, seed, shuffle=True):
+    """A pool with random contents (stale values everywhere), random page assignment, and the true K/V."""
+    g = torch.Generator().manual_seed(seed)
+    max_pages = max((l + page_size - 1) // page_size for l in lens) + 1
+    num_pages = sum((l + page_size - 1) // page_size for l in lens) + 3
+    pool = (torch.randn((num_pages, n_layers, 2, nkv, page_size, d), generator=g) * 3).to(dtype)
+    perm = torch.randperm(num_pages, generator=g).tolist() if shuffle else list(range(num_pages))
+    bt = torch.full((n_seqs + 2, max_pages), -1, dtype=torch.int32)
+    slots = torch.randperm(n_seqs + 2, generator=g)[:n_seqs].to(torch.int32)
+    for i, l in enumerate(lens):
+        for j in range((l + page_size - 1) // page_size):
+            bt[int(slots[i]), j] = perm.pop()
+    return pool, bt, slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qkv_to_cache(dtype):
+    nh, nkv, d, ps, L = 6, 2, 24, 8, 3
+    lens, new = [13, 40, 1], [5, 40, 1]
+    pool, bt, slots = make_cache(dtype, 3, lens, nkv, d, ps, L, 20)
+    pos, seq = [], []
+    for i, (l, n) in enumerate(zip(lens, new)):
+        pos += list(range(l - n, l)); seq += [i] * n
+    n = len(pos)
+    pos, seq = torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32)
+    qkv, bias = rnd((n, (nh + 2 * nkv) * d), dtype, 21), rnd(((nh + 2 * nkv) * d,), torch.float32, 22)
+    ref_pool, ref_q, st = pool.clone(), torch.empty(n, nh * d, dtype=dtype), torch.zeros(1, dtype=torch.int32)
+    cpu_ops.qkv_to_cache(qkv, bias, ref_q, ref_pool, 1, pos, seq, slots, bt, nh, nkv, d, st)
+    gp, gq, gst = pool.to(DEV), torch.empty(n, nh * d, dtype=dtype, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.qkv_to_cache(qkv.to(DEV), bias.to(DEV), gq, gp, 1, pos.to(DEV), seq.to(DEV), slots.to(DEV), bt.to(DEV),
+                     nh, nkv, d, gst)
+    assert int(gst.item()) == 0
+    close(gq, ref_q, dtype, "q", rel=1e-6 if dtype == torch.float32 else 8e-3)
+    close(gp, ref_pool, dtype, "pool", rel=1e-6 if dtype == torch.float32 else 8e-3)
+    assert torch.equal(gp[:, 0].cpu(), pool[:, 0]) and torch.equal(gp[:, 2].cpu(), pool[:, 2]), "other layers untouched"
+    # a hole in the block table is reported, not written through
+    bt2 = bt.clone(); bt2[int(slots[1]), 2] = -1
+    ops.qkv_to_cache(qkv.to(DEV), bias.to(DEV), gq, gp, 1, pos.to(DEV), seq.to(DEV), slots.to(DEV), bt2.to(DEV),
+                     nh, nkv, d, gst)
+    assert int(gst.item()) == 1
+
+
+def attention_case(dtype, nh, nkv, d, ps, lens, new, seed, window=0):
+    L = 2
+    pool, bt, slots = make_cache(dtype, len(lens), lens, nkv, d, ps, L, seed)
+    pos, seq, q_start = [], [], [0]
+    for i, (l, n) in enumerate(zip(lens, new)):
+        pos += list(range(l - n, l)); seq += [i] * n; q_start.append(q_start[-1] + n)
+    n = len(pos)
+    t = dict(pos=torch.tensor(pos, dtype=torch.int32), seq=torch.tensor(seq, dtype=torch.int32),
+             q_start=torch.tensor(q_start, dtype=torch.int32),
+             start=torch.tensor([l - m for l, m in zip(lens, new)], dtype=torch.int32))
+    q = rnd((n, nh * d), dtype, seed + 1)
+    scale = 1 / math.sqrt(d)
+    ref = torch.zeros(n, nh * d, dtype=dtype)
+    cpu_ops.attention_plain(q, pool, 1, ref, t["pos"], t["seq"], slots, bt, nh, scale, window)
+    return pool, bt, slots, t, q, scale, ref
+
+
+ATT_SHAPES = [  # nh, nkv, d, page_size
+    (4, 4, 16, 8), (3, 3, 32, 16), (5, 5, 48, 32), (6, 2, 64, 16), (2, 1, 80, 4), (4, 4, 128, 16), (2, 2, 256, 64),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_plain(dtype, shape, window):
+    nh, nkv, d, ps = shape
+    lens, new = [150, 9, 300, 1], [150, 2, 1, 1]
+    pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 30, window)
+    out = torch.zeros_like(ref, device=DEV)
+    ops.attention_plain(q.to(DEV), pool.to(DEV), 1, out, t["pos"].to(DEV), t["seq"].to(DEV), slots.to(DEV),
+                        bt.to(DEV), nh, scale, window)
+    close(out, ref, dtype, "attention_plain", rel=3e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attention_decode(shape, window, n_splits):
+    nh, nkv, d, ps = shape
+    dtype = torch.bfloat16
+    lens, new = [150, 9, 700, 1, 64], [1, 2, 1, 1, 3]
+    pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 40, window)
+    n = q.shape[0]
+    items = torch.tensor([i for i in range(n) if i != 2], dtype=torch.int32)   # token 2 is left to "another kernel"
+    out = torch.full_like(ref, 7.0, device=DEV)
+    partial = torch.empty(ops.attention_decode_scratch(len(items), nh, d, n_splits) + 1, device=DEV)
+    ops.attention_decode(q.to(DEV), pool.to(DEV), 1, out, items.to(DEV), len(items), t["pos"].to(DEV),
+                         t["seq"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window, n_splits, partial)
+    close(out[items.long()], ref[items.long()], dtype, "attention_decode", rel=1e-2)
+    assert torch.all(out[2] == 7.0), "a token that is not in the item list must not be written"
+
+
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_prefill(shape, window):
+    nh, nkv, d, ps = shape
+    dtype = torch.bfloat16
+    lens, new = [150, 200, 300, 64, 17], [150, 70, 16, 64, 17]
+    pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 50, window)
+    tiles = []
+    for i, m in enumerate(new):
+        if i == 2:
+            continue                                   # request 2 is left to "another kernel"
+        tiles += [(i, off) for off in range(0, m, 64)]
+    tiles_t = torch.tensor(tiles, dtype=torch.int32).flatten()
+    out = torch.full_like(ref, 7.0, device=DEV)
+    ops.attention_prefill(q.to(DEV), pool.to(DEV), 1, out, tiles_t.to(DEV), len(tiles), t["q_start"].to(DEV),
+                          t["start"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window)
+    keep = t["seq"] != 2
+    close(out[keep], ref[keep], dtype, "attention_prefill", rel=1.5e-2)
+    assert torch.all(out[~keep] == 7.0)
+
+
+def test_attention_finds_a_far_key_among_hundreds():
+    """One key far back is made to dominate: a kernel that skips or misplaces it shows at once."""
+    nh, nkv, d, ps = 2, 2, 64, 16
+    for dtype in DTYPES:
+        lens, new = [600], [1]
+        pool, bt, slots, t, q, scale, _ = attention_case(dtype, nh, nkv, d, ps, lens, new, 60)
+        far = 37
+        page = int(bt[int(slots[0]), far // ps])
+        pool[page, 1, 0, :, far % ps, :] = (q[0].float().view(nh, d) * 4).to(dtype)   # key aligned with the query
+        pool[page, 1, 1, :, far % ps, :] = 100.0
+        ref = torch.zeros(1, nh * d, dtype=dtype)
+        cpu_ops.attention_plain(q, pool, 1, ref, t["pos"], t["seq"], slots, bt, nh, scale)
+        assert ref.float().mean() > 90
+        args = (t["pos"].to(DEV), t["seq"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale)
+        out = torch.zeros_like(ref, device=DEV)
+        ops.attention_plain(q.to(DEV), pool.to(DEV), 1, out, *args)
+        close(out, ref, dtype, "plain far key", rel=3e-6 if dtype == torch.float32 else 1e-2)
+        if dtype == torch.bfloat16:
+            for ns in (1, 4):
+                out = torch.zeros_like(ref, device=DEV)
+                partial = torch.empty(ops.attention_decode_scratch(1, nh, d, ns) + 1, device=DEV)
+                ops.attention_decode(q.to(DEV), pool.to(DEV), 1, out, None, 1, *args, 0, ns, partial)
+                close(out, ref, dtype, "decode far key", rel=1e-2)
+
+
+def test_argmax_and_sample():
+    g = torch.Generator().manual_seed(70)
+    logits = torch.randn((9, 50272), generator=g) * 3
+    logits[3, 100] = logits[3, 40000] = 50.0          # a tie: the lowest id wins
+    got = ops.argmax(logits.to(DEV)).cpu()
+    assert torch.equal(got, cpu_ops.argmax(logits)) and int(got[3]) == 100
+    n = logits.shape[0]
+    temps = torch.tensor([0.0, 0.8, 1.0, 0.0, 1.5, 0.7, 1.0, 0.3, 2.0])
+    topk = torch.tensor([0, 0, 50, 0, 5, 1, 0, 1000, 0], dtype=torch.int32)
+    seeds = torch.arange(n, dtype=torch.int64) + 1234
+    same = 0
+    for step in range(20):
+        counters = torch.full((n,), step, dtype=torch.int64)
+        ref = cpu_ops.sample(logits, temps, topk, seeds, counters)
+        got = ops.sample(logits.to(DEV), temps.to(DEV), topk.to(DEV), seeds.to(DEV), counters.to(DEV)).cpu()
+        for r in range(n):
+            if int(got[r]) == int(ref[r]):
+                same += 1
+            else:
+                # float32 vs float64 CDF: a draw that lands within rounding of a boundary may
+                # pick the neighbouring kept id; it must still be a kept id of similar mass
+                assert temps[r] > 0
+                k = int(topk[r])
+                if k > 0:
+                    kth = torch.sort(logits[r], descending=True).values[k - 1]
+                    assert logits[r, int(got[r])] >= kth
+    assert same >= 20 * n - 2
+    assert int(got[5]) == int(torch.argmax(logits[5]))   # top_k = 1 is greedy
+    assert abs(ops.uniform(5, 9) - cpu_ops.uniform(5, 9)) == 0.0
+
+
+def test_sampling_distribution():
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5]]).repeat(4000, 1)
+    n = logits.shape[0]
+    got = ops.sample(logits.to(DEV), torch.full((n,), 0.7, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+                     torch.full((n,), 99, dtype=torch.int64, device=DEV),
+                     torch.arange(n, dtype=torch.int64, device=DEV)).cpu()
+    freq = torch.bincount(got.long(), minlength=5).double() / n
+    p = torch.softmax(logits[0].double() / 0.7, 0)
+    assert (freq - p).abs().max() < 0.03
+
+
+def test_cpu_tensors_are_refused():
+    with pytest.raises(ops.KernelError):
+        ops.bias_act(torch.zeros(2, 2), torch.zeros(2), "relu")
