@@ -1,0 +1,258 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: OPT-1.3B layer sizes with random bfloat16 weights, a batch of 8 requests with 512-token
+prompts that then decode; ``value`` is decoded tokens per second over K decode steps timed with CUDA
+events on the device; ``e2e`` is the same through ``LLMEngine.step`` (host token ids in, sampled ids
+out, wall clock).  Also reported: a 2,048-token prefill, the decode step's HBM roofline fraction, and
+decode at batch 1 and 64.  Prints ONE JSON line.  For --gpus > 1 it says that the engine is
+single-GPU and exits with 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        out = dict(FALLBACK_PEAKS)
+        for k in out:
+            if isinstance(raw.get(k), (int, float)) and raw[k] > 0:
+                out[k] = float(raw[k])
+        out["source"] = "measured"
+        return out
+    except Exception:
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6 and parts[0].isdigit():
+                self.rows.append(parts)
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(int(r[0]) for r in self.rows)),
+                "sm_max_mhz": int(self.rows[0][1]), "reasons": reasons, "samples": len(self.rows)}
+
+
+def prefill_flops(cfg, n_layers, n):
+    H, F, V = cfg.hidden_size, cfg.ffn_dim, cfg.vocab_size
+    per_layer = 2 * n * H * 3 * H + 2 * n * H * H + 2 * 2 * n * H * F
+    attn = 2 * 2 * H * n * (n + 1) // 2            # QK^T and PV over the causal half
+    return n_layers * (per_layer + attn) + 2 * H * V   # + the output product for the one wanted row
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model-name", default="opt_1.3b")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "LLMServe/SwiftTransformer cannot be built offline: its xformers submodule is empty, "
+                          "CMake fetches googletest/json/argparse from the network, and it needs MPI headers"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import dataclasses
+    import numpy as np
+    import torch
+    from swifttransformer_b200 import ops
+    from swifttransformer_b200.config import opt_preset
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.engine.step import StepEntry
+    from swifttransformer_b200.models import random_model
+    from swifttransformer_b200.sampling import SamplingParams
+
+    peaks = load_peaks()
+    cfg = opt_preset(args.model_name)
+    full_layers = cfg.num_hidden_layers
+    if args.layers and args.layers < full_layers:
+        cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
+    torch.cuda.set_device(0)
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    P, K, W = args.prompt_len, args.steps, args.warmup
+    ctx_max = cfg.max_position_embeddings
+    gen_room = min(ctx_max - P, 2 * (K + W) + 16)
+    rng = np.random.default_rng(0)
+
+    def new_engine(batch):
+        pages = batch * ((P + gen_room + 15) // 16 + 1) + (2048 // 16 + 2)
+        return LLMEngine(model, page_size=16, num_pages=pages, max_batch_tokens=max(2048, batch * P if batch * P <= 8192 else 4096),
+                         chunk_size=2048, max_num_seqs=max(batch, 1))
+
+    def prompts(batch, n):
+        return [rng.integers(3, cfg.vocab_size, n).tolist() for _ in range(batch)]
+
+    def decode_device(batch, steps, warmup):
+        """Device-timed decode: prompts prefilled through the runner, then `steps` recorded decode steps."""
+        eng = new_engine(batch)
+        slots = [eng.cache.alloc_slot() for _ in range(batch)]
+        lens = [0] * batch
+        for i, p in enumerate(prompts(batch, P)):
+            eng.runner.step([StepEntry(slots[i], p, 0, [])])
+            lens[i] = P
+        toks = rng.integers(3, cfg.vocab_size, (warmup + steps, batch)).tolist()
+
+        def one(k):
+            entries = [StepEntry(slots[i], [toks[k][i]], lens[i], [0]) for i in range(batch)]
+            logits = eng.runner.step(entries)
+            ops.argmax(logits)
+            for i in range(batch):
+                lens[i] += 1
+        for k in range(warmup):
+            one(k)
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for k in range(warmup, warmup + steps):
+            one(k)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        kernels = eng.runner.kernels_last_step + 1
+        mean_ctx = P + warmup + steps / 2
+        step_bytes = model.step_param_bytes() + batch * mean_ctx * eng.cache.bytes_per_token()
+        eng.runner.check_status()
+        return dict(ms=ms, tok_s=batch / ms * 1e3, kernels_per_step=kernels, bytes=step_bytes,
+                    graph_steps=eng.runner.graph_steps)
+
+    def decode_e2e(batch, steps, warmup):
+        """The same through LLMEngine.step: host ids in, sampled ids out, wall clock."""
+        eng = new_engine(batch)
+        sp = SamplingParams(max_new_tokens=warmup + steps + 8, ignore_eos=True)
+        for p in prompts(batch, P):
+            eng.add_request(p, dataclasses.replace(sp))
+        while any(r.n_computed < len(r.prompt) for r in eng.requests.values()):
+            eng.step()
+        for _ in range(warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        h2d0 = eng.runner.h2d_bytes
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            eng.step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        return dict(tok_s=batch * steps / dt, ms=dt / steps * 1e3,
+                    h2d=(eng.runner.h2d_bytes - h2d0) / steps, d2h=batch * 4)
+
+    def prefill(n):
+        eng = new_engine(1)
+        times = []
+        for it in range(5):
+            slot = eng.cache.alloc_slot()
+            p = prompts(1, n)[0]
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            logits = eng.runner.step([StepEntry(slot, p, 0, [n - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            eng.cache.free_slot(slot)
+        ms = min(times[2:])
+        fl = prefill_flops(cfg, cfg.num_hidden_layers, n)
+        return dict(value=n / ms * 1e3, tokens=n, ms=ms, frac=fl / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12))
+
+    with ClockSampler(0) as clocks:
+        dev = decode_device(args.batch, K, W)
+    e2e = decode_e2e(args.batch, K, W)
+    out = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2048 tokens (OPT-1.3B fp16)",
+        "value": round(dev["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(dev["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), token ids uniform in [3,vocab))",
+        "impl": "ours",
+        "config": {"model": args.model_name, "global_batch": args.batch, "seq_len": ctx_max,
+                   "parallelism": "single-gpu", "prompt_len": P, "layers": cfg.num_hidden_layers,
+                   "layers_full": full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "head_dim": cfg.head_dim, "ffn_dim": cfg.ffn_dim, "vocab": cfg.vocab_size, "page_size": 16,
+                   "cuda_graphs": dev["graph_steps"] > 0, "l2": "inputs larger than L2 (weights read every step)",
+                   "peaks": peaks["source"]},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
+                "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])},
+        "gpu_launches": int(dev["kernels_per_step"] * K),
+        "roofline": {"bound": "hbm", "achieved": round(dev["bytes"] / (dev["ms"] * 1e-3) / 1e9, 1),
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(dev["bytes"] / (dev["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)},
+    }
+    if not args.no_points:
+        pf = prefill(2048)
+        out["prefill"] = {"value": round(pf["value"], 1), "tokens": pf["tokens"], "ms": round(pf["ms"], 3),
+                          "frac": round(pf["frac"], 4)}
+        pts = {}
+        for b in (1, 64):
+            r = decode_device(b, min(K, 64), W)
+            pts[f"decode_b{b}"] = round(r["tok_s"], 1)
+            pts[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        out["points"] = pts
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

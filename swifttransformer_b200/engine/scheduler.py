@@ -60,11 +60,11 @@ class Request:
 class Scheduled:
     request: Request
     n: int                           # tokens of the request that run in this step
+    # whether this portion reaches the request's last token, so that a token is drawn after it
+    samples: bool = False
 
-    @property
-    def samples(self) -> bool:
-        """Whether this portion reaches the request's last token, so that a token is drawn after it."""
-        return self.request.n_computed + self.n == self.request.n_tokens
+    def __post_init__(self):
+        self.samples = self.request.n_computed + self.n == self.request.n_tokens
 
 
 class Scheduler:
@@ -115,6 +115,7 @@ class Scheduler:
     def _try_schedule(self) -> List[Scheduled]:
         budget = self.max_batch_tokens
         plan: List[Scheduled] = []
+        preemptions_before = self.num_preemptions
         # 1. one token for every decoding request (oldest first); preempt the youngest when a page is missing
         for req in sorted(self.running, key=lambda r: r.admitted_at):
             if req.state != RUNNING or req.remaining != 1 or budget < 1:
@@ -140,14 +141,20 @@ class Scheduler:
             if n > 0:
                 plan.append(Scheduled(req, n))
                 budget -= n
-        # 3. admit waiting requests, first come first served
-        while self.waiting and budget >= 1 and len(self.running) < self.max_num_seqs:
+        # 3. admit waiting requests, first come first served; not in a step that had to preempt
+        #    (the pages just freed are for the requests that stayed)
+        while (self.waiting and budget >= 1 and len(self.running) < self.max_num_seqs
+               and self.num_preemptions == preemptions_before):
             req = self.waiting[0]
             slot = self.cache.alloc_slot()
             if slot is None:
                 break
             req.slot = slot
-            n = self._fit_portion(req, min(req.remaining, self.chunk_size, budget))
+            # a newcomer is admitted only if its whole next portion has pages: a request that
+            # holds pages but cannot move would only stand in the way of those running
+            n = min(req.remaining, self.chunk_size, budget)
+            if not self.cache.reserve(slot, req.n_computed, req.n_computed + n):
+                n = 0
             if n <= 0:
                 self.cache.free_slot(slot)
                 req.slot = None

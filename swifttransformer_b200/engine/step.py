@@ -12,6 +12,11 @@ greedy token per request; its per-step host work is eight blocking copies
 (gpt.cc:92-103,118-144,269-300,536-539).  Here every index array of the step
 is packed into one pinned buffer and reaches the device in one asynchronous
 copy; block-table changes ride along and are applied by a small kernel.
+
+Steps that hold only single tokens whose logits are all wanted (decoding) are
+recorded once per batch-size bucket into a CUDA graph and replayed: the step's
+index arrays live at fixed addresses, the batch is padded to the bucket with
+entries at position -1, which every kernel skips.
 """
 from __future__ import annotations
 
@@ -43,26 +48,22 @@ class StepEntry:
     want: Sequence[int] = ()        # places among `tokens` whose logits are wanted
 
 
+def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148) -> int:
+    """Parts the key range of a single-token query is cut into, so that the launch fills the GPU."""
+    blocks = max(1, n_items * nh)
+    s = max(1, (2 * sms + blocks - 1) // blocks)
+    return min(s, max(1, max_kv // 128), 32)
+
+
 class AttentionPlan:
     """Which of the step's tokens go to which attention kernel (bfloat16 path)."""
 
     def __init__(self, items, n_items, tiles, n_tiles, max_item_kv):
         self.items, self.n_items, self.tiles, self.n_tiles = items, n_items, tiles, n_tiles
         self.max_item_kv = max_item_kv
-        self.fixed_splits: Optional[int] = None
 
     def splits(self, nh: int) -> int:
-        """Parts the key range of a single-token query is cut into, so that the launch fills the GPU."""
-        if self.fixed_splits is not None:
-            return self.fixed_splits
         return choose_splits(self.n_items, nh, self.max_item_kv)
-
-
-def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148) -> int:
-    blocks = max(1, n_items * nh)
-    s = max(1, (2 * sms + blocks - 1) // blocks)
-    s = min(s, max(1, max_kv // 128), 32)
-    return s
 
 
 class StepContext:
@@ -70,54 +71,151 @@ class StepContext:
 
     Device tensors (int32): token_ids[N], positions[N], seq_of_token[N], q_start[B+1],
     start_pos[B], kv_len[B] (length after the step), slots[B], want_rows[n_want].
-    Host lists of the same names with an ``h_`` prefix.
+    Host lists of the same names with an ``h_`` prefix (None while a graph is recorded
+    or replayed: a part that needs them is not ``graph_safe``).
     """
 
     def __init__(self):
         self.n_tokens = self.n_seqs = self.n_want = 0
         self.token_ids = self.positions = self.seq_of_token = None
         self.q_start = self.start_pos = self.kv_len = self.slots = self.want_rows = None
-        self.h_q_start: List[int] = []
-        self.h_start_pos: List[int] = []
-        self.h_kv_len: List[int] = []
-        self.h_slots: List[int] = []
+        self.h_q_start: Optional[List[int]] = None
+        self.h_start_pos: Optional[List[int]] = None
+        self.h_kv_len: Optional[List[int]] = None
+        self.h_slots: Optional[List[int]] = None
         self.status: Optional[torch.Tensor] = None
         self.act_dtype: torch.dtype = torch.float32
         self.device: Optional[torch.device] = None
         self._plan: Optional[AttentionPlan] = None
-        self._runner: Any = None
+        self._scratch_owner: Any = None
 
     def attention_plan(self) -> AttentionPlan:
         return self._plan
 
     def scratch_f32(self, n: int) -> torch.Tensor:
-        return self._runner._scratch(n)
+        return self._scratch_owner._scratch(n)
+
+
+class _Staging:
+    """Pinned host buffers used in turn, and the device buffer they are copied to.  A host buffer is
+    rewritten only after the copy that last read it has finished (the host may run ahead of the GPU)."""
+
+    def __init__(self, words: int, device: torch.device, turns: int = 2):
+        pin = device.type == "cuda"
+        self.hosts = [torch.zeros(words, dtype=torch.int32, pin_memory=pin) for _ in range(turns)]
+        self.events = [torch.cuda.Event() if pin else None for _ in range(turns)]
+        self.dev = torch.zeros(words, dtype=torch.int32, device=device)
+        self.turn = 0
+        self.bytes_copied = 0
+
+    def begin(self) -> np.ndarray:
+        self.turn = (self.turn + 1) % len(self.hosts)
+        if self.events[self.turn] is not None:
+            self.events[self.turn].synchronize()
+        return self.hosts[self.turn].numpy()
+
+    def commit(self, words: int) -> None:
+        self.dev[:words].copy_(self.hosts[self.turn][:words], non_blocking=True)
+        if self.events[self.turn] is not None:
+            self.events[self.turn].record()
+        self.bytes_copied += 4 * words
+
+
+GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+
+class _DecodeGraph:
+    """One recorded decode step for up to ``cap`` requests."""
+
+    FIELDS = ("token_ids", "positions", "start_pos", "kv_len", "slots")
+
+    def __init__(self, runner: "ModelRunner", cap: int):
+        self.runner, self.cap = runner, cap
+        self.staging = _Staging(5 * cap, runner.device)
+        dev = runner.device
+        ar = torch.arange(cap + 1, dtype=torch.int32, device=dev)
+        d = self.staging.dev
+        ctx = StepContext()
+        ctx.n_tokens = ctx.n_seqs = ctx.n_want = cap
+        ctx.token_ids, ctx.positions = d[0:cap], d[cap:2 * cap]
+        ctx.start_pos, ctx.kv_len, ctx.slots = d[2 * cap:3 * cap], d[3 * cap:4 * cap], d[4 * cap:5 * cap]
+        ctx.seq_of_token, ctx.q_start, ctx.want_rows = ar[:cap], ar, ar[:cap]
+        ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, dev
+        ctx._plan = AttentionPlan(None, cap, None, 0, runner.cache.max_seq_len)
+        ctx._scratch_owner = self
+        self.ctx = ctx
+        self._keep = ar
+        self._scratch_buf: Optional[torch.Tensor] = None
+        self._frozen = False
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.kernels = 0
+
+    def _scratch(self, n: int) -> torch.Tensor:
+        if self._scratch_buf is None or self._scratch_buf.numel() < n:
+            if self._frozen:
+                raise RuntimeError("a recorded step asked for more scratch memory than when it was recorded")
+            self._scratch_buf = torch.empty(max(n, 1), dtype=torch.float32, device=self.runner.device)
+        return self._scratch_buf
+
+    def fill(self, entries: Sequence[StepEntry]) -> None:
+        cap, b = self.cap, len(entries)
+        h = self.staging.begin()
+        h[0:cap] = 0
+        h[cap:2 * cap] = -1                      # padding entries: position -1, skipped by every kernel
+        h[2 * cap:5 * cap] = 0
+        for i, e in enumerate(entries):
+            h[i] = e.tokens[0]
+            h[cap + i] = e.start_pos
+            h[2 * cap + i] = e.start_pos
+            h[3 * cap + i] = e.start_pos + 1
+            h[4 * cap + i] = e.slot
+        self.staging.commit(5 * cap)
+
+    def record(self) -> None:
+        r = self.runner
+        # once without recording: sizes the scratch memory and lets libraries set themselves up
+        r.model.forward(self.ctx, r._entries)
+        torch.cuda.synchronize()
+        self._frozen = True
+        before = ops.launch_count()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=r._graph_pool):
+            self.logits = r.model.forward(self.ctx, r._entries)
+        self.kernels = ops.launch_count() - before
+        self.graph = g
+
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        self.fill(entries)
+        if self.graph is None:
+            self.record()
+        self.graph.replay()
+        return self.logits[:len(entries)]
 
 
 class ModelRunner:
     """Owns the model, its cache and the staging buffers; runs steps."""
 
     def __init__(self, model: CausalLM, cache: CacheManager, max_batch_tokens: int = 8192,
-                 use_cuda_graphs: bool = False):
+                 use_cuda_graphs: bool = True):
         self.model, self.cache = model, cache
         self.device = model.device
         self.max_batch_tokens = max_batch_tokens
         self.use_cuda_graphs = use_cuda_graphs and self.device.type == "cuda" and model.graph_safe()
         self.max_seqs = cache.max_seqs
         self.tile_rows = 64
-        cap = self._layout(max_batch_tokens, self.max_seqs, max_batch_tokens,
-                           [self.max_seqs * cache.max_pages_per_seq + 16] * len(cache.groups))["total"]
-        pin = self.device.type == "cuda"
-        # two pinned staging buffers used in turn: a buffer is rewritten only after
-        # the copy that last read it has finished (the host may run ahead of the GPU)
-        self._hosts = [torch.zeros(cap, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
-        self._host_events = [torch.cuda.Event() if pin else None for _ in range(2)]
-        self._host_turn = 0
-        self._dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._upd_cap = self.max_seqs * cache.max_pages_per_seq + 16
+        words = self._layout(max_batch_tokens, self.max_seqs, max_batch_tokens)["total"]
+        self._staging = _Staging(words, self.device)
+        self._upd_staging = _Staging(1 + 2 * self._upd_cap, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch_buf: Optional[torch.Tensor] = None
         self._entries = cache.entries()
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_cuda_graphs else None
         self.steps_run = 0
+        self.graph_steps = 0
+        self.kernels_last_step = 0
 
     # ------------------------------------------------------------ buffers
     def _scratch(self, n: int) -> torch.Tensor:
@@ -125,29 +223,23 @@ class ModelRunner:
             self._scratch_buf = torch.empty(max(n, 1 << 20), dtype=torch.float32, device=self.device)
         return self._scratch_buf
 
-    def _layout(self, n_cap: int, b_cap: int, w_cap: int, upd_caps: Sequence[int]) -> Dict[str, Any]:
+    def _layout(self, n_cap: int, b_cap: int, w_cap: int) -> Dict[str, Any]:
         off = 0
         lay: Dict[str, Any] = {}
-
-        def take(name, n):
-            nonlocal off
+        for name, n in (("token_ids", n_cap), ("positions", n_cap), ("seq_of_token", n_cap),
+                        ("q_start", b_cap + 1), ("start_pos", b_cap), ("kv_len", b_cap), ("slots", b_cap),
+                        ("want_rows", w_cap), ("items", n_cap),
+                        ("tiles", 2 * ((n_cap + self.tile_rows - 1) // self.tile_rows + b_cap))):
             lay[name] = (off, n)
             off += n
-        g = len(upd_caps)
-        take("upd_count", max(g, 1))
-        for name in ("token_ids", "positions", "seq_of_token"):
-            take(name, n_cap)
-        take("q_start", b_cap + 1)
-        for name in ("start_pos", "kv_len", "slots"):
-            take(name, b_cap)
-        take("want_rows", w_cap)
-        take("items", n_cap)
-        take("tiles", 2 * ((n_cap + self.tile_rows - 1) // self.tile_rows + b_cap))
-        for i, c in enumerate(upd_caps):
-            take(f"upd_idx{i}", c)
-            take(f"upd_val{i}", c)
         lay["total"] = off
         return lay
+
+    @property
+    def h2d_bytes(self) -> int:
+        """Bytes of step metadata copied host -> device so far."""
+        return (self._staging.bytes_copied + self._upd_staging.bytes_copied
+                + sum(g.staging.bytes_copied for g in self._graphs.values()))
 
     # --------------------------------------------------------------- step
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -180,26 +272,49 @@ class ModelRunner:
             raise StepError(f"{len(entries)} requests in one step exceed the limit of {self.max_seqs}")
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run one step; returns float32 logits [number of wanted places, vocab] (None if none wanted)."""
+        """Run one step; returns float32 logits [number of wanted places, vocab] (None if none wanted).
+
+        The returned tensor may be overwritten by the next step: use it (sample from it, copy it) first.
+        """
         self.validate(entries)
-        for e in entries:
-            if not self.cache.can_reserve(e.slot, e.start_pos, e.start_pos + len(e.tokens)):
-                raise OutOfPages(f"no pages left for {len(e.tokens)} tokens of slot {e.slot}")
         # pages for all entries together, or none
-        need = [sum(len(g.missing(e.slot, e.start_pos, e.start_pos + len(e.tokens))) for e in entries)
-                for g in self.cache.groups]
-        for g, n in zip(self.cache.groups, need):
-            if n > g.pool.num_free:
-                raise OutOfPages(f"the step needs {n} pages, {g.pool.num_free} are free")
+        for g in self.cache.groups:
+            need = sum(len(g.missing(e.slot, e.start_pos, e.start_pos + len(e.tokens))) for e in entries)
+            if need > g.pool.num_free:
+                raise OutOfPages(f"the step needs {need} pages, {g.pool.num_free} are free")
         for e in entries:
             ok = self.cache.reserve(e.slot, e.start_pos, e.start_pos + len(e.tokens))
             assert ok
-        ctx = self._build_context(entries)
-        logits = self.model.forward(ctx, self._entries)
+        self._flush_block_tables()
+        before = ops.launch_count()
+        bucket = self._graph_bucket(entries)
+        if bucket:
+            if bucket not in self._graphs:
+                self._graphs[bucket] = _DecodeGraph(self, bucket)
+            dg = self._graphs[bucket]
+            logits = dg.run(entries)
+            self.graph_steps += 1
+            self.kernels_last_step = dg.kernels
+        else:
+            ctx = self._build_context(entries)
+            logits = self.model.forward(ctx, self._entries)
+            self.kernels_last_step = ops.launch_count() - before
         for e in entries:
             self.cache.commit(e.slot, e.start_pos + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def _graph_bucket(self, entries: Sequence[StepEntry]) -> int:
+        if not self.use_cuda_graphs:
+            return 0
+        for e in entries:
+            if len(e.tokens) != 1 or len(e.want) != 1:
+                return 0
+        b = len(entries)
+        for cap in GRAPH_BUCKETS:
+            if cap >= b:
+                return cap
+        return 0
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault (a hole in a block table).  Synchronises."""
@@ -207,24 +322,31 @@ class ModelRunner:
             self.status.zero_()
             raise RuntimeError("a kernel found a token whose position has no page in its block table")
 
+    def _flush_block_tables(self) -> None:
+        """Apply the cache manager's queued block-table changes on the device."""
+        for g in self.cache.groups:
+            u = g.take_updates()
+            while u:
+                part, u = u[:self._upd_cap], u[self._upd_cap:]
+                n = len(part)
+                h = self._upd_staging.begin()
+                h[0] = n
+                h[1:1 + n] = [x[0] for x in part]
+                h[1 + n:1 + 2 * n] = [x[1] for x in part]
+                self._upd_staging.commit(1 + 2 * n)
+                d = self._upd_staging.dev
+                ops.scatter_i32(g.block_table, d[1:1 + n], d[1 + n:1 + 2 * n], d[0:1], n)
+
     def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
         B = len(entries)
         lens = [len(e.tokens) for e in entries]
         N = sum(lens)
         W = sum(len(e.want) for e in entries)
-        updates = [g.take_updates() for g in self.cache.groups]
-        lay = self._layout(N, B, W, [len(u) for u in updates])
-        turn = self._host_turn
-        self._host_turn ^= 1
-        host = self._hosts[turn]
-        if lay["total"] > host.numel():
-            raise StepError("the step's index arrays exceed the staging buffer")
-        if self._host_events[turn] is not None:
-            self._host_events[turn].synchronize()
-        h = host.numpy()
+        lay = self._layout(N, B, W)
+        h = self._staging.begin()
 
         def put(name, values):
-            o, n = lay[name]
+            o, _ = lay[name]
             h[o:o + len(values)] = values
 
         q_start = np.zeros(B + 1, dtype=np.int32)
@@ -240,7 +362,6 @@ class ModelRunner:
             pos[a:b] = np.arange(e.start_pos, e.start_pos + lens[i], dtype=np.int32)
             seq[a:b] = i
             want_rows.extend(int(a) + w for w in e.want)
-        put("upd_count", [len(u) for u in updates] or [0])
         put("token_ids", tok)
         put("positions", pos)
         put("seq_of_token", seq)
@@ -263,22 +384,13 @@ class ModelRunner:
         tiles.sort(reverse=True)
         put("items", items)
         put("tiles", [v for t in tiles for v in (t[1], t[2])])
-        for gi, u in enumerate(updates):
-            put(f"upd_idx{gi}", [x[0] for x in u])
-            put(f"upd_val{gi}", [x[1] for x in u])
-        total = lay["total"]
-        self._dev[:total].copy_(host[:total], non_blocking=True)
-        if self._host_events[turn] is not None:
-            self._host_events[turn].record()
+        self._staging.commit(lay["total"])
+        dev = self._staging.dev
 
         def view(name):
             o, n = lay[name]
-            return self._dev[o:o + n]
+            return dev[o:o + n]
 
-        for gi, (g, u) in enumerate(zip(self.cache.groups, updates)):
-            if u:
-                ops.scatter_i32(g.block_table, view(f"upd_idx{gi}"), view(f"upd_val{gi}"),
-                                self._dev[lay["upd_count"][0] + gi:lay["upd_count"][0] + gi + 1], len(u))
         ctx = StepContext()
         ctx.n_tokens, ctx.n_seqs, ctx.n_want = N, B, W
         ctx.token_ids, ctx.positions, ctx.seq_of_token = view("token_ids"), view("positions"), view("seq_of_token")
@@ -290,5 +402,5 @@ class ModelRunner:
         ctx.h_slots = [e.slot for e in entries]
         ctx.status, ctx.act_dtype, ctx.device = self.status, self.model.dtype, self.device
         ctx._plan = AttentionPlan(view("items"), len(items), view("tiles"), len(tiles), max_item_kv)
-        ctx._runner = self
+        ctx._scratch_owner = self
         return ctx

@@ -51,7 +51,17 @@ def library_path() -> str:
     return _build.ensure_built()
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """How many kernel launchers of this library have been called so far (recorded launches count once)."""
+    return _LAUNCHES
+
+
 def _check(rc: int, what: str) -> None:
+    global _LAUNCHES
+    _LAUNCHES += 1
     if rc == 0:
         return
     if rc < 0:

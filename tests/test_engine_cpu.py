@@ -1,0 +1,103 @@
+"""The engine's host logic without a GPU: the device operations are replaced by their plain CPU references
+(tests/cpu_ops.py), everything else - parts, blocks, step building, cache manager, scheduler, sampler - is
+the product's."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_opt
+from helpers import TINY
+
+
+def session(model_dir, name, max_tokens, **kw):
+    from swifttransformer_b200.engine.replay import TraceSession
+    return TraceSession(model_dir, "float32", max_tokens, page_size=TINY[name]["page_size"], device="cpu", **kw)
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("mode", ["whole", "portions", "mixed"])
+def test_step_function_matches_plain(model_dirs, cpu_ops_installed, name, mode):
+    vocab = TINY[name]["cfg"]["vocab_size"]
+    reqs = {f"r{i}": helpers.random_tokens(vocab, n, 50 + i) for i, n in enumerate([5, 33, 1, 40, 18])}
+    steps = {"whole": helpers.trace_whole, "portions": helpers.trace_portions,
+             "mixed": helpers.trace_mixed}[mode](reqs)
+    s = session(model_dirs[name], name, helpers.live_token_need(steps), max_requests=4)
+    got = helpers.replay(s, steps)
+    helpers.check_against_plain(model_dirs[name], reqs, got, "float32", f"cpu/{name}/{mode}")
+    assert s.cache.free_pages == s.cache.total_pages
+
+
+def test_step_validation(model_dirs, cpu_ops_installed):
+    from swifttransformer_b200.engine import OutOfPages, StepEntry, StepError
+    s = session(model_dirs["a"], "a", 64, max_batch_tokens=256)
+    slot = s.cache.alloc_slot()
+    r = s.runner
+    with pytest.raises(StepError, match="vocabulary"):
+        r.step([StepEntry(slot, [5, 512], 0, [])])
+    with pytest.raises(StepError, match="at least one token"):
+        r.step([StepEntry(slot, [], 0, [])])
+    with pytest.raises(StepError, match="wanted place"):
+        r.step([StepEntry(slot, [5], 0, [1])])
+    with pytest.raises(StepError, match="twice"):
+        r.step([StepEntry(slot, [5], 0, []), StepEntry(slot, [6], 1, [])])
+    with pytest.raises(StepError, match="holds 0 tokens"):
+        r.step([StepEntry(slot, [5], 3, [])])
+    with pytest.raises(StepError, match="positions end at 128"):
+        r.step([StepEntry(slot, [5] * 129, 0, [])])
+    with pytest.raises(OutOfPages):
+        r.step([StepEntry(slot, [5] * 100, 0, [])])
+    assert s.cache.free_pages == s.cache.total_pages
+    assert r.step([StepEntry(slot, [5, 6], 0, [])]) is None
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_greedy_generation_matches_plain(model_dirs, cpu_ops_installed, name):
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs[name], "float32", "cpu")
+    eng = LLMEngine(model, page_size=TINY[name]["page_size"], num_pages=40, max_batch_tokens=24, chunk_size=16,
+                    max_num_seqs=3)
+    vocab = TINY[name]["cfg"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 70 + i) for i, n in enumerate([5, 17, 33, 1])]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=6))
+    cfg, w = plain_opt.load_model(model_dirs[name])
+    for p, o in zip(prompts, outs):
+        assert o == plain_opt.greedy_generate(cfg, w, p, 6)
+    assert eng.cache.free_pages == eng.cache.total_pages
+
+
+def test_preempted_requests_generate_the_same_tokens(model_dirs, cpu_ops_installed):
+    """So few pages that requests are preempted and recomputed: the tokens must not change, for greedy
+    and for seeded temperature sampling alike."""
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    prompts = [helpers.random_tokens(512, n, 90 + i) for i, n in enumerate([9, 14, 11])]
+    params = [SamplingParams(max_new_tokens=10), SamplingParams(temperature=0.8, seed=3, max_new_tokens=10),
+              SamplingParams(temperature=1.2, top_k=20, seed=4, max_new_tokens=10)]
+    roomy = LLMEngine(model, page_size=8, num_pages=64, max_batch_tokens=64, chunk_size=32, max_num_seqs=4)
+    tight = LLMEngine(model, page_size=8, num_pages=6, max_batch_tokens=64, chunk_size=32, max_num_seqs=4)
+    a = roomy.generate(prompts, params)
+    b = tight.generate(prompts, params)
+    assert tight.scheduler.num_preemptions > 0 and roomy.scheduler.num_preemptions == 0
+    assert a == b
+    assert a[1] != a[0][:0] and len(a[1]) == 10
+
+
+def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
+    from swifttransformer_b200 import ops
+    from swifttransformer_b200.sampling import Sampler, SamplingParams
+    rng = np.random.default_rng(0)
+    logits = torch.tensor(rng.normal(size=(6, 300)) * 2, dtype=torch.float32)
+    params = [SamplingParams(temperature=t, top_k=k, seed=s) for t, k, s in
+              [(0.0, 0, 1), (0.8, 0, 2), (1.0, 10, 3), (0.5, 1, 4), (2.0, 0, 5), (0.8, 299, 6)]]
+    got = Sampler("cpu").sample(logits, params, [0, 1, 2, 3, 4, 5])
+    for r, p in enumerate(params):
+        if p.temperature == 0:
+            assert got[r] == int(np.argmax(logits[r].numpy()))
+        else:
+            u = ops.uniform(p.seed, r)
+            assert got[r] == plain_opt.softmax_sample(logits[r].numpy(), p.temperature, u, p.top_k)
