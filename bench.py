@@ -102,6 +102,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run just the device-timed decode loop or just the prefill (for profiling small cases)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -217,6 +219,13 @@ def main():
         fl = prefill_flops(cfg, cfg.num_hidden_layers, n)
         return dict(value=n / ms * 1e3, tokens=n, ms=ms, frac=fl / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12))
 
+    if args.only == "decode":
+        r = decode_device(args.batch, K, W)
+        print(json.dumps({"only": "decode", "ms_per_step": round(r["ms"], 4), "tok_s": round(r["tok_s"], 1)}))
+        return 0
+    if args.only == "prefill":
+        print(json.dumps(dict(prefill(2048), only="prefill")))
+        return 0
     with ClockSampler(0) as clocks:
         dev = decode_device(args.batch, K, W)
     e2e = decode_e2e(args.batch, K, W)

@@ -1,0 +1,314 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with state of its
+own that is registered, built and stepped without touching the package."""
+import dataclasses
+import math
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_opt
+from swifttransformer_b200 import ops
+from swifttransformer_b200.cache import CacheManager
+from swifttransformer_b200.config.base import ModelConfig, register_config
+from swifttransformer_b200.engine.step import ModelRunner, StepEntry
+from swifttransformer_b200.models import LayerStep, ModelDef, load_model, register_model, write_random_model
+from swifttransformer_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Delta, Embedding,
+                                         Mixer, OutputHead, ResidualStream, StateSpec)
+from swifttransformer_b200.weights import MATRIX, ParamSpec
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def rnd(shape, seed, scale=1.0):
+    return (np.random.default_rng(seed).normal(size=shape) * scale).astype(np.float32)
+
+
+def dev(a, dtype=torch.float32):
+    return torch.tensor(a).to(dtype).to(DEV)
+
+
+def bf(a):
+    """Round to bfloat16 and back: what a bfloat16 part sees."""
+    return torch.tensor(a).to(torch.bfloat16).float().numpy()
+
+
+def close(got, ref, dtype, rel32=3e-6, rel16=1.2e-2):
+    got = got.float().cpu().numpy()
+    tol = (rel32 if dtype == torch.float32 else rel16) * max(np.abs(ref).max(), 1e-6)
+    assert np.abs(got - ref).max() <= tol, (np.abs(got - ref).max(), tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    W, n = 200, 9
+    x, g, b = rnd((n, W), 1) + 5, 1 + rnd((W,), 2, 0.1), rnd((W,), 3, 0.1)
+    norm = NORMS.build("layernorm", width=W, eps=2e-4, affine=True, prefix="n")
+    assert [s.name for s in norm.param_specs()] == ["n.weight", "n.bias"]
+    norm.bind({"n.weight": dev(g), "n.bias": dev(b)})
+    xs = dev(x)
+    out = norm.apply(xs, None, act_dtype=dtype)
+    close(out, plain_opt.layer_norm(x.astype(np.float64), g, b, 2e-4), dtype)
+    assert torch.equal(xs.cpu(), torch.tensor(x))
+    plain = NORMS.build("layernorm", width=W, eps=2e-4, affine=False, prefix="n")
+    assert plain.param_specs() == []
+    close(plain.apply(dev(x), None, act_dtype=dtype), plain_opt.layer_norm(x.astype(np.float64), None, None, 2e-4), dtype)
+    rms = NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix="r")
+    rms.bind({"r.weight": dev(g)})
+    ref = x / np.sqrt((x.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-6) * g
+    close(rms.apply(dev(x), None, act_dtype=dtype), ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["relu", "gelu"])
+def test_feed_forward_part(dtype, act):
+    H, F, n = 72, 200, 11
+    w1, b1, w2, b2 = rnd((F, H), 4, 0.2), rnd((F,), 5, 0.2), rnd((H, F), 6, 0.2), rnd((H,), 7, 0.2)
+    x = rnd((n, H), 8)
+    if dtype == torch.bfloat16:
+        w1, w2, x = bf(w1), bf(w2), bf(x)
+    ffn = FEED_FORWARDS.build("dense", hidden=H, inner=F, activation=act, fc1_name="f1", fc2_name="f2", bias=True)
+    ffn.bind({"f1.weight": dev(w1, dtype), "f1.bias": dev(b1), "f2.weight": dev(w2, dtype), "f2.bias": dev(b2)})
+    d = ffn.forward(dev(x, dtype), None)
+    got = d.value.float() + d.bias
+    w = {"fc1.weight": w1.astype(np.float64), "fc1.bias": b1, "fc2.weight": w2.astype(np.float64), "fc2.bias": b2}
+    ref = plain_opt.feed_forward(x.astype(np.float64), w, "", dict(enable_bias=True, activation_function=act))
+    close(got, ref, dtype)
+    with pytest.raises(ValueError, match="swish"):
+        FEED_FORWARDS.build("dense", hidden=H, inner=F, activation="swish", fc1_name="a", fc2_name="b")
+
+
+class OneStep:
+    """A hand-made step context for one request that brings all its tokens at once."""
+
+    def __init__(self, n, cache, slot, start=0):
+        i32 = dict(dtype=torch.int32, device=DEV)
+        self.n_tokens, self.n_seqs = n, 1
+        self.token_ids = torch.zeros(n, **i32)
+        self.positions = torch.arange(start, start + n, **i32)
+        self.seq_of_token = torch.zeros(n, **i32)
+        self.q_start = torch.tensor([0, n], **i32)
+        self.start_pos = torch.tensor([start], **i32)
+        self.kv_len = torch.tensor([start + n], **i32)
+        self.slots = torch.tensor([slot], **i32)
+        self.status = torch.zeros(1, **i32)
+        from swifttransformer_b200.engine.step import AttentionPlan
+        tiles = torch.tensor([v for off in range(0, n, 64) for v in (0, off)], **i32)
+        self._plan = AttentionPlan(torch.arange(n, **i32), n if n < 16 else 0, tiles, 0 if n < 16 else (n + 63) // 64,
+                                   start + n)
+        self._buf = None
+
+    def attention_plan(self):
+        return self._plan
+
+    def scratch_f32(self, k):
+        self._buf = torch.empty(max(k, 1), device=DEV)
+        return self._buf
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n", [7, 90])
+def test_attention_part(dtype, n):
+    H, nh = 96, 3
+    d = H // nh
+    ws = {k: rnd((H, H), 10 + i, 0.15) for i, k in enumerate("qkvo")}
+    bs = {k: rnd((H,), 20 + i, 0.1) for i, k in enumerate("qkvo")}
+    x = rnd((n, H), 30)
+    if dtype == torch.bfloat16:
+        ws = {k: bf(v) for k, v in ws.items()}
+        x = bf(x)
+    mixer = MIXERS.build("attention", hidden=H, num_heads=nh, head_dim=d, bias=True,
+                         names={k: f"a.{k}" for k in "qkvo"})
+    assert len(mixer.param_specs()) == 8
+    t = {}
+    for k in "qkvo":
+        t[f"a.{k}.weight"], t[f"a.{k}.bias"] = dev(ws[k], dtype), dev(bs[k])
+    mixer.bind(t)
+    cache = CacheManager([mixer.cache_spec()], dtype, DEV, page_size=8, num_pages=16, max_seqs=2, max_seq_len=128)
+    slot = cache.alloc_slot()
+    assert cache.reserve(slot, 0, n)
+    for idx, val in cache.groups[0].take_updates():
+        cache.groups[0].block_table.view(-1)[idx] = val
+    ctx = OneStep(n, cache, slot)
+    out = mixer.forward(dev(x, dtype), ctx, cache.entries()[0].view())
+    got = out.value.float() + out.bias
+    w = {}
+    for k, name in zip("qkvo", ("q_proj", "k_proj", "v_proj", "out_proj")):
+        w[f"{name}.weight"], w[f"{name}.bias"] = ws[k].astype(np.float64), bs[k].astype(np.float64)
+    ref = plain_opt.attention_block(x.astype(np.float64), w, "", dict(num_attention_heads=nh, enable_bias=True))
+    close(got, ref, dtype, rel16=2e-2)
+    assert int(ctx.status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    V, E, H, P, off = 300, 40, 56, 30, 2
+    table, pin, pout, ptab = rnd((V, E), 40), rnd((H, E), 41, 0.2), rnd((E, H), 42, 0.2), rnd((P + off, H), 43)
+    if dtype == torch.bfloat16:
+        table, pin, pout, ptab = bf(table), bf(pin), bf(pout), bf(ptab)
+    emb = Embedding(V, E, H, "tok", "pin")
+    pos = POSITION_ENCODINGS.build("learned", max_positions=P, width=H, offset=off, name="pos")
+    head = OutputHead(V, E, H, "head", tied_to="tok", project_out_name="pout")
+    assert [s.shape for s in pos.param_specs()] == [(P + off, H)]
+    tensors = {"tok": dev(table, dtype), "pin": dev(pin, dtype), "pos": dev(ptab, dtype), "pout": dev(pout, dtype)}
+    tensors["head"] = tensors["tok"]
+    for p in (emb, pos, head):
+        p.bind(tensors)
+    ids = np.array([5, 299, 0, 17, 5])
+    positions = np.array([0, 1, 29, 3, 4])
+    x = emb.forward(dev(ids, torch.int32), dev(positions, torch.int32), pos)
+    ref = plain_opt.linear(plain_opt.embed_tokens(ids, table.astype(np.float64)), pin.astype(np.float64)) \
+        + plain_opt.learned_positions(positions, ptab.astype(np.float64), off)
+    close(x, ref, dtype, rel16=6e-3)
+    h = rnd((4, H), 44)
+    if dtype == torch.bfloat16:
+        h = bf(h)
+    logits = head.forward(dev(h, dtype))
+    assert logits.dtype == torch.float32
+    ref = plain_opt.linear(plain_opt.linear(h.astype(np.float64), pout.astype(np.float64)), table.astype(np.float64))
+    close(logits, ref, dtype, rel16=8e-3)
+    with pytest.raises(ValueError, match="input projection"):
+        Embedding(V, E, H, "tok", None)
+
+
+@pytest.mark.parametrize("order", ["pre_norm", "post_norm"])
+def test_block_arrangement(order):
+    """A block with stand-in sub-layers: only the wiring around the residual stream is under test."""
+    W, n = 48, 6
+
+    class Scale(Mixer):
+        def __init__(self, k):
+            self.k = k
+
+        def forward(self, h, ctx, cache=None):
+            return Delta((h.float() * self.k).to(h.dtype), torch.full((W,), 0.25, device=DEV))
+    n1 = NORMS.build("layernorm", width=W, eps=1e-5, affine=False, prefix="a")
+    n2 = NORMS.build("layernorm", width=W, eps=1e-5, affine=False, prefix="b")
+    blk = BLOCKS.build(order, mixer=Scale(2.0), feed_forward=Scale(-0.5), norm1=n1, norm2=n2)
+    x = rnd((n, W), 50)
+    stream = ResidualStream(dev(x), torch.float32)
+    blk.forward(stream, None, None)
+    got = stream.materialise().cpu().numpy()
+    ln = lambda t: plain_opt.layer_norm(t, None, None, 1e-5)
+    x64 = x.astype(np.float64)
+    if order == "pre_norm":
+        r = x64 + 2.0 * ln(x64) + 0.25
+        ref = r + (-0.5) * ln(r) + 0.25
+    else:
+        r = ln(x64 + 2.0 * x64 + 0.25)
+        ref = ln(r + (-0.5) * r + 0.25)
+    assert np.abs(got - ref).max() < 2e-5
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy architecture defined here: layers alternate the package's attention with a mixer that keeps
+# a running average per request in a state slot.  Nothing in the package knows about it.
+# ---------------------------------------------------------------------------------------------
+@register_config
+@dataclasses.dataclass(frozen=True)
+class ToyConfig(ModelConfig):
+    ARCHITECTURE: ClassVar[str] = "ToyStateForCausalLM"
+    vocab_size: int
+    width: int
+    layers: int
+    heads: int
+    inner: int
+    decay: float
+    max_positions: int
+
+
+@MIXERS.register("toy_running_average")
+class RunningAverage(Mixer):
+    """s_t = decay * s_{t-1} + (1 - decay) * h_t per request;  out_t = s_t W^T.  State: s, [width] float32."""
+    graph_safe = False
+
+    def __init__(self, width, decay, name):
+        self.width, self.decay, self.name = width, decay, name
+
+    def param_specs(self):
+        return [ParamSpec(self.name + ".weight", (self.width, self.width), MATRIX)]
+
+    def bind(self, tensors):
+        self.w = tensors[self.name + ".weight"]
+
+    def cache_spec(self):
+        return StateSpec((self.width,), torch.float32)
+
+    def forward(self, h, ctx, cache):
+        out = torch.empty_like(h)
+        for i, slot in enumerate(ctx.h_slots):
+            s = cache.state[slot]
+            for t in range(ctx.h_q_start[i], ctx.h_q_start[i + 1]):
+                s.mul_(self.decay).add_(h[t].float(), alpha=1 - self.decay)
+                out[t] = (s @ self.w.float().t()).to(h.dtype)
+        return Delta(out)
+
+
+@register_model(ToyConfig.ARCHITECTURE)
+def build_toy(cfg):
+    W = cfg.width
+    emb = Embedding(cfg.vocab_size, W, W, "tok.weight")
+    pos = POSITION_ENCODINGS.build("learned", max_positions=cfg.max_positions, width=W, offset=0, name="pos.weight")
+    blocks = []
+    for i in range(cfg.layers):
+        if i % 2 == 0:
+            mixer = MIXERS.build("toy_running_average", width=W, decay=cfg.decay, name=f"l{i}.avg")
+        else:
+            mixer = MIXERS.build("attention", hidden=W, num_heads=cfg.heads, head_dim=W // cfg.heads, bias=False,
+                                 names={k: f"l{i}.{k}" for k in "qkvo"})
+        ffn = FEED_FORWARDS.build("dense", hidden=W, inner=cfg.inner, activation="relu", fc1_name=f"l{i}.up",
+                                  fc2_name=f"l{i}.down", bias=False)
+        blocks.append(BLOCKS.build("pre_norm", mixer=mixer, feed_forward=ffn,
+                                   norm1=NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix=f"l{i}.n1"),
+                                   norm2=NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix=f"l{i}.n2")))
+    head = OutputHead(cfg.vocab_size, W, W, "head.weight", tied_to="tok.weight")
+    # the order of layers is data: layer 1 (attention) runs a second time at the end with a cache of its own
+    order = [LayerStep(i, i) for i in range(cfg.layers)] + [LayerStep(1, cfg.layers)]
+    return ModelDef(cfg, emb, pos, blocks, order, NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix="fn"), head)
+
+
+def toy_plain(model_dir, cfg, ids):
+    _, w = plain_opt.load_model(model_dir)
+    rms = lambda x, g: x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-6) * g
+    x = w["tok.weight"][ids] + w["pos.weight"][np.arange(len(ids))]
+    for i in list(range(cfg.layers)) + [1]:
+        h = rms(x, w[f"l{i}.n1.weight"])
+        if i % 2 == 0:
+            s, rows = np.zeros(cfg.width), []
+            for t in range(len(ids)):
+                s = cfg.decay * s + (1 - cfg.decay) * h[t]
+                rows.append(s @ w[f"l{i}.avg.weight"].T)
+            a = np.stack(rows)
+        else:
+            q, k, v = (h @ w[f"l{i}.{n}.weight"].T for n in "qkv")
+            a = plain_opt.causal_attention(q, k, v, cfg.heads) @ w[f"l{i}.o.weight"].T
+        x = x + a
+        h = rms(x, w[f"l{i}.n2.weight"])
+        x = x + np.maximum(h @ w[f"l{i}.up.weight"].T, 0) @ w[f"l{i}.down.weight"].T
+    return rms(x, w["fn.weight"]) @ w["tok.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_runs_through_the_engine(tmp_path, dtype):
+    from swifttransformer_b200.engine.replay import TraceSession
+    cfg = ToyConfig(vocab_size=211, width=48, layers=3, heads=3, inner=100, decay=0.8, max_positions=96)
+    d = write_random_model(str(tmp_path / "toy"), cfg, seed=3, std=0.15)
+    model = load_model(d, dtype, DEV)
+    specs = model.definition.cache_specs()
+    assert isinstance(specs[0], StateSpec) and isinstance(specs[2], StateSpec) and len(specs) == 4
+    assert not model.graph_safe()
+    reqs = {"p": helpers.random_tokens(211, 70, 1), "q": helpers.random_tokens(211, 41, 2),
+            "r": helpers.random_tokens(211, 23, 3)}
+    refs = {k: toy_plain(d, cfg, np.array(v)) for k, v in reqs.items()}
+    for build in (helpers.trace_whole, helpers.trace_portions, lambda r: helpers.trace_mixed(r, max_live=2, chunk=9)):
+        steps = build(reqs)
+        s = TraceSession(d, dtype, helpers.live_token_need(steps), page_size=8, max_requests=2)
+        got = helpers.replay(s, steps)
+        for k in reqs:
+            scale = np.abs(refs[k]).max()
+            bad = helpers.first_bad(got[k], refs[k], helpers.TOL[dtype] * scale)
+            assert bad is None, (k, bad)
