@@ -80,53 +80,76 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     const size_t head_stride = (size_t)page_size * d;
     const size_t kv_stride = (size_t)nkv * head_stride;
 
-    // every lane of the block runs the same number of rounds (the shuffles need
-    // all 32 lanes); a group whose key lies past the end re-reads the last key
-    // and drops the result.
-    for (int key0 = k_lo; key0 < k_hi; key0 += DEC_GROUPS) {
-        const bool valid = key0 + g < k_hi;
-        const int key = valid ? key0 + g : k_hi - 1;
-        const int page = bt[key / page_size];
-        const bf16* krow = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
-                           + (size_t)(key % page_size) * d;
-        const bf16* vrow = krow + kv_stride;
-        bf16x8 kreg[NCHUNK], vreg[NCHUNK];
+    // Every lane of the block runs the same number of rounds (the shuffles need all 32 lanes).  In a
+    // round each 8-lane group takes KU keys and issues all of their loads before it uses any, so that
+    // several rows are in flight per lane; a key past the end re-reads the last key and is dropped.
+    constexpr int KU = NCHUNK <= 2 ? 4 : 2;
+    for (int key0 = k_lo; key0 < k_hi; key0 += DEC_GROUPS * KU) {
+        bool valid[KU];
+        const bf16* krow[KU];
 #pragma unroll
-        for (int c = 0; c < NCHUNK; ++c) {
-            const int dim0 = (c * 8 + l8) * 8;
-            if (dim0 < d) { kreg[c] = ldg16(krow + dim0); vreg[c] = ldg16(vrow + dim0); }
+        for (int u = 0; u < KU; ++u) {
+            const int kk = key0 + u * DEC_GROUPS + g;
+            valid[u] = kk < k_hi;
+            const int key = valid[u] ? kk : k_hi - 1;
+            const int page = bt[key / page_size];
+            krow[u] = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
+                      + (size_t)(key % page_size) * d;
         }
-        float s = 0.f;
+        bf16x8 kreg[KU][NCHUNK], vreg[KU][NCHUNK];
 #pragma unroll
-        for (int c = 0; c < NCHUNK; ++c) {
-            const int dim0 = (c * 8 + l8) * 8;
-            if (dim0 < d) {
+        for (int u = 0; u < KU; ++u)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(kreg[c].v[i]);
-                    s = fmaf(qf[c][2 * i], f.x, s);
-                    s = fmaf(qf[c][2 * i + 1], f.y, s);
+            for (int c = 0; c < NCHUNK; ++c) {
+                const int dim0 = (c * 8 + l8) * 8;
+                if (dim0 < d) { kreg[u][c] = ldg16(krow[u] + dim0); vreg[u][c] = ldg16(krow[u] + kv_stride + dim0); }
+            }
+        float s[KU];
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            float a = 0.f;
+#pragma unroll
+            for (int c = 0; c < NCHUNK; ++c) {
+                const int dim0 = (c * 8 + l8) * 8;
+                if (dim0 < d) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(kreg[u][c].v[i]);
+                        a = fmaf(qf[c][2 * i], f.x, a);
+                        a = fmaf(qf[c][2 * i + 1], f.y, a);
+                    }
                 }
             }
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            a += __shfl_xor_sync(0xffffffffu, a, 4);
+            s[u] = valid[u] ? a : -INFINITY;
         }
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (!valid) continue;
-        const float m_new = fmaxf(m, s);
-        const float corr = exp2f(m - m_new);   // m = -inf on the first key: exp2f(-inf) = 0
-        const float p = exp2f(s - m_new);
-        l = l * corr + p;
+        float m_new = m;
+#pragma unroll
+        for (int u = 0; u < KU; ++u) m_new = fmaxf(m_new, s[u]);
+        if (m_new == -INFINITY) continue;            // this group had no key in this round (nor before)
+        const float corr = exp2f(m - m_new);          // m = -inf before the first key: exp2f(-inf) = 0
+        float p[KU];
+        float psum = 0.f;
+#pragma unroll
+        for (int u = 0; u < KU; ++u) { p[u] = exp2f(s[u] - m_new); psum += p[u]; }
+        l = l * corr + psum;
         m = m_new;
 #pragma unroll
         for (int c = 0; c < NCHUNK; ++c) {
             const int dim0 = (c * 8 + l8) * 8;
             if (dim0 < d) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(vreg[c].v[i]);
-                    acc[c][2 * i] = fmaf(p, f.x, acc[c][2 * i] * corr);
-                    acc[c][2 * i + 1] = fmaf(p, f.y, acc[c][2 * i + 1] * corr);
+                for (int i = 0; i < 8; ++i) acc[c][i] *= corr;
+#pragma unroll
+                for (int u = 0; u < KU; ++u) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(vreg[u][c].v[i]);
+                        acc[c][2 * i] = fmaf(p[u], f.x, acc[c][2 * i]);
+                        acc[c][2 * i + 1] = fmaf(p[u], f.y, acc[c][2 * i + 1]);
+                    }
                 }
             }
         }

@@ -6,72 +6,73 @@
 // bias+activation src/csrc/kernel/fused_addbias_activ.cu:25-45, residual add
 // src/csrc/kernel/addbias.cu:22-37, last-row gather src/csrc/kernel/gather_last_tokens.cu:23-37.
 // Differences by design: sums, statistics and the residual stream are float for
-// every storage type; the variance is two-pass; any width is accepted.
+// every storage type; the variance is two-pass; any width is accepted (widths
+// that are a multiple of 4 take the vector path: four elements per access and
+// several independent loads in flight per thread, which is what makes the
+// kernels bandwidth- rather than latency-bound at decode batch sizes).
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-template <typename T, typename TO>
-__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, int width,
-                             const int* __restrict__ pos, const T* __restrict__ pos_table, int pos_offset,
-                             TO* __restrict__ out) {
+// VEC: width % 4 == 0.  src != nullptr: rows come from src[t] instead of table[ids[t]].
+template <typename T, typename TO, bool VEC>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ src,
+                             int width, const int* __restrict__ pos, const T* __restrict__ pos_table,
+                             int pos_offset, TO* __restrict__ out) {
     const int t = blockIdx.x;
-    const T* row = table + (size_t)ids[t] * width;
+    const T* row = src ? src + (size_t)t * width : table + (size_t)ids[t] * width;
     const T* prow = pos_table ? pos_table + (size_t)(pos[t] + pos_offset) * width : nullptr;
     TO* o = out + (size_t)t * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
-        float v = to_f32(row[e]);
-        if (prow) v += to_f32(prow[e]);
-        o[e] = from_f32<TO>(v);
+    if (VEC) {
+        for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+            float4 v = load4(row + e);
+            if (prow) v = add4(v, load4(prow + e));
+            store4(o + e, v);
+        }
+    } else {
+        for (int e = threadIdx.x; e < width; e += blockDim.x) {
+            float v = to_f32(row[e]);
+            if (prow) v += to_f32(prow[e]);
+            o[e] = from_f32<TO>(v);
+        }
     }
 }
 
-// out[t,:] = in[t,:] + pos_table[pos[t]+offset,:]   (used after a project_in product)
 template <typename T, typename TO>
-__global__ void add_positions_kernel(const T* __restrict__ in, int width, const int* __restrict__ pos,
-                                     const T* __restrict__ pos_table, int pos_offset, TO* __restrict__ out) {
-    const int t = blockIdx.x;
-    const T* prow = pos_table + (size_t)(pos[t] + pos_offset) * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x)
-        out[(size_t)t * width + e] = from_f32<TO>(to_f32(in[(size_t)t * width + e]) + to_f32(prow[e]));
+static int launch_embed(const int* ids, const void* table, const void* src, int n_tokens, int width, const int* pos,
+                        const void* pos_table, int pos_offset, void* out, cudaStream_t s) {
+    const bool vec = width % 4 == 0 && aligned16(table) && aligned16(src) && aligned16(pos_table) && aligned16(out);
+    int block = vec ? (width / 4 + 31) / 32 * 32 : 256;
+    if (block > 512) block = 512;
+    if (block < 32) block = 32;
+    if (vec)
+        embed_kernel<T, TO, true><<<n_tokens, block, 0, s>>>(ids, (const T*)table, (const T*)src, width, pos,
+                                                              (const T*)pos_table, pos_offset, (TO*)out);
+    else
+        embed_kernel<T, TO, false><<<n_tokens, block, 0, s>>>(ids, (const T*)table, (const T*)src, width, pos,
+                                                               (const T*)pos_table, pos_offset, (TO*)out);
+    return st_launch_status();
 }
 
-// out_dtype: 0 float, 1 same as dtype
+// out[t] = table[ids[t]] (+ pos_table[pos[t] + pos_offset]);  out is float when out_f32, else the table's type
 ST_EXPORT int st_embed(const int* ids, const void* table, int n_tokens, int width, const int* pos,
                        const void* pos_table, int pos_offset, void* out, int dtype, int out_f32, void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = width >= 1024 ? 256 : 128;
-    if (dtype == 0) {
-        embed_kernel<float, float><<<n_tokens, block, 0, s>>>(ids, (const float*)table, width, pos,
-                                                               (const float*)pos_table, pos_offset, (float*)out);
-    } else if (dtype == 1) {
-        if (out_f32)
-            embed_kernel<bf16, float><<<n_tokens, block, 0, s>>>(ids, (const bf16*)table, width, pos,
-                                                                  (const bf16*)pos_table, pos_offset, (float*)out);
-        else
-            embed_kernel<bf16, bf16><<<n_tokens, block, 0, s>>>(ids, (const bf16*)table, width, pos,
-                                                                 (const bf16*)pos_table, pos_offset, (bf16*)out);
-    } else return ST_ERR_BAD_DTYPE;
-    return st_launch_status();
+    if (dtype == 0) return launch_embed<float, float>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s);
+    if (dtype != 1) return ST_ERR_BAD_DTYPE;
+    if (out_f32) return launch_embed<bf16, float>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s);
+    return launch_embed<bf16, bf16>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s);
 }
 
+// out[t] = in[t] + pos_table[pos[t] + pos_offset]   (used after a project_in product)
 ST_EXPORT int st_add_positions(const void* in, int n_tokens, int width, const int* pos, const void* pos_table,
                                int pos_offset, void* out, int dtype, int out_f32, void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = width >= 1024 ? 256 : 128;
-    if (dtype == 0)
-        add_positions_kernel<float, float><<<n_tokens, block, 0, s>>>((const float*)in, width, pos,
-                                                                       (const float*)pos_table, pos_offset, (float*)out);
-    else if (dtype == 1) {
-        if (out_f32)
-            add_positions_kernel<bf16, float><<<n_tokens, block, 0, s>>>((const bf16*)in, width, pos,
-                                                                          (const bf16*)pos_table, pos_offset, (float*)out);
-        else
-            add_positions_kernel<bf16, bf16><<<n_tokens, block, 0, s>>>((const bf16*)in, width, pos,
-                                                                         (const bf16*)pos_table, pos_offset, (bf16*)out);
-    } else return ST_ERR_BAD_DTYPE;
-    return st_launch_status();
+    if (dtype == 0) return launch_embed<float, float>(nullptr, nullptr, in, n_tokens, width, pos, pos_table, pos_offset, out, s);
+    if (dtype != 1) return ST_ERR_BAD_DTYPE;
+    if (out_f32) return launch_embed<bf16, float>(nullptr, nullptr, in, n_tokens, width, pos, pos_table, pos_offset, out, s);
+    return launch_embed<bf16, bf16>(nullptr, nullptr, in, n_tokens, width, pos, pos_table, pos_offset, out, s);
 }
 
 // ------------------------------------------------------- residual add + norm
@@ -83,27 +84,52 @@ ST_EXPORT int st_add_positions(const void* in, int n_tokens, int width, const in
 //       kind 2: s                                                    (no norm)
 //   out_act[r] = T(y)  (optional), out_f32[r] = y  (optional; may alias x when rows is null)
 // The row is staged in shared memory as float; all statistics are float.
-template <typename T>
-__global__ void add_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+template <typename T, bool VEC>
+__global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
                                 const T* __restrict__ delta, const float* __restrict__ delta_bias,
                                 float* resid_out, const float* __restrict__ gamma,
                                 const float* __restrict__ beta, float eps, int kind, int width,
                                 T* __restrict__ out_act, float* out_f32) {
-    extern __shared__ float srow[];
+    extern __shared__ __align__(16) float srow[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t i = rows ? (size_t)rows[r] : (size_t)r;
     const float* xr = x + i * width;
     float sum = 0.f;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
-        float v = xr[e];
-        if (delta) v += to_f32(delta[i * width + e]);
-        if (delta_bias) v += delta_bias[e];
-        srow[e] = v;
-        sum += v;
-    }
-    if (resid_out) {
-        for (int e = threadIdx.x; e < width; e += blockDim.x) resid_out[i * width + e] = srow[e];
+    if (VEC) {
+        const int nvec = width >> 2;
+        for (int v0 = threadIdx.x; v0 < nvec; v0 += blockDim.x * 2) {   // two independent sets of loads in flight
+            const int v1 = v0 + blockDim.x;
+            const bool two = v1 < nvec;
+            float4 a = load4(xr + v0 * 4), b = two ? load4(xr + v1 * 4) : make_float4(0, 0, 0, 0);
+            if (delta) {
+                a = add4(a, load4(delta + i * width + v0 * 4));
+                if (two) b = add4(b, load4(delta + i * width + v1 * 4));
+            }
+            if (delta_bias) {
+                a = add4(a, load4(delta_bias + v0 * 4));
+                if (two) b = add4(b, load4(delta_bias + v1 * 4));
+            }
+            store4(srow + v0 * 4, a);
+            sum += (a.x + a.y) + (a.z + a.w);
+            if (two) {
+                store4(srow + v1 * 4, b);
+                sum += (b.x + b.y) + (b.z + b.w);
+            }
+            if (resid_out) {
+                store4(resid_out + i * width + v0 * 4, a);
+                if (two) store4(resid_out + i * width + v1 * 4, b);
+            }
+        }
+    } else {
+        for (int e = threadIdx.x; e < width; e += blockDim.x) {
+            float v = xr[e];
+            if (delta) v += to_f32(delta[i * width + e]);
+            if (delta_bias) v += delta_bias[e];
+            srow[e] = v;
+            sum += v;
+            if (resid_out) resid_out[i * width + e] = v;
+        }
     }
     float mean = 0.f, rstd = 1.f;
     if (kind == 0) {
@@ -116,21 +142,58 @@ __global__ void add_norm_kernel(const float* __restrict__ x, const int* __restri
         const float var = block_sum(sq, scratch) / (float)width;
         rstd = 1.0f / sqrtf(var + eps);
     } else if (kind == 1) {
+        __syncthreads();
         float sq = 0.f;
         for (int e = threadIdx.x; e < width; e += blockDim.x) sq += srow[e] * srow[e];
         const float ms = block_sum(sq, scratch) / (float)width;
         rstd = 1.0f / sqrtf(ms + eps);
+    } else {
+        __syncthreads();
     }
-    for (int e = threadIdx.x; e < width; e += blockDim.x) {
-        float y = srow[e];
-        if (kind != 2) {
-            y = (y - mean) * rstd;
-            if (gamma) y *= gamma[e];
-            if (beta) y += beta[e];
+    if (VEC) {
+        for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+            float4 y = load4(srow + e);
+            if (kind != 2) {
+                y = make_float4((y.x - mean) * rstd, (y.y - mean) * rstd, (y.z - mean) * rstd, (y.w - mean) * rstd);
+                if (gamma) { const float4 g = load4(gamma + e); y = make_float4(y.x * g.x, y.y * g.y, y.z * g.z, y.w * g.w); }
+                if (beta) y = add4(y, load4(beta + e));
+            }
+            if (out_act) store4(out_act + (size_t)r * width + e, y);
+            if (out_f32) store4(out_f32 + (size_t)r * width + e, y);
         }
-        if (out_act) out_act[(size_t)r * width + e] = from_f32<T>(y);
-        if (out_f32) out_f32[(size_t)r * width + e] = y;
+    } else {
+        for (int e = threadIdx.x; e < width; e += blockDim.x) {
+            float y = srow[e];
+            if (kind != 2) {
+                y = (y - mean) * rstd;
+                if (gamma) y *= gamma[e];
+                if (beta) y += beta[e];
+            }
+            if (out_act) out_act[(size_t)r * width + e] = from_f32<T>(y);
+            if (out_f32) out_f32[(size_t)r * width + e] = y;
+        }
     }
+}
+
+template <typename T>
+static int launch_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias,
+                           float* resid_out, const float* gamma, const float* beta, float eps, int kind, int n_rows,
+                           int width, void* out_act, float* out_f32, cudaStream_t s) {
+    const size_t smem = (size_t)width * sizeof(float);
+    const bool vec = width % 4 == 0 && aligned16(x) && aligned16(delta) && aligned16(delta_bias) &&
+                     aligned16(resid_out) && aligned16(gamma) && aligned16(beta) && aligned16(out_act) &&
+                     aligned16(out_f32);
+    int block = vec ? (width / 8 + 31) / 32 * 32 : 256;   // vector path: two vectors per thread and round
+    if (block > 512) block = 512;
+    if (block < 64) block = 64;
+    auto kern = vec ? add_norm_kernel<T, true> : add_norm_kernel<T, false>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<n_rows, block, smem, s>>>(x, rows, (const T*)delta, delta_bias, resid_out, gamma, beta, eps, kind, width,
+                                     (T*)out_act, out_f32);
+    return st_launch_status();
 }
 
 ST_EXPORT int st_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias,
@@ -138,45 +201,52 @@ ST_EXPORT int st_add_norm(const float* x, const int* rows, const void* delta, co
                           int n_rows, int width, void* out_act, float* out_f32, int dtype, void* stream) {
     if (n_rows <= 0) return 0;
     if (kind < 0 || kind > 2 || width <= 0) return ST_ERR_BAD_ARG;
+    if ((size_t)width * sizeof(float) > 200 * 1024) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)width * sizeof(float);
-    if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;
-    int block = 128;
-    if (width >= 2048) block = 256;
-    if (width >= 8192) block = 512;
-    if (dtype == 0) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_norm_kernel<float><<<n_rows, block, smem, s>>>(x, rows, (const float*)delta, delta_bias, resid_out,
-                                                           gamma, beta, eps, kind, width, (float*)out_act, out_f32);
-    } else if (dtype == 1) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_norm_kernel<bf16><<<n_rows, block, smem, s>>>(x, rows, (const bf16*)delta, delta_bias, resid_out,
-                                                          gamma, beta, eps, kind, width, (bf16*)out_act, out_f32);
-    } else return ST_ERR_BAD_DTYPE;
-    return st_launch_status();
+    if (dtype == 0)
+        return launch_add_norm<float>(x, rows, delta, delta_bias, resid_out, gamma, beta, eps, kind, n_rows, width,
+                                      out_act, out_f32, s);
+    if (dtype == 1)
+        return launch_add_norm<bf16>(x, rows, delta, delta_bias, resid_out, gamma, beta, eps, kind, n_rows, width,
+                                     out_act, out_f32, s);
+    return ST_ERR_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------ bias + activation
-template <typename T>
+template <typename T, bool VEC>
 __global__ void bias_act_kernel(T* __restrict__ y, const float* __restrict__ bias, int act, size_t total, int width) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        float v = to_f32(y[i]);
-        if (bias) v += bias[i % width];
-        y[i] = from_f32<T>(apply_act(v, act));
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    if (VEC) {
+        const size_t nvec = total >> 2;
+        for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+            float4 a = load4(y + v * 4);
+            if (bias) a = add4(a, load4(bias + (v * 4) % width));
+            store4(y + v * 4, make_float4(apply_act(a.x, act), apply_act(a.y, act), apply_act(a.z, act), apply_act(a.w, act)));
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+            float v = to_f32(y[i]);
+            if (bias) v += bias[i % width];
+            y[i] = from_f32<T>(apply_act(v, act));
+        }
     }
 }
 
 ST_EXPORT int st_bias_act(void* y, const float* bias, int act, int n_rows, int width, int dtype, void* stream) {
     if (n_rows <= 0) return 0;
     const size_t total = (size_t)n_rows * width;
-    int grid = (int)((total + 255) / 256);
-    if (grid > 148 * 16) grid = 148 * 16;
+    const bool vec = width % 4 == 0 && aligned16(y) && aligned16(bias);
+    const size_t work = vec ? total / 4 : total;
+    int grid = (int)((work + 255) / 256);
+    if (grid > 148 * 8) grid = 148 * 8;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == 0) bias_act_kernel<float><<<grid, 256, 0, s>>>((float*)y, bias, act, total, width);
-    else if (dtype == 1) bias_act_kernel<bf16><<<grid, 256, 0, s>>>((bf16*)y, bias, act, total, width);
-    else return ST_ERR_BAD_DTYPE;
+    if (dtype == 0) {
+        if (vec) bias_act_kernel<float, true><<<grid, 256, 0, s>>>((float*)y, bias, act, total, width);
+        else bias_act_kernel<float, false><<<grid, 256, 0, s>>>((float*)y, bias, act, total, width);
+    } else if (dtype == 1) {
+        if (vec) bias_act_kernel<bf16, true><<<grid, 256, 0, s>>>((bf16*)y, bias, act, total, width);
+        else bias_act_kernel<bf16, false><<<grid, 256, 0, s>>>((bf16*)y, bias, act, total, width);
+    } else return ST_ERR_BAD_DTYPE;
     return st_launch_status();
 }
 

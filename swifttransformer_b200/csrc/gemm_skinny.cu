@@ -1,0 +1,177 @@
+// Matrix product for a handful of tokens (decode steps), bfloat16:
+//   out[m, n] = act( sum_k x[m,k] * w[n,k] + bias[n] ),   m < M <= 32,  w stored [out, in]
+// At these sizes the product is weight streaming: every byte of w is read once
+// and the arithmetic is free, so the kernel is built around the loads.
+//
+// Operands are swapped for the tensor cores: 16 rows of w are the M side of an
+// m16n8k16 product and 8 tokens its N side.  A thread loads its fragments
+// straight from global memory, 16 contiguous bytes at a time: within a block of
+// 32 k the lane with (group g, thread-in-group t) takes k = 8t..8t+7 of row g and
+// row g+8 of w and of token g of x, and feeds elements (0,1 | 2,3) and (4,5 | 6,7)
+// to two consecutive products.  The product sums over k, so any assignment of k
+// to fragment slots is right as long as w and x use the same one.  No shared
+// memory staging, no barriers in the main loop; each of the block's 8 warps
+// takes every 8th k-block (four blocks in flight) and the partial sums meet in
+// shared memory.  One thread block per 16 output features.
+//
+// Epilogues: bias and activation; float or bfloat16 output; or the fused
+// q|k|v form: q (+bias) to a dense buffer, k and v (+bias) straight into the
+// paged cache at each token's position (what st_qkv_to_cache does after a
+// library product).
+//
+// The reference calls cuBLAS for these products at every batch size
+// (src/csrc/layer/attention.cc:102-111,255-264, src/csrc/layer/ffn.cc:71-105,
+// src/csrc/model/gpt/gpt.cc:192-201) and adds bias / activation / cache
+// writes in separate kernels.
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_THREADS (SK_WARPS * 32)
+#define SK_UNROLL 4
+
+struct QkvTarget {
+    bf16* q_out;               // [M, qw]
+    bf16* pool;                // paged cache
+    const int* positions;      // [M]
+    const int* seq_of_token;   // [M]
+    const int* slots;          // [sequences]
+    const int* block_table;    // [slots, max_pages]
+    int* status;
+    int max_pages, num_pages, n_layers, layer, nkv, d, page_size, qw, write_kv;
+};
+
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read once, do not keep in L1
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+template <int NT, bool QKV>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
+                   void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt) {
+    __shared__ float red[SK_WARPS][16][8 * NT + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * 16;
+    const bf16* wa = w + (size_t)min(row0 + g, N - 1) * K + t * 8;
+    const bf16* wb = w + (size_t)min(row0 + g + 8, N - 1) * K + t * 8;
+    const bf16* xr[NT];
+    bool xok[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        xok[j] = j * 8 + g < M;
+        xr[j] = x + (size_t)(xok[j] ? j * 8 + g : 0) * K + t * 8;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    const int nkb = (K + 31) >> 5;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int kb0 = warp; kb0 < nkb; kb0 += SK_WARPS * SK_UNROLL) {
+        uint4 ua[SK_UNROLL], ub[SK_UNROLL], xb[SK_UNROLL][NT];
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+            const int k = (kb0 + u * SK_WARPS) * 32;
+            const bool ok = k + t * 8 < K;      // K % 8 == 0: a 16-byte piece is inside or outside as a whole
+            ua[u] = ok ? ldg_stream(wa + k) : zero;
+            ub[u] = ok ? ldg_stream(wb + k) : zero;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                xb[u][j] = (ok && xok[j]) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                mma16816(acc[j], ua[u].x, ub[u].x, ua[u].y, ub[u].y, xb[u][j].x, xb[u][j].y);
+                mma16816(acc[j], ua[u].z, ub[u].z, ua[u].w, ub[u].w, xb[u][j].z, xb[u][j].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        red[warp][g][j * 8 + 2 * t] = acc[j][0];
+        red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+        red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+        red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * 8 * NT; i += SK_THREADS) {
+        const int r = i & 15, m = i >> 4;
+        const int n = row0 + r;
+        if (m >= M || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < SK_WARPS; ++wi) v += red[wi][r][m];
+        if (bias) v += bias[n];
+        if (!QKV) {
+            v = apply_act(v, act);
+            if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
+            else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
+        } else {
+            if (n < tgt.qw) {
+                tgt.q_out[(size_t)m * tgt.qw + n] = __float2bfloat16_rn(v);
+            } else if (tgt.write_kv) {
+                const int pos = tgt.positions[m];
+                if (pos < 0) continue;                      // padding token of a fixed-shape step
+                const int page = tgt.block_table[(size_t)tgt.slots[tgt.seq_of_token[m]] * tgt.max_pages + pos / tgt.page_size];
+                if (page < 0 || page >= tgt.num_pages) { atomicExch(tgt.status, 1); continue; }
+                const int kw = tgt.nkv * tgt.d;
+                const int rr = n - tgt.qw;
+                const int kv = rr / kw, rem = rr - kv * kw;
+                const int head = rem / tgt.d, dim = rem - head * tgt.d;
+                tgt.pool[(((((size_t)page * tgt.n_layers + tgt.layer) * 2 + kv) * tgt.nkv + head) * tgt.page_size
+                          + pos % tgt.page_size) * tgt.d + dim] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+ST_EXPORT int st_gemm_skinny_max_rows() { return 32; }
+
+template <bool QKV>
+static int launch_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, int act,
+                         int out_f32, const QkvTarget& tgt, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 32) return ST_ERR_TOO_LARGE;
+    if (K <= 0 || K % 8) return ST_ERR_BAD_SIZE;
+    if (!aligned16(x) || !aligned16(w)) return ST_ERR_BAD_ARG;
+    const int grid = (N + 15) / 16;
+    if (M <= 8)
+        gemm_skinny_kernel<1, QKV><<<grid, SK_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
+    else if (M <= 16)
+        gemm_skinny_kernel<2, QKV><<<grid, SK_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
+    else
+        gemm_skinny_kernel<4, QKV><<<grid, SK_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
+    return st_launch_status();
+}
+
+ST_EXPORT int st_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                             int act, int out_f32, void* stream) {
+    QkvTarget none = {};
+    return launch_skinny<false>(x, w, bias, out, M, N, K, act, out_f32, none, (cudaStream_t)stream);
+}
+
+// x [M,K] . w [(nh + 2 nkv) d, K]^T + bias -> q_out [M, nh d] and the paged cache
+ST_EXPORT int st_gemm_skinny_qkv(const void* x, const void* w, const float* bias, void* q_out, void* pool,
+                                 const int* positions, const int* seq_of_token, const int* slots,
+                                 const int* block_table, int max_pages, int num_pages, int n_layers, int layer,
+                                 int M, int K, int nh, int nkv, int d, int page_size, int write_kv, int* status,
+                                 void* stream) {
+    if (nh <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || layer < 0 || layer >= n_layers) return ST_ERR_BAD_ARG;
+    QkvTarget tgt;
+    tgt.q_out = (bf16*)q_out; tgt.pool = (bf16*)pool; tgt.positions = positions; tgt.seq_of_token = seq_of_token;
+    tgt.slots = slots; tgt.block_table = block_table; tgt.status = status; tgt.max_pages = max_pages;
+    tgt.num_pages = num_pages; tgt.n_layers = n_layers; tgt.layer = layer; tgt.nkv = nkv; tgt.d = d;
+    tgt.page_size = page_size; tgt.qw = nh * d; tgt.write_kv = write_kv;
+    return launch_skinny<true>(x, w, bias, nullptr, M, (nh + 2 * nkv) * d, K, 0, 0, tgt, (cudaStream_t)stream);
+}

@@ -13,7 +13,8 @@
 // here one kernel serves every kind of token.
 #include "common.cuh"
 
-template <typename T>
+// VEC: head_dim % 4 == 0, four elements per access
+template <typename T, bool VEC>
 __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
                                     T* __restrict__ q_out, T* __restrict__ pool,
                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -23,29 +24,58 @@ __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __re
     const int t = blockIdx.x;
     const int qw = nh * d, kw = nkv * d;
     const T* row = qkv + (size_t)t * (qw + 2 * kw);
-    for (int e = threadIdx.x; e < qw; e += blockDim.x) {
-        float v = to_f32(row[e]);
-        if (bias) v += bias[e];
-        q_out[(size_t)t * qw + e] = from_f32<T>(v);
-    }
-    if (!write_kv) return;
     const int pos = positions[t];
-    if (pos < 0) return;   // padding token of a fixed-shape step
-    const int slot = slots[seq_of_token[t]];
-    const int page = block_table[(size_t)slot * max_pages + pos / page_size];
-    if (page < 0 || page >= num_pages) {   // a hole in the block table: record it, write nothing
-        if (threadIdx.x == 0) atomicExch(status, 1);
-        return;
+    int page = -1, off = 0;
+    if (write_kv && pos >= 0) {   // pos < 0: padding token of a fixed-shape step, nothing is cached
+        page = block_table[(size_t)slots[seq_of_token[t]] * max_pages + pos / page_size];
+        off = pos % page_size;
+        if (page < 0 || page >= num_pages) {   // a hole in the block table: record it, write nothing
+            if (threadIdx.x == 0) atomicExch(status, 1);
+            page = -1;
+        }
     }
-    const int off = pos % page_size;
-    for (int e = threadIdx.x; e < 2 * kw; e += blockDim.x) {
-        const int kv = e / kw, rem = e - kv * kw;
-        const int head = rem / d, dim = rem - head * d;
-        float v = to_f32(row[qw + e]);
-        if (bias) v += bias[qw + e];
-        const size_t idx = (((((size_t)page * n_layers + layer) * 2 + kv) * nkv + head) * page_size + off) * d + dim;
-        pool[idx] = from_f32<T>(v);
+    constexpr int W = VEC ? 4 : 1;
+    const int total = (page >= 0 ? qw + 2 * kw : qw) / W;
+    for (int v = threadIdx.x; v < total; v += blockDim.x) {
+        const int e = v * W;
+        T* dst;
+        if (e < qw) {
+            dst = q_out + (size_t)t * qw + e;
+        } else {
+            const int r = e - qw;
+            const int kv = r / kw, rem = r - kv * kw;
+            const int head = rem / d, dim = rem - head * d;
+            dst = pool + (((((size_t)page * n_layers + layer) * 2 + kv) * nkv + head) * page_size + off) * d + dim;
+        }
+        if (VEC) {
+            float4 a = load4(row + e);
+            if (bias) a = add4(a, load4(bias + e));
+            store4(dst, a);
+        } else {
+            float a = to_f32(row[e]);
+            if (bias) a += bias[e];
+            *dst = from_f32<T>(a);
+        }
     }
+}
+
+template <typename T>
+static int launch_qkv_to_cache(const void* qkv, const float* bias, void* q_out, void* pool, const int* positions,
+                               const int* seq_of_token, const int* slots, const int* block_table, int max_pages,
+                               int num_pages, int n_layers, int layer, int n_tokens, int nh, int nkv, int d,
+                               int page_size, int write_kv, int* status, cudaStream_t s) {
+    const bool vec = d % 4 == 0 && aligned16(qkv) && aligned16(bias) && aligned16(q_out) && aligned16(pool);
+    const int work = (nh + 2 * nkv) * d / (vec ? 4 : 1);
+    int block = (work + 31) / 32 * 32;
+    if (block > 512) block = 512;
+    if (block < 64) block = 64;
+    if (vec)
+        qkv_to_cache_kernel<T, true><<<n_tokens, block, 0, s>>>((const T*)qkv, bias, (T*)q_out, (T*)pool, positions,
+            seq_of_token, slots, block_table, max_pages, num_pages, n_layers, layer, nh, nkv, d, page_size, write_kv, status);
+    else
+        qkv_to_cache_kernel<T, false><<<n_tokens, block, 0, s>>>((const T*)qkv, bias, (T*)q_out, (T*)pool, positions,
+            seq_of_token, slots, block_table, max_pages, num_pages, n_layers, layer, nh, nkv, d, page_size, write_kv, status);
+    return st_launch_status();
 }
 
 ST_EXPORT int st_qkv_to_cache(const void* qkv, const float* bias, void* q_out, void* pool, const int* positions,
@@ -55,15 +85,11 @@ ST_EXPORT int st_qkv_to_cache(const void* qkv, const float* bias, void* q_out, v
     if (n_tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || layer < 0 || layer >= n_layers) return ST_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int block = 256;
     if (dtype == 0)
-        qkv_to_cache_kernel<float><<<n_tokens, block, 0, s>>>((const float*)qkv, bias, (float*)q_out, (float*)pool,
-            positions, seq_of_token, slots, block_table, max_pages, num_pages, n_layers, layer, nh, nkv, d,
-            page_size, write_kv, status);
-    else if (dtype == 1)
-        qkv_to_cache_kernel<bf16><<<n_tokens, block, 0, s>>>((const bf16*)qkv, bias, (bf16*)q_out, (bf16*)pool,
-            positions, seq_of_token, slots, block_table, max_pages, num_pages, n_layers, layer, nh, nkv, d,
-            page_size, write_kv, status);
-    else return ST_ERR_BAD_DTYPE;
-    return st_launch_status();
+        return launch_qkv_to_cache<float>(qkv, bias, q_out, pool, positions, seq_of_token, slots, block_table,
+            max_pages, num_pages, n_layers, layer, n_tokens, nh, nkv, d, page_size, write_kv, status, s);
+    if (dtype == 1)
+        return launch_qkv_to_cache<bf16>(qkv, bias, q_out, pool, positions, seq_of_token, slots, block_table,
+            max_pages, num_pages, n_layers, layer, n_tokens, nh, nkv, d, page_size, write_kv, status, s);
+    return ST_ERR_BAD_DTYPE;
 }

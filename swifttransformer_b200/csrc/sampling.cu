@@ -9,9 +9,9 @@
 //   request's tokens do not depend on what else is in the batch.
 #include "common.cuh"
 
-#define SAMPLE_THREADS 256
+#define SAMPLE_THREADS 1024
 
-// lowest index among the largest values
+// lowest index among the largest values; rows whose length is a multiple of 4 are read four at a time
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
     __shared__ float sv[SAMPLE_THREADS / 32];
@@ -19,9 +19,27 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
     const float* row = logits + (size_t)blockIdx.x * vocab;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best || (v == best && i < best_i) || best_i == 0x7fffffff) { best = v; best_i = i; }
+    if ((vocab & 3) == 0) {
+        const int nvec = vocab >> 2;
+        for (int v0 = threadIdx.x; v0 < nvec; v0 += 2 * SAMPLE_THREADS) {
+            const int v1 = v0 + SAMPLE_THREADS;
+            const float4 a = load4(row + 4 * v0);
+            const float4 b = v1 < nvec ? load4(row + 4 * v1) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (av[k] > best || best_i == 0x7fffffff) { best = av[k]; best_i = 4 * v0 + k; }
+            if (v1 < nvec) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (bv[k] > best) { best = bv[k]; best_i = 4 * v1 + k; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best || best_i == 0x7fffffff) { best = v; best_i = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -171,11 +171,48 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         raise KernelError("this engine runs on a CUDA device only; got a CPU tensor")
     if n == 0:
         return torch.empty((0, m), dtype=out_dtype, device=a.device)
+    if n <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0:
+        return gemm_skinny(a, w, bias, act, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(a, w.t(), out_dtype=torch.float32)
     else:
         y = torch.mm(a, w.t())
     return bias_act(y, bias, act)
+
+
+SKINNY_MAX_ROWS = 32    # up to this many tokens the weight-streaming kernel serves bfloat16 products
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(a @ w.T + bias) for at most SKINNY_MAX_ROWS rows of bfloat16 ``a``; w is [out, in] with in % 8 == 0."""
+    out_dtype = out_dtype or a.dtype
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny is a bfloat16 kernel")
+    a = a.contiguous()
+    assert w.is_contiguous()
+    n, k = a.shape
+    m = w.shape[0]
+    out = torch.empty((n, m), dtype=out_dtype, device=a.device)
+    _check(lib().st_gemm_skinny(_p(a), _p(w), _p(bias), _p(out), n, m, k, ACT_CODES[act],
+                                int(out_dtype == torch.float32), _stream()), "gemm_skinny")
+    return out
+
+
+def qkv_linear_to_cache(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                        pool: torch.Tensor, layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                        slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, d: int,
+                        status: torch.Tensor, write_kv: bool = True) -> None:
+    """The fused form of ``linear`` + ``qkv_to_cache`` for at most SKINNY_MAX_ROWS bfloat16 tokens:
+    q_out = (h @ w.T + bias)[:, :nh*d]; the k and v parts go straight into the paged cache."""
+    if h.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+        raise KernelError("qkv_linear_to_cache is a bfloat16 kernel")
+    num_pages, n_layers, _, pnkv, page_size, pd = pool.shape
+    assert pnkv == nkv and pd == d and w.shape[0] == (nh + 2 * nkv) * d and h.is_contiguous() and w.is_contiguous()
+    _check(lib().st_gemm_skinny_qkv(_p(h), _p(w), _p(bias), _p(q_out), _p(pool), _p(positions), _p(seq_of_token),
+                                    _p(slots), _p(block_table), block_table.shape[1], num_pages, n_layers, layer,
+                                    h.shape[0], h.shape[1], nh, nkv, d, page_size, int(write_kv), _p(status),
+                                    _stream()), "qkv_linear_to_cache")
 
 
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",

@@ -91,10 +91,17 @@ class Attention(Mixer):
         return PagedKVSpec(self.nkv, self.d, self.window)
 
     def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:
-        qkv = ops.linear(h, self.w_qkv)
         q = torch.empty((h.shape[0], self.nh * self.d), dtype=h.dtype, device=h.device)
-        ops.qkv_to_cache(qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token, ctx.slots,
-                         cache.block_table, self.nh, self.nkv, self.d, ctx.status, write_kv=cache.writable)
+        if h.dtype == torch.bfloat16 and h.shape[0] <= ops.SKINNY_MAX_ROWS and self.hidden % 8 == 0:
+            # a few tokens: one weight-streaming kernel does the product, the bias and the cache write
+            ops.qkv_linear_to_cache(h, self.w_qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions,
+                                    ctx.seq_of_token, ctx.slots, cache.block_table, self.nh, self.nkv, self.d,
+                                    ctx.status, write_kv=cache.writable)
+        else:
+            qkv = ops.linear(h, self.w_qkv)
+            ops.qkv_to_cache(qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token,
+                             ctx.slots, cache.block_table, self.nh, self.nkv, self.d, ctx.status,
+                             write_kv=cache.writable)
         o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
         return Delta(ops.linear(o, self.w_o), self.b_o)
 

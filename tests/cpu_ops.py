@@ -86,6 +86,15 @@ def linear(a, w, bias=None, act="none", out_dtype=None):
 
 
 gemm_plain = linear
+gemm_skinny = linear
+SKINNY_MAX_ROWS = 32
+
+
+def qkv_linear_to_cache(h, w, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d,
+                        status, write_kv=True):
+    qkv = linear(h, w)
+    qkv_to_cache(qkv, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d, status,
+                 write_kv)
 
 
 def qkv_to_cache(qkv, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d,
@@ -216,7 +225,8 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
     return res
 
 
-ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "linear", "gemm_plain", "qkv_to_cache",
+ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "linear", "gemm_plain", "gemm_skinny",
+       "qkv_linear_to_cache", "qkv_to_cache",
        "attention_plain", "attention_decode_scratch", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]
 

@@ -71,8 +71,13 @@ def test_seeded_sampling_is_reproducible_and_batch_independent(model_dirs):
     assert alone == together, "a request's tokens do not depend on what else is scheduled or how it is cut"
     assert len({tuple(o) for o in together}) > 1
     # preemption by recompute leaves the tokens unchanged
-    tight = engine(model_dirs[name], name, "float32", num_pages=12, chunk_size=32)
-    assert tight.generate(prompts, params) == together and tight.scheduler.num_preemptions > 0
+    # three requests whose prompts fill the pool: when they grow, the youngest is preempted and recomputed
+    prompts3 = [helpers.random_tokens(1000, 62, 450 + i) for i in range(3)]
+    roomy = engine(model_dirs[name], name, "float32", max_batch_tokens=256, chunk_size=64)
+    tight = engine(model_dirs[name], name, "float32", num_pages=12, max_batch_tokens=256, chunk_size=64)
+    want = roomy.generate(prompts3, params[:3])
+    assert tight.generate(prompts3, params[:3]) == want
+    assert tight.scheduler.num_preemptions > 0 and roomy.scheduler.num_preemptions == 0
 
 
 def test_run_gpt_command_line(model_dirs, tmp_path):

@@ -306,3 +306,46 @@ def test_sampling_distribution():
 def test_cpu_tensors_are_refused():
     with pytest.raises(ops.KernelError):
         ops.bias_act(torch.zeros(2, 2), torch.zeros(2), "relu")
+
+
+@pytest.mark.parametrize("shape", [(1, 50, 24), (3, 2048, 2048), (8, 777, 520), (9, 130, 8192), (16, 96, 72),
+                                   (17, 1000, 264), (32, 6144, 2048)])
+def test_gemm_skinny(shape):
+    n, m, k = shape
+    dtype = torch.bfloat16
+    a, w, b = rnd((n, k), dtype, 80), rnd((m, k), dtype, 81, 0.1), rnd((m,), torch.float32, 82)
+    for act in ("none", "relu", "gelu"):
+        got = ops.gemm_skinny(a.to(DEV), w.to(DEV), b.to(DEV), act, torch.float32)
+        close(got, cpu_ops.linear(a, w, b, act, torch.float32), torch.float32, f"gemm_skinny {act}", rel=2e-5)
+    got = ops.gemm_skinny(a.to(DEV), w.to(DEV))
+    close(got, cpu_ops.linear(a, w), dtype, "gemm_skinny bf16 out", rel=8e-3)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny(rnd((33, k), dtype, 83).to(DEV), w.to(DEV))
+    # a row's result does not depend on the other rows in the batch
+    one = ops.gemm_skinny(a[n - 1:n].to(DEV).contiguous(), w.to(DEV), b.to(DEV), "none", torch.float32)
+    full = ops.gemm_skinny(a.to(DEV), w.to(DEV), b.to(DEV), "none", torch.float32)
+    assert torch.equal(one[0], full[n - 1])
+
+
+@pytest.mark.parametrize("n", [1, 8, 13, 32])
+def test_qkv_linear_to_cache(n):
+    dtype = torch.bfloat16
+    nh, nkv, d, ps, L, K = 6, 2, 24, 8, 3, 136
+    lens = [40 + i for i in range(n)]
+    pool, bt, slots = make_cache(dtype, n, lens, nkv, d, ps, L, 90)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    pos[n // 2] = -1 if n > 1 else pos[0]                      # one padding token
+    seq = torch.arange(n, dtype=torch.int32)
+    h, w = rnd((n, K), dtype, 91), rnd(((nh + 2 * nkv) * d, K), dtype, 92, 0.2)
+    bias = rnd(((nh + 2 * nkv) * d,), torch.float32, 93)
+    ref_pool, ref_q, st = pool.clone(), torch.zeros(n, nh * d, dtype=dtype), torch.zeros(1, dtype=torch.int32)
+    cpu_ops.qkv_linear_to_cache(h, w, bias, ref_q, ref_pool, 2, pos, seq, slots, bt, nh, nkv, d, st)
+    gp, gq = pool.to(DEV), torch.zeros(n, nh * d, dtype=dtype, device=DEV)
+    gst = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.qkv_linear_to_cache(h.to(DEV), w.to(DEV), bias.to(DEV), gq, gp, 2, pos.to(DEV), seq.to(DEV), slots.to(DEV),
+                            bt.to(DEV), nh, nkv, d, gst)
+    assert int(gst.item()) == 0
+    close(gq, ref_q, dtype, "q", rel=1e-2)
+    close(gp, ref_pool, dtype, "pool", rel=1e-2)
+    changed = (gp.cpu() != pool).any(dim=-1).sum().item()
+    assert changed <= 2 * nkv * n, "only the new tokens' rows of layer 2 may change"
