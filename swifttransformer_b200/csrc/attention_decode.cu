@@ -36,8 +36,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                         const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                         int n_layers, int layer, int nh, int nkv, int d, int page_size, float scale_log2,
-                        int window, int n_splits) {
+                        int window, int n_splits, int* __restrict__ counters) {
     __shared__ float s_m[DEC_GROUPS], s_l[DEC_GROUPS];
+    __shared__ int s_last;
     extern __shared__ float s_acc[];   // [DEC_GROUPS][d]
     const int t = items ? items[blockIdx.x] : blockIdx.x;
     const int h = blockIdx.y, split = blockIdx.z;
@@ -81,29 +82,29 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     const size_t kv_stride = (size_t)nkv * head_stride;
 
     // Every lane of the block runs the same number of rounds (the shuffles need all 32 lanes).  In a
-    // round each 8-lane group takes KU keys and issues all of their loads before it uses any, so that
-    // several rows are in flight per lane; a key past the end re-reads the last key and is dropped.
-    constexpr int KU = NCHUNK <= 2 ? 4 : 2;
-    for (int key0 = k_lo; key0 < k_hi; key0 += DEC_GROUPS * KU) {
-        bool valid[KU];
-        const bf16* krow[KU];
+    // round each 8-lane group takes KU keys; the loads of the next round are issued before the
+    // current one is used (two register buffers), so that rows are in flight all the time.  A key
+    // past the end re-reads the last key and is dropped.
+    constexpr int KU = NCHUNK == 1 ? 4 : (NCHUNK == 2 ? 2 : 1);
+    constexpr int STEP = DEC_GROUPS * KU;
+    struct Round { bf16x8 k[KU][NCHUNK], v[KU][NCHUNK]; bool valid[KU]; };
+    auto issue = [&](Round& r, int key0) {
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
             const int kk = key0 + u * DEC_GROUPS + g;
-            valid[u] = kk < k_hi;
-            const int key = valid[u] ? kk : k_hi - 1;
+            r.valid[u] = kk < k_hi;
+            const int key = r.valid[u] ? kk : k_hi - 1;
             const int page = bt[key / page_size];
-            krow[u] = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
-                      + (size_t)(key % page_size) * d;
-        }
-        bf16x8 kreg[KU][NCHUNK], vreg[KU][NCHUNK];
-#pragma unroll
-        for (int u = 0; u < KU; ++u)
+            const bf16* krow = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
+                               + (size_t)(key % page_size) * d;
 #pragma unroll
             for (int c = 0; c < NCHUNK; ++c) {
                 const int dim0 = (c * 8 + l8) * 8;
-                if (dim0 < d) { kreg[u][c] = ldg16(krow[u] + dim0); vreg[u][c] = ldg16(krow[u] + kv_stride + dim0); }
+                if (dim0 < d) { r.k[u][c] = ldg16(krow + dim0); r.v[u][c] = ldg16(krow + kv_stride + dim0); }
             }
+        }
+    };
+    auto consume = [&](const Round& r) {
         float s[KU];
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
@@ -114,7 +115,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
                 if (dim0 < d) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(kreg[u][c].v[i]);
+                        const float2 f = __bfloat1622float2(r.k[u][c].v[i]);
                         a = fmaf(qf[c][2 * i], f.x, a);
                         a = fmaf(qf[c][2 * i + 1], f.y, a);
                     }
@@ -123,12 +124,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
             a += __shfl_xor_sync(0xffffffffu, a, 1);
             a += __shfl_xor_sync(0xffffffffu, a, 2);
             a += __shfl_xor_sync(0xffffffffu, a, 4);
-            s[u] = valid[u] ? a : -INFINITY;
+            s[u] = r.valid[u] ? a : -INFINITY;
         }
         float m_new = m;
 #pragma unroll
         for (int u = 0; u < KU; ++u) m_new = fmaxf(m_new, s[u]);
-        if (m_new == -INFINITY) continue;            // this group had no key in this round (nor before)
+        if (m_new == -INFINITY) return;               // this group has had no key so far
         const float corr = exp2f(m - m_new);          // m = -inf before the first key: exp2f(-inf) = 0
         float p[KU];
         float psum = 0.f;
@@ -146,12 +147,23 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
                 for (int u = 0; u < KU; ++u) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(vreg[u][c].v[i]);
+                        const float2 f = __bfloat1622float2(r.v[u][c].v[i]);
                         acc[c][2 * i] = fmaf(p[u], f.x, acc[c][2 * i]);
                         acc[c][2 * i + 1] = fmaf(p[u], f.y, acc[c][2 * i + 1]);
                     }
                 }
             }
+        }
+    };
+    if (k_lo < k_hi) {
+        Round ra, rb;
+        issue(ra, k_lo);
+        for (int key0 = k_lo; key0 < k_hi; key0 += 2 * STEP) {
+            const bool more_b = key0 + STEP < k_hi;           // uniform over the block
+            if (more_b) issue(rb, key0 + STEP);
+            consume(ra);
+            if (key0 + 2 * STEP < k_hi) issue(ra, key0 + 2 * STEP);
+            if (more_b) consume(rb);
         }
     }
     if (l8 == 0) { s_m[g] = m; s_l[g] = l; }
@@ -180,6 +192,35 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
         else part[2 + e] = a;
     }
     if (n_splits > 1 && threadIdx.x == 0) { part[0] = mm; part[1] = ll; }
+    if (n_splits == 1 || !counters) return;
+    // The split that arrives last at this (token, head) merges all of them (in split order, so the
+    // result does not depend on which one that was) and resets the counter for the next launch.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* c = counters + (size_t)blockIdx.x * nh + h;
+        s_last = atomicAdd(c, 1) == n_splits - 1;
+        if (s_last) *c = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* all = partial + ((size_t)blockIdx.x * nh + h) * n_splits * (d + 2);
+    float gm = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) gm = fmaxf(gm, __ldcg(all + (size_t)sp * (d + 2)));
+    float gl = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+        const float ms = __ldcg(all + (size_t)sp * (d + 2));
+        gl += (ms == -INFINITY) ? 0.f : __ldcg(all + (size_t)sp * (d + 2) + 1) * exp2f(ms - gm);
+    }
+    for (int e = threadIdx.x; e < d; e += DEC_THREADS) {
+        float a = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float ms = __ldcg(all + (size_t)sp * (d + 2));
+            a += (ms == -INFINITY) ? 0.f : __ldcg(all + (size_t)sp * (d + 2) + 2 + e) * exp2f(ms - gm);
+        }
+        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / gl);
+    }
 }
 
 // merge the splits of every (item, head)
@@ -212,10 +253,13 @@ ST_EXPORT long long st_attention_decode_scratch_floats(int n_items, int nh, int 
     return n_splits > 1 ? (long long)n_items * nh * n_splits * (d + 2) : 0;
 }
 
+// counters: n_items * nh ints, zero before the first launch (the kernel leaves them zero), or null: the
+// splits are then merged by a second kernel.
 ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, float* partial, const int* items,
                                   int n_items, const int* positions, const int* seq_of_token, const int* slots,
                                   const int* block_table, int max_pages, int n_layers, int layer, int nh, int nkv,
-                                  int d, int page_size, float scale, int window, int n_splits, void* stream) {
+                                  int d, int page_size, float scale, int window, int n_splits, int* counters,
+                                  void* stream) {
     if (n_items <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
     if (d % 8 || d <= 0) return ST_ERR_BAD_SIZE;
@@ -228,7 +272,7 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
 #define LAUNCH_DEC(NC)                                                                                         \
     attention_decode_kernel<NC><<<grid, DEC_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,  \
         n_splits > 1 ? partial : nullptr, items, positions, seq_of_token, slots, block_table, max_pages,        \
-        n_layers, layer, nh, nkv, d, page_size, sl2, window, n_splits)
+        n_layers, layer, nh, nkv, d, page_size, sl2, window, n_splits, counters)
     if (d <= 64) LAUNCH_DEC(1);
     else if (d <= 128) LAUNCH_DEC(2);
     else if (d <= 192) LAUNCH_DEC(3);
@@ -236,7 +280,7 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
 #undef LAUNCH_DEC
     int rc = st_launch_status();
     if (rc) return rc;
-    if (n_splits > 1) {
+    if (n_splits > 1 && !counters) {
         dim3 g2(n_items, nh);
         attention_combine_kernel<<<g2, 64, 0, s>>>(partial, (bf16*)out, items, positions, nh, d, n_splits);
         rc = st_launch_status();

@@ -1,6 +1,6 @@
 // Paged, chunked causal attention for portions of prompts, bfloat16 storage.
 //
-// One thread block per (tile of 64 consecutive query tokens of one request,
+// One thread block per (tile of 128 consecutive query tokens of one request,
 // head).  The queries at positions start_pos + off .. attend every key of the
 // request up to their own position (or inside their window), so a portion
 // that begins in the middle of a prompt reads the earlier portions' keys from
@@ -18,9 +18,9 @@
 // cache has no counterpart there.
 #include "common.cuh"
 
-#define PF_BM 64
-#define PF_BN 64
-#define PF_THREADS 128
+#define PF_BM 128            // query rows per thread block (16 per warp)
+#define PF_BN 64             // keys per tile
+#define PF_THREADS 256
 #define LOG2E 1.4426950408889634f
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -49,6 +49,11 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: 2 ulp, exp2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // element (row, 16-byte chunk c) of a tile whose rows hold DMAX bf16: chunks are
@@ -88,27 +93,33 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
     const size_t head_stride = (size_t)page_size * d;
     const size_t kv_stride = (size_t)nkv * head_stride;
 
+    // four threads share a key row of a tile: one page lookup per thread and tile
+    constexpr int KV_TPR = PF_THREADS / PF_BN;
+    const int kv_r = threadIdx.x / KV_TPR, kv_c0 = threadIdx.x % KV_TPR;
     auto load_kv = [&](int kt, int buf) {
         bf16* dk = sK + buf * PF_BN * DMAX;
         bf16* dv = sV + buf * PF_BN * DMAX;
-        for (int idx = threadIdx.x; idx < PF_BN * chunks; idx += PF_THREADS) {
-            const int r = idx / chunks, c = idx - r * chunks;
-            const int key = kt * PF_BN + r;
-            const bool ok = key >= key_lo && key < kv_hi;   // outside: never read (its page may be gone)
-            const int page = ok ? bt[key / page_size] : 0;
-            const bf16* src = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
-                              + (size_t)(ok ? key % page_size : 0) * d + c * 8;
-            cp_async16(tile_ptr<DMAX>(dk, r, c), ok ? src : pool, ok);
-            cp_async16(tile_ptr<DMAX>(dv, r, c), ok ? src + kv_stride : pool, ok);
+        const int key = kt * PF_BN + kv_r;
+        const bool ok = key >= key_lo && key < kv_hi;   // outside: never read (its page may be gone)
+        const bf16* src = pool;
+        if (ok) {
+            const int page = bt[key / page_size];
+            src = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
+                  + (size_t)(key % page_size) * d;
+        }
+        for (int c = kv_c0; c < chunks; c += KV_TPR) {
+            cp_async16(tile_ptr<DMAX>(dk, kv_r, c), ok ? src + c * 8 : pool, ok);
+            cp_async16(tile_ptr<DMAX>(dv, kv_r, c), ok ? src + kv_stride + c * 8 : pool, ok);
         }
     };
 
     // queries of the tile (rows past the portion's end are zero)
-    for (int idx = threadIdx.x; idx < PF_BM * chunks; idx += PF_THREADS) {
-        const int r = idx / chunks, c = idx - r * chunks;
+    {
+        constexpr int Q_TPR = PF_THREADS / PF_BM;
+        const int r = threadIdx.x / Q_TPR;
         const bool ok = r < n_rows;
-        const bf16* src = q + ((size_t)(tok0 + (ok ? r : 0)) * nh + h) * d + c * 8;
-        cp_async16(tile_ptr<DMAX>(sQ, r, c), src, ok);
+        const bf16* src = q + ((size_t)(tok0 + (ok ? r : 0)) * nh + h) * d;
+        for (int c = threadIdx.x % Q_TPR; c < chunks; c += Q_TPR) cp_async16(tile_ptr<DMAX>(sQ, r, c), src + c * 8, ok);
     }
     load_kv(kt_begin, 0);
     cp_async_commit();
@@ -116,12 +127,18 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
     float o_acc[DMAX / 8][4];
 #pragma unroll
     for (int i = 0; i < DMAX / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    // running maximum in the scaled (log2) domain, running sum
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     // this thread's two rows of the warp's 16 and their positions (-1: no query in that row)
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
     const int pos_a = row_a < n_rows ? pos0 + row_a : -1;
     const int pos_b = row_b < n_rows ? pos0 + row_b : -1;
     const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+    // the warp's rows: a tile whose keys all lie at or before the first row's position (and inside
+    // every row's window) needs no mask
+    const int warp_pos_first = pos0 + warp * 16;
+    const bool warp_full = warp * 16 + 16 <= n_rows;
+    const bool warp_idle = warp * 16 >= n_rows;
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
@@ -131,91 +148,101 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
         __syncthreads();
         const bf16* tK = sK + buf * PF_BN * DMAX;
         const bf16* tV = sV + buf * PF_BN * DMAX;
-
-        // S = Q K^T for the warp's 16 rows x 64 keys
-        float s_acc[PF_BN / 8][4];
+        // a warp whose rows all lie before this tile's first key (causal) has nothing to do in it
+        const bool skip = warp_idle || kt * PF_BN > warp_pos_first + 15;
+        if (!skip) {
+            // S = Q K^T for the warp's 16 rows x 64 keys
+            float s_acc[PF_BN / 8][4];
 #pragma unroll
-        for (int i = 0; i < PF_BN / 8; ++i) { s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f; }
+            for (int i = 0; i < PF_BN / 8; ++i) { s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f; }
 #pragma unroll
-        for (int kk = 0; kk < DMAX / 16; ++kk) {
-            if (kk * 16 < d) {
-                uint32_t a[4];
-                ldmatrix_x4(a[0], a[1], a[2], a[3],
-                            tile_ptr<DMAX>(sQ, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
+            for (int kk = 0; kk < DMAX / 16; ++kk) {
+                if (kk * 16 < d) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a[0], a[1], a[2], a[3],
+                                tile_ptr<DMAX>(sQ, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
 #pragma unroll
-                for (int np = 0; np < PF_BN / 16; ++np) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4(b0, b1, b2, b3,
-                                tile_ptr<DMAX>(const_cast<bf16*>(tK), np * 16 + (lane & 7) + (lane >> 4) * 8,
-                                               2 * kk + ((lane >> 3) & 1)));
-                    mma_bf16(s_acc[2 * np], a, b0, b1);
-                    mma_bf16(s_acc[2 * np + 1], a, b2, b3);
+                    for (int np = 0; np < PF_BN / 16; ++np) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(b0, b1, b2, b3,
+                                    tile_ptr<DMAX>(const_cast<bf16*>(tK), np * 16 + (lane & 7) + (lane >> 4) * 8,
+                                                   2 * kk + ((lane >> 3) & 1)));
+                        mma_bf16(s_acc[2 * np], a, b0, b1);
+                        mma_bf16(s_acc[2 * np + 1], a, b2, b3);
+                    }
                 }
             }
-        }
-        // scale, mask, online softmax
-        float mx[2] = {-INFINITY, -INFINITY};
+            // mask (only on tiles that touch the diagonal, a window's edge or a ragged last warp)
+            const bool need_mask = !warp_full || kt * PF_BN + PF_BN - 1 > warp_pos_first ||
+                                   (window > 0 && kt * PF_BN < warp_pos_first + 15 - window + 1);
+            if (need_mask) {
 #pragma unroll
-        for (int nt = 0; nt < PF_BN / 8; ++nt) {
-            const int key = kt * PF_BN + nt * 8 + (lane & 3) * 2;
+                for (int nt = 0; nt < PF_BN / 8; ++nt) {
+                    const int key = kt * PF_BN + nt * 8 + (lane & 3) * 2;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int k2 = key + e;
-                float va = s_acc[nt][e] * scale_log2, vb = s_acc[nt][2 + e] * scale_log2;
-                if (k2 > pos_a || k2 < lo_a) va = -INFINITY;
-                if (k2 > pos_b || k2 < lo_b) vb = -INFINITY;
-                s_acc[nt][e] = va; s_acc[nt][2 + e] = vb;
-                mx[0] = fmaxf(mx[0], va); mx[1] = fmaxf(mx[1], vb);
+                    for (int e = 0; e < 2; ++e) {
+                        const int k2 = key + e;
+                        if (k2 > pos_a || k2 < lo_a) s_acc[nt][e] = -INFINITY;
+                        if (k2 > pos_b || k2 < lo_b) s_acc[nt][2 + e] = -INFINITY;
+                    }
+                }
             }
-        }
-        float corr[2], m_use[2];
+            float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;          // a row with no key yet
-            corr[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_use[r]);
-            m_run[r] = m_new;
-        }
-        float rs[2] = {0.f, 0.f};
-#pragma unroll
-        for (int nt = 0; nt < PF_BN / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float pa = exp2f(s_acc[nt][e] - m_use[0]), pb = exp2f(s_acc[nt][2 + e] - m_use[1]);
-                s_acc[nt][e] = pa; s_acc[nt][2 + e] = pb;
-                rs[0] += pa; rs[1] += pb;
+            for (int nt = 0; nt < PF_BN / 8; ++nt) {
+                mx[0] = fmaxf(mx[0], fmaxf(s_acc[nt][0], s_acc[nt][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s_acc[nt][2], s_acc[nt][3]));
             }
-        }
+            float corr[2], m_use[2];
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
-            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
-            l_run[r] = l_run[r] * corr[r] + rs[r];
-        }
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r] * scale_log2);   // scale > 0: max commutes with it
+                m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;            // a row with no key yet
+                corr[r] = fast_exp2(m_run[r] - m_use[r]);                 // m_run = -inf: 0
+                m_run[r] = m_new;
+            }
+            float rs[2] = {0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < DMAX / 8; ++i) {
-            o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0];
-            o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1];
-        }
-        // O += P V
+            for (int nt = 0; nt < PF_BN / 8; ++nt) {
 #pragma unroll
-        for (int j = 0; j < PF_BN / 16; ++j) {
-            uint32_t a[4];
-            a[0] = pack_bf16(s_acc[2 * j][0], s_acc[2 * j][1]);
-            a[1] = pack_bf16(s_acc[2 * j][2], s_acc[2 * j][3]);
-            a[2] = pack_bf16(s_acc[2 * j + 1][0], s_acc[2 * j + 1][1]);
-            a[3] = pack_bf16(s_acc[2 * j + 1][2], s_acc[2 * j + 1][3]);
+                for (int e = 0; e < 2; ++e) {
+                    const float pa = fast_exp2(fmaf(s_acc[nt][e], scale_log2, -m_use[0]));
+                    const float pb = fast_exp2(fmaf(s_acc[nt][2 + e], scale_log2, -m_use[1]));
+                    s_acc[nt][e] = pa; s_acc[nt][2 + e] = pb;
+                    rs[0] += pa; rs[1] += pb;
+                }
+            }
 #pragma unroll
-            for (int np = 0; np < DMAX / 16; ++np) {
-                if (np * 16 < d) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4_trans(b0, b1, b2, b3,
-                                      tile_ptr<DMAX>(const_cast<bf16*>(tV), j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                                     2 * np + (lane >> 4)));
-                    mma_bf16(o_acc[2 * np], a, b0, b1);
-                    mma_bf16(o_acc[2 * np + 1], a, b2, b3);
+            for (int r = 0; r < 2; ++r) {
+                rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+                rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+                l_run[r] = l_run[r] * corr[r] + rs[r];
+            }
+#pragma unroll
+            for (int i = 0; i < DMAX / 8; ++i) {
+                o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0];
+                o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1];
+            }
+            // O += P V
+#pragma unroll
+            for (int j = 0; j < PF_BN / 16; ++j) {
+                uint32_t a[4];
+                a[0] = pack_bf16(s_acc[2 * j][0], s_acc[2 * j][1]);
+                a[1] = pack_bf16(s_acc[2 * j][2], s_acc[2 * j][3]);
+                a[2] = pack_bf16(s_acc[2 * j + 1][0], s_acc[2 * j + 1][1]);
+                a[3] = pack_bf16(s_acc[2 * j + 1][2], s_acc[2 * j + 1][3]);
+#pragma unroll
+                for (int np = 0; np < DMAX / 16; ++np) {
+                    if (np * 16 < d) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4_trans(b0, b1, b2, b3,
+                                          tile_ptr<DMAX>(const_cast<bf16*>(tV), j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                         2 * np + (lane >> 4)));
+                        mma_bf16(o_acc[2 * np], a, b0, b1);
+                        mma_bf16(o_acc[2 * np + 1], a, b2, b3);
+                    }
                 }
             }
         }

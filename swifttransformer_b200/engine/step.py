@@ -203,7 +203,7 @@ class ModelRunner:
         self.max_batch_tokens = max_batch_tokens
         self.use_cuda_graphs = use_cuda_graphs and self.device.type == "cuda" and model.graph_safe()
         self.max_seqs = cache.max_seqs
-        self.tile_rows = 64
+        self.tile_rows = ops.attention_prefill_tile_rows()   # query rows one attention tile covers
         self._upd_cap = self.max_seqs * cache.max_pages_per_seq + 16
         words = self._layout(max_batch_tokens, self.max_seqs, max_batch_tokens)["total"]
         self._staging = _Staging(words, self.device)

@@ -42,6 +42,7 @@ def lib() -> ctypes.CDLL:
         except OSError as e:
             raise KernelError(f"cannot load {path}: {e}") from None
         _LIB.st_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        _LIB.st_gemm_skinny_scratch_floats.restype = ctypes.c_longlong
         _LIB.st_uniform_host.restype = ctypes.c_float
         _LIB.st_uniform_host.argtypes = [ctypes.c_longlong, ctypes.c_longlong]
     return _LIB
@@ -181,6 +182,21 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
 
 SKINNY_MAX_ROWS = 32    # up to this many tokens the weight-streaming kernel serves bfloat16 products
+_SKINNY_TILES = 600     # feature tiles (of 16) the k-slicing scratch is sized for; wider products are not sliced
+_skinny_buffers = {}
+
+
+def _skinny_scratch(device: torch.device):
+    """Per-device scratch of the skinny product's k-slices: partial sums and per-tile arrival counters.
+    Allocated once at first use (which must not be inside a graph recording) and kept for good; launches
+    on one stream use it one after the other."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _skinny_buffers:
+        n = int(lib().st_gemm_skinny_scratch_floats(_SKINNY_TILES * 16))
+        _skinny_buffers[key] = (torch.empty(n, dtype=torch.float32, device=device),
+                                torch.zeros(_SKINNY_TILES, dtype=torch.int32, device=device))
+    return _skinny_buffers[key]
+
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
@@ -194,8 +210,10 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     n, k = a.shape
     m = w.shape[0]
     out = torch.empty((n, m), dtype=out_dtype, device=a.device)
+    scratch, counters = _skinny_scratch(a.device)
     _check(lib().st_gemm_skinny(_p(a), _p(w), _p(bias), _p(out), n, m, k, ACT_CODES[act],
-                                int(out_dtype == torch.float32), _stream()), "gemm_skinny")
+                                int(out_dtype == torch.float32), _p(scratch), _p(counters), _SKINNY_TILES,
+                                _stream()), "gemm_skinny")
     return out
 
 
@@ -209,10 +227,11 @@ def qkv_linear_to_cache(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.T
         raise KernelError("qkv_linear_to_cache is a bfloat16 kernel")
     num_pages, n_layers, _, pnkv, page_size, pd = pool.shape
     assert pnkv == nkv and pd == d and w.shape[0] == (nh + 2 * nkv) * d and h.is_contiguous() and w.is_contiguous()
+    scratch, counters = _skinny_scratch(h.device)
     _check(lib().st_gemm_skinny_qkv(_p(h), _p(w), _p(bias), _p(q_out), _p(pool), _p(positions), _p(seq_of_token),
                                     _p(slots), _p(block_table), block_table.shape[1], num_pages, n_layers, layer,
                                     h.shape[0], h.shape[1], nh, nkv, d, page_size, int(write_kv), _p(status),
-                                    _stream()), "qkv_linear_to_cache")
+                                    _p(scratch), _p(counters), _SKINNY_TILES, _stream()), "qkv_linear_to_cache")
 
 
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
@@ -259,6 +278,18 @@ def attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.
     return out
 
 
+_DECODE_COUNTERS = 1 << 16
+_decode_counter_buffers = {}
+
+
+def _decode_counters(device: torch.device) -> torch.Tensor:
+    """Per-device arrival counters of the split decode attention (zero between launches)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _decode_counter_buffers:
+        _decode_counter_buffers[key] = torch.zeros(_DECODE_COUNTERS, dtype=torch.int32, device=device)
+    return _decode_counter_buffers[key]
+
+
 def attention_decode_scratch(n_items: int, nh: int, d: int, n_splits: int) -> int:
     return int(lib().st_attention_decode_scratch_floats(n_items, nh, d, n_splits))
 
@@ -267,7 +298,7 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                      items: Optional[torch.Tensor], n_items: int, positions: torch.Tensor,
                      seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
                      scale: float, window: int = 0, n_splits: int = 1,
-                     partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     partial: Optional[torch.Tensor] = None, fused_merge: bool = True) -> torch.Tensor:
     """bfloat16 paged attention for single query tokens; ``items`` lists the token indices it serves
     (None: tokens 0..n_items-1).  A token whose position is negative is skipped."""
     _, n_layers, _, nkv, page_size, d = pool.shape
@@ -277,10 +308,12 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
         need = attention_decode_scratch(n_items, nh, d, n_splits)
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
             raise KernelError(f"attention_decode: needs {need} floats of scratch for {n_splits} splits")
+    counters = _decode_counters(q.device) if (n_splits > 1 and fused_merge
+                                              and n_items * nh <= _DECODE_COUNTERS) else None
     _check(lib().st_attention_decode(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items, _p(positions),
                                      _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
                                      n_layers, layer, nh, nkv, d, page_size, _f(scale), window, n_splits,
-                                     _stream()), "attention_decode")
+                                     _p(counters), _stream()), "attention_decode")
     return out
 
 

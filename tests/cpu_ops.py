@@ -158,8 +158,11 @@ def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_toke
     return out
 
 
+TILE_ROWS = 128
+
+
 def attention_prefill_tile_rows():
-    return 64
+    return TILE_ROWS
 
 
 def attention_prefill(q, pool, layer, out, tiles, n_tiles, q_start, start_pos, slots, block_table, nh, scale,
@@ -170,7 +173,7 @@ def attention_prefill(q, pool, layer, out, tiles, n_tiles, q_start, start_pos, s
     for i in range(n_tiles):
         seq, off = int(tiles[2 * i]), int(tiles[2 * i + 1])
         a = int(q_start[seq]) + off
-        b = min(a + 64, int(q_start[seq + 1]))
+        b = min(a + TILE_ROWS, int(q_start[seq + 1]))
         pos[a:b] = torch.arange(int(start_pos[seq]) + off, int(start_pos[seq]) + off + (b - a), dtype=torch.int32)
         seq_of[a:b] = seq
     tmp = torch.zeros_like(out)

@@ -220,13 +220,13 @@ def test_attention_decode(shape, window, n_splits):
 def test_attention_prefill(shape, window):
     nh, nkv, d, ps = shape
     dtype = torch.bfloat16
-    lens, new = [150, 200, 300, 64, 17], [150, 70, 16, 64, 17]
+    lens, new = [150, 200, 300, 64, 17, 400], [150, 70, 16, 64, 17, 300]
     pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 50, window)
     tiles = []
     for i, m in enumerate(new):
         if i == 2:
             continue                                   # request 2 is left to "another kernel"
-        tiles += [(i, off) for off in range(0, m, 64)]
+        tiles += [(i, off) for off in range(0, m, ops.attention_prefill_tile_rows())]
     tiles_t = torch.tensor(tiles, dtype=torch.int32).flatten()
     out = torch.full_like(ref, 7.0, device=DEV)
     ops.attention_prefill(q.to(DEV), pool.to(DEV), 1, out, tiles_t.to(DEV), len(tiles), t["q_start"].to(DEV),

@@ -97,9 +97,10 @@ class OneStep:
         self.slots = torch.tensor([slot], **i32)
         self.status = torch.zeros(1, **i32)
         from swifttransformer_b200.engine.step import AttentionPlan
-        tiles = torch.tensor([v for off in range(0, n, 64) for v in (0, off)], **i32)
-        self._plan = AttentionPlan(torch.arange(n, **i32), n if n < 16 else 0, tiles, 0 if n < 16 else (n + 63) // 64,
-                                   start + n)
+        tr = ops.attention_prefill_tile_rows()
+        tiles = torch.tensor([v for off in range(0, n, tr) for v in (0, off)] or [0], **i32)
+        self._plan = AttentionPlan(torch.arange(n, **i32), n if n < 16 else 0, tiles,
+                                   0 if n < 16 else (n + tr - 1) // tr, start + n)
         self._buf = None
 
     def attention_plan(self):
@@ -111,7 +112,7 @@ class OneStep:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n", [7, 90])
+@pytest.mark.parametrize("n", [7, 90, 128])
 def test_attention_part(dtype, n):
     H, nh = 96, 3
     d = H // nh
@@ -128,7 +129,7 @@ def test_attention_part(dtype, n):
     for k in "qkvo":
         t[f"a.{k}.weight"], t[f"a.{k}.bias"] = dev(ws[k], dtype), dev(bs[k])
     mixer.bind(t)
-    cache = CacheManager([mixer.cache_spec()], dtype, DEV, page_size=8, num_pages=16, max_seqs=2, max_seq_len=128)
+    cache = CacheManager([mixer.cache_spec()], dtype, DEV, page_size=8, num_pages=20, max_seqs=2, max_seq_len=160)
     slot = cache.alloc_slot()
     assert cache.reserve(slot, 0, n)
     for idx, val in cache.groups[0].take_updates():
