@@ -21,6 +21,7 @@ entries at position -1, which every kernel skips.
 from __future__ import annotations
 
 import dataclasses
+import gc
 from typing import Any, Dict, List, Optional, Sequence
 
 import numpy as np
@@ -180,8 +181,18 @@ class _DecodeGraph:
         self._frozen = True
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, pool=r._graph_pool):
-            self.logits = r.model.forward(self.ctx, r._entries)
+        # Nothing may destroy a CUDA object while the stream records: collect dead objects (an
+        # engine that went out of scope owns graphs of its own) now, and keep the collector off
+        # until the recording has ended.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g, pool=r._graph_pool):
+                self.logits = r.model.forward(self.ctx, r._entries)
+        finally:
+            if gc_was_on:
+                gc.enable()
         self.kernels = ops.launch_count() - before
         self.graph = g
 
