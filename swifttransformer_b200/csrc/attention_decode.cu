@@ -287,3 +287,75 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     }
     return rc;
 }
+
+// ---------------------------------------------------------------------------
+// The same operation for callers that cannot allocate: scratch inside the
+// library.  See attention_decode_noalloc.h for who needs this and the rules.
+// ---------------------------------------------------------------------------
+#include <stdio.h>
+#include "attention_decode_noalloc.h"
+
+// counters first (as ints), then the partial results
+static __device__ __align__(256) float st_noalloc_scratch[ST_NOALLOC_MAX_PAIRS + ST_NOALLOC_SCRATCH_FLOATS];
+
+#define ST_NOALLOC_MAX_DEVICES 64
+// In host code the array's name is only a handle for the runtime, not an address a kernel can use:
+// the device address is asked for once per device and kept here.
+static float* st_noalloc_device_ptr[ST_NOALLOC_MAX_DEVICES];
+
+static void noalloc_say(char* err, int err_len, const char* fmt, long long a, long long b) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, fmt, a, b);
+}
+
+ST_EXPORT int st_attention_decode_noalloc(const void* q, const void* pool, void* out, const int* items, int n_items,
+                                          const int* positions, const int* seq_of_token, const int* slots,
+                                          const int* block_table, int max_pages, int n_layers, int layer, int nh,
+                                          int nkv, int d, int page_size, float scale, int window, int n_splits,
+                                          void* stream, char* err, int err_len) {
+    if (err && err_len > 0) err[0] = 0;
+    if (n_items <= 0) return 0;
+    if (nh <= 0 || d <= 0 || n_splits < 1) {
+        noalloc_say(err, err_len, "invalid sizes: %lld heads, %lld splits", nh, n_splits);
+        return ST_ERR_BAD_ARG;
+    }
+    const long long pairs = (long long)n_items * nh;
+    const long long floats = n_splits > 1 ? pairs * n_splits * (d + 2) : 0;
+    if (pairs > ST_NOALLOC_MAX_PAIRS) {
+        noalloc_say(err, err_len, "%lld (token, head) pairs exceed the built-in scratch's limit of %lld",
+                    pairs, (long long)ST_NOALLOC_MAX_PAIRS);
+        return ST_ERR_TOO_LARGE;
+    }
+    if (floats > ST_NOALLOC_SCRATCH_FLOATS) {
+        noalloc_say(err, err_len, "the call needs %lld floats of scratch; the built-in scratch holds %lld",
+                    floats, (long long)ST_NOALLOC_SCRATCH_FLOATS);
+        return ST_ERR_TOO_LARGE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= ST_NOALLOC_MAX_DEVICES) {
+        noalloc_say(err, err_len, "device index %lld is beyond the %lld devices this entry point keeps track of",
+                    dev, (long long)ST_NOALLOC_MAX_DEVICES);
+        return ST_ERR_BAD_ARG;
+    }
+    if (!st_noalloc_device_ptr[dev]) {   // first call on this device: set-up (not inside a stream capture)
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, st_noalloc_scratch);
+        if (e != cudaSuccess) {
+            noalloc_say(err, err_len, "cudaGetSymbolAddress failed with error %lld on device %lld", (long long)e, dev);
+            return (int)e;
+        }
+        st_noalloc_device_ptr[dev] = p;
+    }
+    float* base = st_noalloc_device_ptr[dev];
+    int* counters = reinterpret_cast<int*>(base);
+    float* partial = base + ST_NOALLOC_MAX_PAIRS;
+    if (n_splits > 1) {
+        // the array keeps whatever the last call left: the counters must start at zero
+        e = cudaMemsetAsync(counters, 0, (size_t)pairs * sizeof(int), (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return st_attention_decode(q, pool, out, partial, items, n_items, positions, seq_of_token, slots, block_table,
+                               max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window, n_splits,
+                               n_splits > 1 ? counters : nullptr, stream);
+}
