@@ -23,9 +23,12 @@
 
 struct __align__(16) bf16x8 { __nv_bfloat162 v[4]; };
 
+// 16-byte load that is served by L2, not by the per-SM caches: the newest key/value row and the
+// queries were written by the kernel just before this one, which may still have been running when
+// this block became resident (programmatic dependent launch).
 __device__ __forceinline__ bf16x8 ldg16(const bf16* p) {
     bf16x8 r;
-    *reinterpret_cast<uint4*>(&r) = __ldg(reinterpret_cast<const uint4*>(p));
+    *reinterpret_cast<uint4*>(&r) = __ldcg(reinterpret_cast<const uint4*>(p));
     return r;
 }
 
@@ -40,6 +43,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     __shared__ float s_m[DEC_GROUPS], s_l[DEC_GROUPS];
     __shared__ int s_last;
     extern __shared__ float s_acc[];   // [DEC_GROUPS][d]
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
     const int t = items ? items[blockIdx.x] : blockIdx.x;
     const int h = blockIdx.y, split = blockIdx.z;
     const int kvh = h / (nh / nkv);
@@ -227,6 +232,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
 __global__ void attention_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                          const int* __restrict__ items, const int* __restrict__ positions,
                                          int nh, int d, int n_splits) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
     const int t = items ? items[blockIdx.x] : blockIdx.x;
     if (positions[t] < 0) return;
     const int h = blockIdx.y;
@@ -270,20 +277,21 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     const size_t smem = (size_t)DEC_GROUPS * d * sizeof(float);
     const float sl2 = scale * LOG2E;
 #define LAUNCH_DEC(NC)                                                                                         \
-    attention_decode_kernel<NC><<<grid, DEC_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,  \
-        n_splits > 1 ? partial : nullptr, items, positions, seq_of_token, slots, block_table, max_pages,        \
-        n_layers, layer, nh, nkv, d, page_size, sl2, window, n_splits, counters)
-    if (d <= 64) LAUNCH_DEC(1);
-    else if (d <= 128) LAUNCH_DEC(2);
-    else if (d <= 192) LAUNCH_DEC(3);
-    else LAUNCH_DEC(4);
+    st_launch_pdl("decode", attention_decode_kernel<NC>, grid, dim3(DEC_THREADS), smem, s, (const bf16*)q,               \
+        (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,              \
+        seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, sl2, window,       \
+        n_splits, counters)
+    int rc;
+    if (d <= 64) rc = LAUNCH_DEC(1);
+    else if (d <= 128) rc = LAUNCH_DEC(2);
+    else if (d <= 192) rc = LAUNCH_DEC(3);
+    else rc = LAUNCH_DEC(4);
 #undef LAUNCH_DEC
-    int rc = st_launch_status();
     if (rc) return rc;
     if (n_splits > 1 && !counters) {
         dim3 g2(n_items, nh);
-        attention_combine_kernel<<<g2, 64, 0, s>>>(partial, (bf16*)out, items, positions, nh, d, n_splits);
-        rc = st_launch_status();
+        rc = st_launch_pdl("combine", attention_combine_kernel, g2, dim3(64), 0, s, (const float*)partial, (bf16*)out, items,
+                           positions, nh, d, n_splits);
     }
     return rc;
 }

@@ -35,6 +35,19 @@ __device__ __forceinline__ float4 load4(const bf16* p) {
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
     return make_float4(a.x, a.y, b.x, b.y);
 }
+// the same through L2 only (see the note on programmatic dependent launch below): for data that the
+// kernel just before may have written while this block was already resident
+__device__ __forceinline__ float4 load4_cg(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4_cg(const bf16* p) {
+    const uint2 u = __ldcg(reinterpret_cast<const uint2*>(p));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float load1_cg(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float load1_cg(const bf16* p) {
+    return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(p))));
+}
 __device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ void store4(bf16* p, float4 v) {
     uint2 u;
@@ -88,3 +101,48 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 }
 
 static inline int st_launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch ---------------------------------------
+// Kernels of a decode step are short and depend on one another; launched this
+// way, a kernel's blocks may become resident while its predecessor in the
+// stream is still running.  A kernel launched so must execute ST_PDL_WAIT()
+// before it reads anything its predecessors write and before it writes
+// anything at all; what comes before the wait may only touch memory that no
+// kernel writes (weights).  After the wait every predecessor has finished and
+// its writes are visible.  ST_PDL_TRIGGER() lets the successor's blocks be
+// scheduled as soon as there is room.  In a kernel that is launched the plain
+// way both are no-ops.  ST_B200_NO_PDL=1 in the environment turns the launch
+// attribute off.
+#include <stdlib.h>
+#include <utility>
+#define ST_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+#define ST_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+
+#include <string.h>
+// ST_B200_NO_PDL=1 turns the attribute off for every kernel; ST_B200_PDL_ONLY=a,b limits it to the
+// kernels whose tag is listed (for finding a kernel that breaks the rules above).
+static inline bool st_pdl_enabled(const char* tag) {
+    const char* off = getenv("ST_B200_NO_PDL");
+    if (off && off[0] && off[0] != '0') return false;
+    const char* only = getenv("ST_B200_PDL_ONLY");
+    if (only && only[0]) return strstr(only, tag) != nullptr;
+    return true;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int st_launch_pdl(const char* tag, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = st_pdl_enabled(tag) ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return st_launch_status();
+}

@@ -18,19 +18,21 @@ template <typename T, typename TO, bool VEC>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ src,
                              int width, const int* __restrict__ pos, const T* __restrict__ pos_table,
                              int pos_offset, TO* __restrict__ out) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
     const int t = blockIdx.x;
     const T* row = src ? src + (size_t)t * width : table + (size_t)ids[t] * width;
     const T* prow = pos_table ? pos_table + (size_t)(pos[t] + pos_offset) * width : nullptr;
     TO* o = out + (size_t)t * width;
     if (VEC) {
         for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
-            float4 v = load4(row + e);
+            float4 v = src ? load4_cg(row + e) : load4(row + e);
             if (prow) v = add4(v, load4(prow + e));
             store4(o + e, v);
         }
     } else {
         for (int e = threadIdx.x; e < width; e += blockDim.x) {
-            float v = to_f32(row[e]);
+            float v = src ? load1_cg(row + e) : to_f32(row[e]);
             if (prow) v += to_f32(prow[e]);
             o[e] = from_f32<TO>(v);
         }
@@ -45,12 +47,10 @@ static int launch_embed(const int* ids, const void* table, const void* src, int 
     if (block > 512) block = 512;
     if (block < 32) block = 32;
     if (vec)
-        embed_kernel<T, TO, true><<<n_tokens, block, 0, s>>>(ids, (const T*)table, (const T*)src, width, pos,
-                                                              (const T*)pos_table, pos_offset, (TO*)out);
-    else
-        embed_kernel<T, TO, false><<<n_tokens, block, 0, s>>>(ids, (const T*)table, (const T*)src, width, pos,
-                                                               (const T*)pos_table, pos_offset, (TO*)out);
-    return st_launch_status();
+        return st_launch_pdl("embed", embed_kernel<T, TO, true>, dim3(n_tokens), dim3(block), 0, s, ids, (const T*)table,
+                             (const T*)src, width, pos, (const T*)pos_table, pos_offset, (TO*)out);
+    return st_launch_pdl("embed", embed_kernel<T, TO, false>, dim3(n_tokens), dim3(block), 0, s, ids, (const T*)table,
+                         (const T*)src, width, pos, (const T*)pos_table, pos_offset, (TO*)out);
 }
 
 // out[t] = table[ids[t]] (+ pos_table[pos[t] + pos_offset]);  out is float when out_f32, else the table's type
@@ -92,6 +92,8 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
                                 T* __restrict__ out_act, float* out_f32) {
     extern __shared__ __align__(16) float srow[];
     __shared__ float scratch[32];
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
     const int r = blockIdx.x;
     const size_t i = rows ? (size_t)rows[r] : (size_t)r;
     const float* xr = x + i * width;
@@ -101,10 +103,10 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
         for (int v0 = threadIdx.x; v0 < nvec; v0 += blockDim.x * 2) {   // two independent sets of loads in flight
             const int v1 = v0 + blockDim.x;
             const bool two = v1 < nvec;
-            float4 a = load4(xr + v0 * 4), b = two ? load4(xr + v1 * 4) : make_float4(0, 0, 0, 0);
+            float4 a = load4_cg(xr + v0 * 4), b = two ? load4_cg(xr + v1 * 4) : make_float4(0, 0, 0, 0);
             if (delta) {
-                a = add4(a, load4(delta + i * width + v0 * 4));
-                if (two) b = add4(b, load4(delta + i * width + v1 * 4));
+                a = add4(a, load4_cg(delta + i * width + v0 * 4));
+                if (two) b = add4(b, load4_cg(delta + i * width + v1 * 4));
             }
             if (delta_bias) {
                 a = add4(a, load4(delta_bias + v0 * 4));
@@ -123,8 +125,8 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
         }
     } else {
         for (int e = threadIdx.x; e < width; e += blockDim.x) {
-            float v = xr[e];
-            if (delta) v += to_f32(delta[i * width + e]);
+            float v = load1_cg(xr + e);
+            if (delta) v += load1_cg(delta + i * width + e);
             if (delta_bias) v += delta_bias[e];
             srow[e] = v;
             sum += v;
@@ -191,9 +193,8 @@ static int launch_add_norm(const float* x, const int* rows, const void* delta, c
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<n_rows, block, smem, s>>>(x, rows, (const T*)delta, delta_bias, resid_out, gamma, beta, eps, kind, width,
-                                     (T*)out_act, out_f32);
-    return st_launch_status();
+    return st_launch_pdl("norm", kern, dim3(n_rows), dim3(block), smem, s, x, rows, (const T*)delta, delta_bias, resid_out,
+                         gamma, beta, eps, kind, width, (T*)out_act, out_f32);
 }
 
 ST_EXPORT int st_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias,

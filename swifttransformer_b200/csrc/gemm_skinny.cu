@@ -8,10 +8,12 @@
 // straight from global memory, 16 contiguous bytes at a time: within a block of
 // 32 k the lane with (group g, thread-in-group t) takes k = 8t..8t+7 of row g and
 // row g+8 of w and of token g of x, and feeds elements (0,1 | 2,3) and (4,5 | 6,7)
-// to two consecutive products.  The product sums over k, so any assignment of k
+// to two consecutive products.  (The activations are read with L2-only loads: under programmatic
+// dependent launch this block may have become resident before its predecessor wrote them, and
+// only loads that bypass the per-SM caches are sure to see the new values after the wait.)  The product sums over k, so any assignment of k
 // to fragment slots is right as long as w and x use the same one.  No shared
 // memory staging, no barriers in the main loop; each of the block's 8 warps
-// takes every 8th k-block (four blocks in flight) and the partial sums meet in
+// takes every 8th k-block (two rounds of two blocks in flight) and the partial sums meet in
 // shared memory.  One thread block per 16 output features and slice of k: when
 // there are too few features to fill the GPU, k is cut into slices
 // (gridDim.y); each block leaves its partial sums in a scratch buffer and the
@@ -32,7 +34,7 @@
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
-#define SK_UNROLL 4
+#define SK_UNROLL 2
 
 struct QkvTarget {
     bf16* q_out;               // [M, qw]
@@ -87,27 +89,54 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     const int kb_begin = blockIdx.y * per_slice;
     const int nkb = min(nkb_all, kb_begin + per_slice);
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int kb0 = kb_begin + warp; kb0 < nkb; kb0 += SK_WARPS * SK_UNROLL) {
-        uint4 ua[SK_UNROLL], ub[SK_UNROLL], xb[SK_UNROLL][NT];
+    // Two register buffers of SK_UNROLL k-blocks each: the loads of the next round are in flight
+    // while the current one is multiplied.  The successor may be scheduled from now on; this
+    // kernel's own first round of weight loads is issued before it waits for its predecessor
+    // (weights are written by no kernel, so the memory system stays busy across the kernel
+    // boundary); the activations are read after the wait.
+    struct Round { uint4 ua[SK_UNROLL], ub[SK_UNROLL], xb[SK_UNROLL][NT]; };
+    auto issue_w = [&](Round& r, int kb0) {
 #pragma unroll
         for (int u = 0; u < SK_UNROLL; ++u) {
             const int kb = kb0 + u * SK_WARPS;
-            const int k = kb * 32;
-            const bool ok = kb < nkb && k + t * 8 < K;   // K % 8 == 0: a 16-byte piece is inside or outside as a whole
-            ua[u] = ok ? ldg_stream(wa + k) : zero;
-            ub[u] = ok ? ldg_stream(wb + k) : zero;
+            const bool ok = kb < nkb && kb * 32 + t * 8 < K;   // K % 8 == 0: a 16-byte piece is inside or outside as a whole
+            r.ua[u] = ok ? ldg_stream(wa + kb * 32) : zero;
+            r.ub[u] = ok ? ldg_stream(wb + kb * 32) : zero;
+        }
+    };
+    auto issue_x = [&](Round& r, int kb0) {
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+            const int kb = kb0 + u * SK_WARPS;
+            const bool ok = kb < nkb && kb * 32 + t * 8 < K;
 #pragma unroll
             for (int j = 0; j < NT; ++j)
-                xb[u][j] = (ok && xok[j]) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
+                r.xb[u][j] = (ok && xok[j]) ? __ldcg(reinterpret_cast<const uint4*>(xr[j] + kb * 32)) : zero;
         }
+    };
+    auto consume = [&](const Round& r) {
 #pragma unroll
         for (int u = 0; u < SK_UNROLL; ++u) {
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                mma16816(acc[j], ua[u].x, ub[u].x, ua[u].y, ub[u].y, xb[u][j].x, xb[u][j].y);
-                mma16816(acc[j], ua[u].z, ub[u].z, ua[u].w, ub[u].w, xb[u][j].z, xb[u][j].w);
+                mma16816(acc[j], r.ua[u].x, r.ub[u].x, r.ua[u].y, r.ub[u].y, r.xb[u][j].x, r.xb[u][j].y);
+                mma16816(acc[j], r.ua[u].z, r.ub[u].z, r.ua[u].w, r.ub[u].w, r.xb[u][j].z, r.xb[u][j].w);
             }
         }
+    };
+    ST_PDL_TRIGGER();
+    constexpr int STEP = SK_WARPS * SK_UNROLL;
+    const int kb_first = kb_begin + warp;
+    Round ra, rb;
+    issue_w(ra, kb_first);          // out-of-range blocks load nothing
+    ST_PDL_WAIT();
+    issue_x(ra, kb_first);
+    for (int kb0 = kb_first; kb0 < nkb; kb0 += 2 * STEP) {
+        const bool more_b = kb0 + STEP < nkb;
+        if (more_b) { issue_w(rb, kb0 + STEP); issue_x(rb, kb0 + STEP); }
+        consume(ra);
+        if (kb0 + 2 * STEP < nkb) { issue_w(ra, kb0 + 2 * STEP); issue_x(ra, kb0 + 2 * STEP); }
+        if (more_b) consume(rb);
     }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -184,13 +213,14 @@ ST_EXPORT long long st_gemm_skinny_scratch_floats(int max_features) {
 }
 ST_EXPORT long long st_gemm_skinny_counter_ints(int max_features) { return (max_features + 15) / 16; }
 
-// how many slices k is cut into: enough blocks for about four per SM, at least eight k-blocks per slice
+// how many slices k is cut into: as many blocks as fit on the GPU at once (about four per SM) and no
+// more, so that there is no second, nearly empty wave; at least one round of loads per warp and slice
 static int skinny_slices(int N, int K, int scratch_tiles) {
     const int tiles = (N + 15) / 16;
     if (tiles > scratch_tiles) return 1;
-    int s = (4 * 148 + tiles - 1) / tiles;
+    int s = (4 * 148) / tiles;
     const int nkb = (K + 31) / 32;
-    if (s > nkb / 8) s = nkb / 8;
+    if (s > nkb / (SK_WARPS * SK_UNROLL)) s = nkb / (SK_WARPS * SK_UNROLL);
     if (s > SK_MAX_SLICES) s = SK_MAX_SLICES;
     return s < 1 ? 1 : s;
 }
@@ -206,12 +236,11 @@ static int launch_skinny(const void* x, const void* w, const float* bias, void* 
     const int slices = (scratch && counters) ? skinny_slices(N, K, scratch_tiles) : 1;
     dim3 grid((N + 15) / 16, slices);
     if (M <= 8)
-        gemm_skinny_kernel<1, QKV><<<grid, SK_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
+        return st_launch_pdl("skinny", gemm_skinny_kernel<1, QKV>, grid, dim3(SK_THREADS), 0, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
     else if (M <= 16)
-        gemm_skinny_kernel<2, QKV><<<grid, SK_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
+        return st_launch_pdl("skinny", gemm_skinny_kernel<2, QKV>, grid, dim3(SK_THREADS), 0, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
     else
-        gemm_skinny_kernel<4, QKV><<<grid, SK_THREADS, 0, s>>>((const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
-    return st_launch_status();
+        return st_launch_pdl("skinny", gemm_skinny_kernel<4, QKV>, grid, dim3(SK_THREADS), 0, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
 }
 
 // scratch / counters may be null (no k-slicing); scratch_tiles = feature tiles they were sized for
