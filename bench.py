@@ -102,6 +102,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--launch-floor", action="store_true",
+                    help="with --only decode: same number of layers and kernels, but hidden size 64, so that the "
+                         "step time is what the chain of dependent launches costs by itself")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run just the device-timed decode loop or just the prefill (for profiling small cases)")
     args = ap.parse_args()
@@ -132,6 +135,9 @@ def main():
     full_layers = cfg.num_hidden_layers
     if args.layers and args.layers < full_layers:
         cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
+    if args.launch_floor:
+        cfg = dataclasses.replace(cfg, hidden_size=64, ffn_dim=256, num_attention_heads=1, word_embed_proj_dim=64,
+                                  vocab_size=512)
     torch.cuda.set_device(0)
     model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     P, K, W = args.prompt_len, args.steps, args.warmup

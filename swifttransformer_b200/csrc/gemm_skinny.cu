@@ -15,11 +15,13 @@
 // memory staging, no barriers in the main loop; each of the block's 8 warps
 // takes every 8th k-block (two rounds of two blocks in flight) and the partial sums meet in
 // shared memory.  One thread block per 16 output features and slice of k: when
-// there are too few features to fill the GPU, k is cut into slices
-// (gridDim.y); each block leaves its partial sums in a scratch buffer and the
-// block that arrives last at a feature tile (a counter per tile, reset by that
-// block) adds the slices in slice order and runs the epilogue, so the result
-// does not depend on which block came last.
+// there are too few features to fill the GPU, k is cut into up to 8 slices
+// (gridDim.y) whose blocks form a thread-block cluster; the partial sums stay
+// in each block's shared memory, and after a cluster barrier the first block
+// of the cluster adds them in slice order through distributed shared memory
+// and runs the epilogue.  No global scratch, no fences, no atomics: a round
+// trip through L2 costs more than a microsecond here, and the old scheme
+// (scratch + counter + re-read) needed four of them.
 //
 // Epilogues: bias and activation; float or bfloat16 output; or the fused
 // q|k|v form: q (+bias) to a dense buffer, k and v (+bias) straight into the
@@ -31,6 +33,8 @@
 // src/csrc/model/gpt/gpt.cc:192-201) and adds bias / activation / cache
 // writes in separate kernels.
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
@@ -64,10 +68,9 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
 template <int NT, bool QKV>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
-                   void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt,
-                   float* __restrict__ split_scratch, int* __restrict__ split_counters) {
+                   void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt) {
     __shared__ float red[SK_WARPS][16][8 * NT + 1];
-    __shared__ int s_last;
+    __shared__ float part[16 * 8 * NT];      // this block's sums over its slice of k
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * 16;
     const bf16* wa = w + (size_t)min(row0 + g, N - 1) * K + t * 8;
@@ -146,40 +149,34 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
     }
     __syncthreads();
-    const int n_slices = gridDim.y;
+    const int n_slices = gridDim.y;            // == cluster size when > 1
     if (n_slices > 1) {
-        // leave this slice's sums in the scratch buffer; the block that arrives last finishes the tile
-        float* mine = split_scratch + ((size_t)blockIdx.x * n_slices + blockIdx.y) * (16 * 8 * NT);
         for (int i = threadIdx.x; i < 16 * 8 * NT; i += SK_THREADS) {
             const int r = i & 15, m = i >> 4;
             float v = 0.f;
 #pragma unroll
             for (int wi = 0; wi < SK_WARPS; ++wi) v += red[wi][r][m];
-            mine[i] = v;
+            part[i] = v;
         }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const int arrived = atomicAdd(split_counters + blockIdx.x, 1);
-            s_last = arrived == n_slices - 1;
-            if (s_last) split_counters[blockIdx.x] = 0;     // ready for the next launch
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                        // every slice's sums are in place
+        if (cluster.block_rank() != 0) {
+            cluster.sync();                    // stay until the first block has read this block's sums
+            return;
         }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
     }
     for (int i = threadIdx.x; i < 16 * 8 * NT; i += SK_THREADS) {
         const int r = i & 15, m = i >> 4;
         const int n = row0 + r;
-        if (m >= M || n >= N) continue;
         float v = 0.f;
         if (n_slices > 1) {
-            const float* tile = split_scratch + (size_t)blockIdx.x * n_slices * (16 * 8 * NT);
-            for (int sl = 0; sl < n_slices; ++sl) v += __ldcg(tile + (size_t)sl * (16 * 8 * NT) + i);
+            cg::cluster_group cluster = cg::this_cluster();
+            for (int sl = 0; sl < n_slices; ++sl) v += cluster.map_shared_rank(part, sl)[i];
         } else {
 #pragma unroll
             for (int wi = 0; wi < SK_WARPS; ++wi) v += red[wi][r][m];
         }
+        if (m >= M || n >= N) continue;
         if (bias) v += bias[n];
         if (!QKV) {
             v = apply_act(v, act);
@@ -202,53 +199,69 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
             }
         }
     }
+    if (n_slices > 1) cg::this_cluster().sync();   // the other blocks of the cluster may leave now
 }
 
 ST_EXPORT int st_gemm_skinny_max_rows() { return 32; }
 
-// Scratch for the k-slices: floats and per-tile counters the caller provides (counters zeroed once).
-#define SK_MAX_SLICES 16
-ST_EXPORT long long st_gemm_skinny_scratch_floats(int max_features) {
-    return (long long)((max_features + 15) / 16) * SK_MAX_SLICES * (16 * 8 * 4);
-}
-ST_EXPORT long long st_gemm_skinny_counter_ints(int max_features) { return (max_features + 15) / 16; }
-
-// how many slices k is cut into: as many blocks as fit on the GPU at once (about four per SM) and no
-// more, so that there is no second, nearly empty wave; at least one round of loads per warp and slice
-static int skinny_slices(int N, int K, int scratch_tiles) {
+// how many slices k is cut into (the cluster size): as many blocks as fit on the GPU at once (about
+// four per SM) and no more, at most 8; at least one round of loads per warp and slice
+static int skinny_slices(int N, int K) {
     const int tiles = (N + 15) / 16;
-    if (tiles > scratch_tiles) return 1;
     int s = (4 * 148) / tiles;
     const int nkb = (K + 31) / 32;
     if (s > nkb / (SK_WARPS * SK_UNROLL)) s = nkb / (SK_WARPS * SK_UNROLL);
-    if (s > SK_MAX_SLICES) s = SK_MAX_SLICES;
+    if (s > 8) s = 8;
     return s < 1 ? 1 : s;
+}
+
+template <typename... KArgs, typename... Args>
+static int launch_skinny_kernel(void (*kernel)(KArgs...), dim3 grid, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(SK_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (st_pdl_enabled("skinny")) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (grid.y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = grid.y;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return st_launch_status();
 }
 
 template <bool QKV>
 static int launch_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, int act,
-                         int out_f32, const QkvTarget& tgt, float* scratch, int* counters, int scratch_tiles,
-                         cudaStream_t s) {
+                         int out_f32, const QkvTarget& tgt, cudaStream_t s) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 32) return ST_ERR_TOO_LARGE;
     if (K <= 0 || K % 8) return ST_ERR_BAD_SIZE;
     if (!aligned16(x) || !aligned16(w)) return ST_ERR_BAD_ARG;
-    const int slices = (scratch && counters) ? skinny_slices(N, K, scratch_tiles) : 1;
-    dim3 grid((N + 15) / 16, slices);
+    dim3 grid((N + 15) / 16, skinny_slices(N, K));
     if (M <= 8)
-        return st_launch_pdl("skinny", gemm_skinny_kernel<1, QKV>, grid, dim3(SK_THREADS), 0, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
-    else if (M <= 16)
-        return st_launch_pdl("skinny", gemm_skinny_kernel<2, QKV>, grid, dim3(SK_THREADS), 0, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
-    else
-        return st_launch_pdl("skinny", gemm_skinny_kernel<4, QKV>, grid, dim3(SK_THREADS), 0, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, scratch, counters);
+        return launch_skinny_kernel(gemm_skinny_kernel<1, QKV>, grid, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
+    if (M <= 16)
+        return launch_skinny_kernel(gemm_skinny_kernel<2, QKV>, grid, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
+    return launch_skinny_kernel(gemm_skinny_kernel<4, QKV>, grid, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
 }
 
-// scratch / counters may be null (no k-slicing); scratch_tiles = feature tiles they were sized for
 ST_EXPORT int st_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                             int act, int out_f32, float* scratch, int* counters, int scratch_tiles, void* stream) {
+                             int act, int out_f32, void* stream) {
     QkvTarget none = {};
-    return launch_skinny<false>(x, w, bias, out, M, N, K, act, out_f32, none, scratch, counters, scratch_tiles,
-                                (cudaStream_t)stream);
+    return launch_skinny<false>(x, w, bias, out, M, N, K, act, out_f32, none, (cudaStream_t)stream);
 }
 
 // x [M,K] . w [(nh + 2 nkv) d, K]^T + bias -> q_out [M, nh d] and the paged cache
@@ -256,13 +269,12 @@ ST_EXPORT int st_gemm_skinny_qkv(const void* x, const void* w, const float* bias
                                  const int* positions, const int* seq_of_token, const int* slots,
                                  const int* block_table, int max_pages, int num_pages, int n_layers, int layer,
                                  int M, int K, int nh, int nkv, int d, int page_size, int write_kv, int* status,
-                                 float* scratch, int* counters, int scratch_tiles, void* stream) {
+                                 void* stream) {
     if (nh <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || layer < 0 || layer >= n_layers) return ST_ERR_BAD_ARG;
     QkvTarget tgt;
     tgt.q_out = (bf16*)q_out; tgt.pool = (bf16*)pool; tgt.positions = positions; tgt.seq_of_token = seq_of_token;
     tgt.slots = slots; tgt.block_table = block_table; tgt.status = status; tgt.max_pages = max_pages;
     tgt.num_pages = num_pages; tgt.n_layers = n_layers; tgt.layer = layer; tgt.nkv = nkv; tgt.d = d;
     tgt.page_size = page_size; tgt.qw = nh * d; tgt.write_kv = write_kv;
-    return launch_skinny<true>(x, w, bias, nullptr, M, (nh + 2 * nkv) * d, K, 0, 0, tgt, scratch, counters,
-                               scratch_tiles, (cudaStream_t)stream);
+    return launch_skinny<true>(x, w, bias, nullptr, M, (nh + 2 * nkv) * d, K, 0, 0, tgt, (cudaStream_t)stream);
 }

@@ -329,7 +329,8 @@ class ModelRunner:
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault (a hole in a block table).  Synchronises."""
-        if int(self.status.item()) != 0:
+        code = int(self.status.item())
+        if code != 0:
             self.status.zero_()
             raise RuntimeError("a kernel found a token whose position has no page in its block table")
 
@@ -412,6 +413,7 @@ class ModelRunner:
         ctx.h_kv_len = [s + n for s, n in zip(ctx.h_start_pos, lens)]
         ctx.h_slots = [e.slot for e in entries]
         ctx.status, ctx.act_dtype, ctx.device = self.status, self.model.dtype, self.device
-        ctx._plan = AttentionPlan(view("items"), len(items), view("tiles"), len(tiles), max_item_kv)
+        ctx._plan = AttentionPlan(view("items"), len(items), view("tiles"), len(tiles),
+                                  max(max_item_kv, max(ctx.h_kv_len)))
         ctx._scratch_owner = self
         return ctx

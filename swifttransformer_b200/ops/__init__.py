@@ -42,7 +42,6 @@ def lib() -> ctypes.CDLL:
         except OSError as e:
             raise KernelError(f"cannot load {path}: {e}") from None
         _LIB.st_attention_decode_scratch_floats.restype = ctypes.c_longlong
-        _LIB.st_gemm_skinny_scratch_floats.restype = ctypes.c_longlong
         _LIB.st_uniform_host.restype = ctypes.c_float
         _LIB.st_uniform_host.argtypes = [ctypes.c_longlong, ctypes.c_longlong]
     return _LIB
@@ -182,21 +181,6 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
 
 SKINNY_MAX_ROWS = 32    # up to this many tokens the weight-streaming kernel serves bfloat16 products
-_SKINNY_TILES = 600     # feature tiles (of 16) the k-slicing scratch is sized for; wider products are not sliced
-_skinny_buffers = {}
-
-
-def _skinny_scratch(device: torch.device):
-    """Per-device scratch of the skinny product's k-slices: partial sums and per-tile arrival counters.
-    Allocated once at first use (which must not be inside a graph recording) and kept for good; launches
-    on one stream use it one after the other."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    if key not in _skinny_buffers:
-        n = int(lib().st_gemm_skinny_scratch_floats(_SKINNY_TILES * 16))
-        _skinny_buffers[key] = (torch.empty(n, dtype=torch.float32, device=device),
-                                torch.zeros(_SKINNY_TILES, dtype=torch.int32, device=device))
-    return _skinny_buffers[key]
-
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
@@ -210,10 +194,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     n, k = a.shape
     m = w.shape[0]
     out = torch.empty((n, m), dtype=out_dtype, device=a.device)
-    scratch, counters = _skinny_scratch(a.device)
     _check(lib().st_gemm_skinny(_p(a), _p(w), _p(bias), _p(out), n, m, k, ACT_CODES[act],
-                                int(out_dtype == torch.float32), _p(scratch), _p(counters), _SKINNY_TILES,
-                                _stream()), "gemm_skinny")
+                                int(out_dtype == torch.float32), _stream()), "gemm_skinny")
     return out
 
 
@@ -227,11 +209,10 @@ def qkv_linear_to_cache(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.T
         raise KernelError("qkv_linear_to_cache is a bfloat16 kernel")
     num_pages, n_layers, _, pnkv, page_size, pd = pool.shape
     assert pnkv == nkv and pd == d and w.shape[0] == (nh + 2 * nkv) * d and h.is_contiguous() and w.is_contiguous()
-    scratch, counters = _skinny_scratch(h.device)
     _check(lib().st_gemm_skinny_qkv(_p(h), _p(w), _p(bias), _p(q_out), _p(pool), _p(positions), _p(seq_of_token),
                                     _p(slots), _p(block_table), block_table.shape[1], num_pages, n_layers, layer,
                                     h.shape[0], h.shape[1], nh, nkv, d, page_size, int(write_kv), _p(status),
-                                    _p(scratch), _p(counters), _SKINNY_TILES, _stream()), "qkv_linear_to_cache")
+                                    _stream()), "qkv_linear_to_cache")
 
 
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
