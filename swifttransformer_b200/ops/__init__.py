@@ -302,14 +302,37 @@ def attention_prefill_tile_rows() -> int:
     return int(lib().st_attention_prefill_tile_rows())
 
 
+_tc_status = {}
+
+
+def _tc_status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
 def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,
                       n_tiles: int, q_start: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
-                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0) -> torch.Tensor:
-    """bfloat16 tensor-core paged attention over tiles of 64 query tokens; tiles: int32 [n_tiles, 2] =
-    (request index in the step, offset of the tile among the request's new tokens)."""
+                      block_table: torch.Tensor, nh: int, scale: float, window: int = 0,
+                      status: Optional[torch.Tensor] = None, kernel: str = "auto") -> torch.Tensor:
+    """bfloat16 tensor-core paged attention over tiles of 128 query tokens; tiles: int32 [n_tiles, 2] =
+    (request index in the step, offset of the tile among the request's new tokens).
+
+    kernel: "tc" = the tcgen05 kernel (head sizes up to 128), "mma" = the mma.sync kernel (up to 256),
+    "auto" = tcgen05 where it applies.  ``status`` receives 3 if the tcgen05 kernel gave up waiting."""
     _, n_layers, _, nkv, page_size, d = pool.shape
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill is a bfloat16 kernel")
+    if kernel == "auto":
+        kernel = "tc" if d <= 128 else "mma"
+    if kernel == "tc":
+        st = status if status is not None else _tc_status_word(q.device)
+        _check(lib().st_attention_prefill_tc(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start),
+                                             _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
+                                             n_layers, layer, nh, nkv, d, page_size, _f(scale), window, _p(st),
+                                             _stream()), "attention_prefill_tc")
+        return out
     _check(lib().st_attention_prefill(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start), _p(start_pos),
                                       _p(slots), _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv,
                                       d, page_size, _f(scale), window, _stream()), "attention_prefill")

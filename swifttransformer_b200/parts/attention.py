@@ -38,7 +38,7 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
     plan = ctx.attention_plan()
     if plan.n_tiles:
         ops.attention_prefill(q, cache.pool, cache.layer, out, plan.tiles, plan.n_tiles, ctx.q_start,
-                              ctx.start_pos, ctx.slots, cache.block_table, nh, scale, window)
+                              ctx.start_pos, ctx.slots, cache.block_table, nh, scale, window, status=ctx.status)
     if plan.n_items:
         n_splits = plan.splits(nh)
         ops.attention_decode(q, cache.pool, cache.layer, out, plan.items, plan.n_items, ctx.positions,

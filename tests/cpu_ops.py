@@ -166,7 +166,7 @@ def attention_prefill_tile_rows():
 
 
 def attention_prefill(q, pool, layer, out, tiles, n_tiles, q_start, start_pos, slots, block_table, nh, scale,
-                      window=0):
+                      window=0, status=None, kernel="auto"):
     n = q.shape[0]
     pos = torch.full((n,), -1, dtype=torch.int32)
     seq_of = torch.zeros(n, dtype=torch.int32)
