@@ -332,7 +332,7 @@ class ModelRunner:
         code = int(self.status.item())
         if code != 0:
             self.status.zero_()
-            if code == 3:
+            if code in (3, 4):
                 raise RuntimeError("the tcgen05 attention kernel gave up waiting for the tensor cores; "
                                    "the step's result is invalid")
             raise RuntimeError("a kernel found a token whose position has no page in its block table")

@@ -53,9 +53,14 @@ def sources() -> List[str]:
     return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
+def _flags() -> List[str]:
+    """NVCC_FLAGS plus what ST_B200_NVCC_EXTRA adds (e.g. -DTC_PROFILE for a kernel's timing stamps)."""
+    return NVCC_FLAGS + os.environ.get("ST_B200_NVCC_EXTRA", "").split()
+
+
 def _digest(nvcc: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     try:
         h.update(subprocess.run([nvcc, "--version"], capture_output=True, check=True).stdout)
     except Exception:
@@ -117,7 +122,7 @@ def ensure_built(verbose: bool = True) -> str:
         env.setdefault("TMPDIR", bdir)
         for src in srcs:
             obj = os.path.join(bdir, src[:-3] + ".o")
-            cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+            cmd = [nvcc] + _flags() + ["-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
             jobs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)))
         pending = list(jobs)
         last = time.time()
