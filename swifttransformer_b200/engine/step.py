@@ -49,10 +49,13 @@ class StepEntry:
     want: Sequence[int] = ()        # places among `tokens` whose logits are wanted
 
 
+SPLIT_TARGET = 2   # blocks per SM the split decode attention aims for
+
+
 def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148) -> int:
     """Parts the key range of a single-token query is cut into, so that the launch fills the GPU."""
     blocks = max(1, n_items * nh)
-    s = max(1, (2 * sms + blocks - 1) // blocks)
+    s = max(1, (SPLIT_TARGET * sms + blocks - 1) // blocks)
     return min(s, max(1, max_kv // 128), 32)
 
 

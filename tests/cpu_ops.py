@@ -87,7 +87,7 @@ def linear(a, w, bias=None, act="none", out_dtype=None):
 
 gemm_plain = linear
 gemm_skinny = linear
-SKINNY_MAX_ROWS = 32
+SKINNY_MAX_ROWS = 8
 
 
 def qkv_linear_to_cache(h, w, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d,
