@@ -58,6 +58,15 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     per = (per + 15) / 16 * 16;
     const int k_lo = lo + split * per;
     const int k_hi = min(hi, k_lo + per);
+    // the page ids of this block's key range, fetched once: a round then costs one trip to memory
+    // (the rows), not two (page id, then rows)
+    int* s_pages = reinterpret_cast<int*>(s_acc + DEC_GROUPS * d);
+    const int p_lo = k_lo / page_size;
+    if (k_lo < k_hi) {
+        const int n_pages = (k_hi - 1) / page_size - p_lo + 1;
+        for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) s_pages[i] = __ldcg(bt + p_lo + i);
+    }
+    __syncthreads();
 
     const int g = threadIdx.x >> 3, l8 = threadIdx.x & 7;
     float qf[NCHUNK][8];
@@ -99,9 +108,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
             const int kk = key0 + u * DEC_GROUPS + g;
             r.valid[u] = kk < k_hi;
             const int key = r.valid[u] ? kk : k_hi - 1;
-            const int page = bt[key / page_size];
+            const int pg = key / page_size;
+            const int page = s_pages[pg - p_lo];
             const bf16* krow = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
-                               + (size_t)(key % page_size) * d;
+                               + (size_t)(key - pg * page_size) * d;
 #pragma unroll
             for (int c = 0; c < NCHUNK; ++c) {
                 const int dim0 = (c * 8 + l8) * 8;
@@ -274,7 +284,9 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     if (n_splits > 1 && !partial) return ST_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_items, nh, n_splits);
-    const size_t smem = (size_t)DEC_GROUPS * d * sizeof(float);
+    // merge buffers of the 16 key groups, then the page ids of the block's key range
+    const size_t smem = (size_t)DEC_GROUPS * d * sizeof(float) + (size_t)max_pages * sizeof(int);
+    if (smem > 48 * 1024) return ST_ERR_TOO_LARGE;
     const float sl2 = scale * LOG2E;
 #define LAUNCH_DEC(NC)                                                                                         \
     st_launch_pdl("decode", attention_decode_kernel<NC>, grid, dim3(DEC_THREADS), smem, s, (const bf16*)q,               \

@@ -66,7 +66,7 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
 }
 
 template <int NT, bool QKV>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 4 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
                    void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt) {
     __shared__ float red[SK_WARPS][16][8 * NT + 1];
