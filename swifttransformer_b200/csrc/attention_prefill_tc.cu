@@ -35,97 +35,9 @@
 // Same mathematics as attention_prefill.cu (the mma.sync kernel, which stays for head sizes
 // above 128) and as the plain kernel.  Reference counterparts:
 // src/csrc/kernel/fused_context_stage_attention.cu:82-453 and src/csrc/kernel/xformers_attention.cu:313-393.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
-#define TC_BM 128
-#define TC_BN 64
 #define TC_SET_THREADS 256  // two warpgroups work on one (query tile, head)
-#define TC_LOG2E 1.4426950408889634f
-#define TC_WAIT_LIMIT (1u << 21)     // polls of about 50 ns each: a wait gives up after roughly 0.1 s
-
-__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void tc_cp16(uint32_t dst, const void* src, bool pred) {
-    const int n = pred ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
-}
-__device__ __forceinline__ void tc_cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void tc_cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-// writes made through the generic proxy (cp.async, st.shared) become visible to the tensor cores' async proxy
-__device__ __forceinline__ void tc_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-__device__ __forceinline__ float tc_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// shared-memory matrix descriptor: 128-byte swizzle, descriptor version 1 (sm_100)
-__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
-}
-// instruction descriptor, kind::f16: bfloat16 operands, float accumulator
-__device__ __forceinline__ uint32_t tc_idesc(int m, int n, int a_mn_major, int b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t mbar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
-}
-// bounded wait for the given phase parity; false: gave up
-__device__ __forceinline__ bool tc_wait(uint32_t mbar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.b32 %0, 1, 0, p;\n\t}\n" : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
-        if (done) return true;
-        if (i > 64) __nanosleep(32);
-    }
-    return false;
-}
-// 32 consecutive float columns of this thread's TMEM lane: the load is only issued here; the values
-// may be used after tc_ld_wait() (several loads can be in flight under one wait)
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
-    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};\n"
-                 ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
-                   "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-// barrier of one warpgroup; the ids are immediates: with a register operand the compiler reserves all
-// sixteen barriers for the block, and two such blocks do not fit one SM
-__device__ __forceinline__ void tc_wg_sync(int wgi) {
-    if (wgi == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
-    else if (wgi == 1) asm volatile("bar.sync 2, 128;\n" ::: "memory");
-    else if (wgi == 2) asm volatile("bar.sync 3, 128;\n" ::: "memory");
-    else asm volatile("bar.sync 4, 128;\n" ::: "memory");
-}
 
 // DB: 64-wide blocks of the head dimension (1: head_dim <= 64, 2: <= 128).  TC_SETS (query tile, head)
 // pairs per block: a set needs 2 x (64 + 64 DB) of the 512 tensor-memory columns, so 2 is possible for DB == 1.

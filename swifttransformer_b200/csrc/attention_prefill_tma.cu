@@ -1,0 +1,484 @@
+// Paged, chunked causal attention for portions of prompts: tcgen05 tensor cores fed by TMA.
+//
+// The variant of attention_prefill_tc.cu for head sizes 64 and 128 and pages of 8, 16, 32 or 64
+// positions (a tile of 64 keys is then a whole number of pages).  Same mathematics and the same
+// layouts in shared and tensor memory; what differs is who does what:
+//
+//   * Keys and values come in by TMA: one rank-3 tensor map describes the whole cache pool as
+//     [page x layer x (K|V) x kv_head][position in page][head_dim]; a box is (one page of one head,
+//     64 of the head's elements) and lands in shared memory already in the 128-byte swizzle that the
+//     matrix descriptors expect.  A copy announces its bytes on an mbarrier (expect_tx) and the
+//     barrier completes when they have landed.  No multicast; only pages that hold a key the tile
+//     may see are fetched (the others may have been given back): the rest of a tile, which is
+//     masked, is filled from the tile's first live page so that it holds finite numbers.
+//   * Each of the two warpgroups (alternate key tiles of one (query tile, head), merged at the end)
+//     has an extra warp whose first lane issues the copies and the products.  Keys and values are
+//     double-buffered, so S of the next tile is issued as soon as the softmax threads have read S of
+//     this one from tensor memory and runs under their softmax; O += P V follows when P is written.
+//
+// Waits are bounded; a wait that expires marks the block dead, the block's other waits end early,
+// `status` gets 3, tensor memory is freed and the kernel returns.
+// Reference counterparts: src/csrc/kernel/fused_context_stage_attention.cu:82-453 and
+// src/csrc/kernel/xformers_attention.cu:313-393.
+#include <cuda.h>
+#include <mutex>
+
+#include "tcgen05.cuh"
+
+#define TM_THREADS 320   // 2 warpgroups of softmax threads + 2 issuing warps
+
+// bounded wait that also ends when the block has been marked dead
+__device__ __forceinline__ bool tm_wait(uint32_t mbar, uint32_t parity, volatile int* dead) {
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.b32 %0, 1, 0, p;\n\t}\n" : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
+        if (done) return true;
+        if (i > 64) {
+            if ((i & 63) == 0 && *dead) return false;
+            __nanosleep(32);
+        }
+    }
+    *dead = 1;
+    return false;
+}
+// named barriers of a warpgroup and its issuing warp (160 threads): A = "S has been read",
+// B = "P has been written".  Softmax threads only arrive, the issuing warp waits.
+__device__ __forceinline__ void tm_arrive(int wg, int which) {
+    if (wg == 0) { if (which == 0) asm volatile("bar.arrive 1, 160;\n" ::: "memory"); else asm volatile("bar.arrive 2, 160;\n" ::: "memory"); }
+    else         { if (which == 0) asm volatile("bar.arrive 3, 160;\n" ::: "memory"); else asm volatile("bar.arrive 4, 160;\n" ::: "memory"); }
+}
+__device__ __forceinline__ void tm_sync(int wg, int which) {
+    if (wg == 0) { if (which == 0) asm volatile("bar.sync 1, 160;\n" ::: "memory"); else asm volatile("bar.sync 2, 160;\n" ::: "memory"); }
+    else         { if (which == 0) asm volatile("bar.sync 3, 160;\n" ::: "memory"); else asm volatile("bar.sync 4, 160;\n" ::: "memory"); }
+}
+
+// DB: 64-wide blocks of the head dimension (head_dim == 64 DB)
+template <int DB>
+__global__ void __launch_bounds__(TM_THREADS, 1)
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q,
+                             bf16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ q_start,
+                             const int* __restrict__ start_pos, const int* __restrict__ slots,
+                             const int* __restrict__ block_table, int max_pages, int n_layers, int layer,
+                             int nh, int nkv, int page_size, float scale_log2, int window, int* status) {
+    extern __shared__ unsigned char tm_raw[];
+    // per warpgroup: S done, O done, K landed x2, V landed x2
+    __shared__ __align__(8) unsigned long long s_mbar[2][6];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_dead;
+    constexpr int d = 64 * DB;
+    constexpr uint32_t Q_BLK = TC_BM * 128, KV_BLK = TC_BN * 128;       // bytes of one [rows][64] block
+    constexpr uint32_t BUF = DB * KV_BLK;                               // one key or value tile
+    constexpr uint32_t WG_BYTES = 4 * BUF + Q_BLK;                      // K x2, V x2, P
+    constexpr int WG_COLS = 64 + 64 * DB;                               // S, then O
+    constexpr uint32_t ALL_BYTES = DB * Q_BLK + 2 * WG_BYTES;
+    constexpr int TMEM_COLS = 2 * WG_COLS <= 256 ? 256 : 512;
+    const uint32_t base = (tc_smem(tm_raw) + 1023u) & ~1023u;           // swizzled tiles start on 1024-byte boundaries
+
+    const int tid = threadIdx.x;
+    const bool issuer = tid >= 256;                                      // warps 8 and 9
+    const int wg = issuer ? (tid - 256) >> 5 : tid >> 7;
+    const int row = tid & 127, warp4 = (tid >> 5) & 3;
+    {
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        if (base + ALL_BYTES > tc_smem(tm_raw) + dyn) {
+            if (tid == 0) atomicExch(status, 4);
+            return;
+        }
+    }
+    const uint32_t sQ = base;
+    const uint32_t sK = sQ + DB * Q_BLK + wg * WG_BYTES;                 // two key buffers
+    const uint32_t sV = sK + 2 * BUF;                                    // two value buffers
+    const uint32_t sP = sV + 2 * BUF;                                    // one [128][64] block
+
+    const int seq = tiles[2 * blockIdx.x], off = tiles[2 * blockIdx.x + 1];
+    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    const int tok0 = q_start[seq] + off;
+    const int n_rows = min(TC_BM, q_start[seq + 1] - tok0);
+    const int pos0 = start_pos[seq] + off;
+    const int pos_last = pos0 + n_rows - 1;
+    const int* bt = block_table + (size_t)slots[seq] * max_pages;
+    const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int kt_begin = key_lo / TC_BN, kt_end = pos_last / TC_BN + 1;
+    const int kv_hi = pos_last + 1;
+    const int n_my = (kt_end - kt_begin - wg + 1) / 2;                   // this warpgroup's tiles: every second one
+    auto my_kt = [&](int i) { return kt_begin + wg + 2 * i; };
+
+    const uint32_t mb_s = tc_smem(&s_mbar[wg][0]), mb_o = tc_smem(&s_mbar[wg][1]);
+    const uint32_t mb_k = tc_smem(&s_mbar[wg][2]);      // K0, K1, V0, V1 landed: four barriers, 8 bytes apart
+    if (tid == 0) {
+        for (int w = 0; w < 2; ++w)
+            for (int k = 0; k < 6; ++k) tc_mbar_init(tc_smem(&s_mbar[w][k]), 1);
+        tc_mbar_init_fence();
+        s_dead = 0;
+    }
+    if (tid < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(tc_smem(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    auto tile_addr = [](uint32_t tile, uint32_t blk_bytes, int r, int c) -> uint32_t {
+        return tile + (c >> 3) * blk_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+    };
+    if (!issuer) {   // the tile's queries: two threads per row (rows past the portion's end are zero)
+        const bool ok = row < n_rows;
+        const bf16* src = q + ((size_t)(tok0 + (ok ? row : 0)) * nh + h) * d;
+        for (int c = wg; c < d / 8; c += 2) tc_cp16(tile_addr(sQ, Q_BLK, row, c), src + c * 8, ok);
+        tc_cp_commit();
+        tc_cp_wait<0>();
+    }
+    tc_fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();                 // Q, the mbarriers, the TMEM address
+    tc_fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    const uint32_t t_wg = tmem + wg * WG_COLS;                               // S at +0, O at +64
+    volatile int* dead = &s_dead;
+
+    if (issuer) {
+        // ---- the issuing warp: lane 0 works, the other lanes only keep the named barriers' count
+        const bool lead = (tid & 31) == 0;
+        bool alive = true;
+        const uint32_t idesc_s = tc_idesc(TC_BM, TC_BN, 0, 0);
+        const uint32_t idesc_o = tc_idesc(TC_BM, d, 0, 1);
+        // barrier x of this warpgroup's four copy barriers (K0, K1, V0, V1): copies announced and awaited so far
+        int n_fetch[4] = {0, 0, 0, 0}, n_wait[4] = {0, 0, 0, 0};
+        // keys (which = 0) or values (1) of key tile kt -> buffer `buf`, page by page
+        auto fetch = [&](int kt, int which, int buf) {
+            const int x = which * 2 + buf;
+            const uint32_t dst = sK + x * BUF, mb = mb_k + 8 * x;
+            ++n_fetch[x];
+            const int k0 = kt * TC_BN;
+            const int pg_lo = max(k0, key_lo) / page_size, pg_hi = (min(k0 + TC_BN, kv_hi) - 1) / page_size;
+            tc_mbar_expect_tx(mb, BUF);
+            for (int pg = k0 / page_size; pg < (k0 + TC_BN) / page_size; ++pg) {
+                // A page without a key this query tile may see may have been given back: its part of the
+                // buffer (masked later) is filled from the tile's first live page instead, so that it holds
+                // finite numbers.  A hole in the table gives a coordinate outside the tensor: zeros.
+                const int page = bt[min(max(pg, pg_lo), pg_hi)];
+                const int c2 = page < 0 ? -1 : ((page * n_layers + layer) * 2 + which) * nkv + kvh;
+                const uint32_t o = (uint32_t)(pg * page_size - k0) * 128;
+#pragma unroll
+                for (int b = 0; b < DB; ++b) tc_tma_load_3d(dst + b * KV_BLK + o, &kv_map, b * 64, 0, c2, mb);
+            }
+        };
+        auto issue_s = [&](uint32_t kb) {
+#pragma unroll
+            for (int kk = 0; kk < d / 16; ++kk) {
+                const uint32_t o = (kk >> 2) * Q_BLK + (kk & 3) * 32, ob = (kk >> 2) * KV_BLK + (kk & 3) * 32;
+                tc_mma(t_wg, tc_desc(sQ + o, 16, 1024), tc_desc(kb + ob, 16, 1024), idesc_s, kk > 0);
+            }
+        };
+        auto landed = [&](int which, int buf) -> bool {       // the oldest copy into this buffer not yet awaited
+            const int x = which * 2 + buf;
+            const bool ok = tm_wait(mb_k + 8 * x, n_wait[x] & 1, dead);
+            if (ok) ++n_wait[x];
+            return ok;
+        };
+        if (lead && n_my > 0) {
+            fetch(my_kt(0), 0, 0);
+            if (n_my > 1) fetch(my_kt(1), 0, 1);
+            fetch(my_kt(0), 1, 0);
+            if (n_my > 1) fetch(my_kt(1), 1, 1);
+            if (landed(0, 0)) {
+                tc_fence_after_sync();
+                issue_s(sK);
+                tc_commit(mb_s);
+            } else alive = false;
+        }
+        for (int i = 0; i < n_my; ++i) {
+            const int b = i & 1;                              // tile i's buffers
+            __syncwarp();
+            tm_sync(wg, 0);          // S(i) is complete and in the softmax threads' registers
+            if (lead && alive && i + 1 < n_my) {
+                if (landed(0, b ^ 1)) {
+                    tc_fence_after_sync();
+                    issue_s(sK + (b ^ 1) * BUF);
+                    tc_commit(mb_s);
+                } else alive = false;
+                if (alive && i + 2 < n_my) fetch(my_kt(i + 2), 0, b);
+            }
+            __syncwarp();
+            tm_sync(wg, 1);          // P(i) is written; O += P V of tile i-1 has completed
+            if (lead && alive) {
+                if (i >= 1 && i + 1 < n_my) fetch(my_kt(i + 1), 1, b ^ 1);
+                if (landed(1, b)) {
+                    tc_fence_after_sync();
+                    const uint32_t vb = sV + b * BUF;
+#pragma unroll
+                    for (int jj = 0; jj < TC_BN / 16; ++jj)
+                        tc_mma(t_wg + 64, tc_desc(sP + jj * 32, 16, 1024), tc_desc(vb + jj * 2048, KV_BLK, 1024),
+                               idesc_o, i > 0 || jj > 0);
+                    tc_commit(mb_o);
+                } else alive = false;
+            }
+        }
+        if (lead && !alive) {
+            // the block is giving up: copies still in flight must land before its shared memory goes away
+            for (int x = 0; x < 4; ++x)
+                while (n_wait[x] < n_fetch[x] && tc_wait(mb_k + 8 * x, n_wait[x] & 1)) ++n_wait[x];
+        }
+        __syncwarp();
+    }
+
+    // ---- softmax threads: thread `row` of the warpgroup owns query row `row` = TMEM lane `row`
+    const uint32_t t_row = t_wg + ((uint32_t)(warp4 * 32) << 16);
+    float m_ref = -INFINITY, l_run = 0.f;       // reference maximum (scaled, log2 domain) and running sum
+    bool alive = true;
+    if (!issuer) {
+        const int pos = row < n_rows ? pos0 + row : -1;
+        const int lo = window > 0 ? pos - window + 1 : 0;
+        uint32_t ph_s = 0, ph_o = 0;
+        for (int i = 0; i < n_my; ++i) {
+            const int kt = my_kt(i);
+            if (alive && !tm_wait(mb_s, ph_s, dead)) alive = false;
+            ph_s ^= 1;
+            tc_fence_after_sync();
+            float s[TC_BN];
+            tc_ld32(t_row, s);              // S: columns 0..63 of this thread's lane
+            tc_ld32(t_row + 32, s + 32);
+            tc_ld_wait();
+            tc_fence_before_sync();
+            tm_arrive(wg, 0);
+            const bool need_mask = kt * TC_BN + TC_BN - 1 > pos || (window > 0 && kt * TC_BN < lo);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < TC_BN; ++c) {
+                    const int key = kt * TC_BN + c;
+                    if (key > pos || key < lo) s[c] = -INFINITY;
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64
+#pragma unroll
+            for (int c = 0; c < TC_BN; c += 4) {
+                mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float m_new = fmaxf(m_ref, mx * scale_log2);
+            // move the reference only when the maximum grew by more than 2^8 (or from "no key yet")
+            const bool move = m_new > m_ref + 8.f;
+            if (i > 0) {     // O += P V of tile i-1: O may be rescaled and P overwritten after it
+                if (alive && !tm_wait(mb_o, ph_o, dead)) alive = false;
+                ph_o ^= 1;
+                tc_fence_after_sync();
+            }
+            if (__any_sync(0xffffffffu, move) && i > 0) {
+                // rescale this row of O in tensor memory (every lane of the warp takes part; a lane that
+                // does not move multiplies by one)
+                const float corr = move ? tc_exp2(m_ref - m_new) : 1.f;
+#pragma unroll
+                for (int cb = 0; cb < DB * 2; ++cb) {
+                    float ov[32];
+                    tc_ld32(t_row + 64 + cb * 32, ov);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) ov[k] *= corr;
+                    tc_st32(t_row + 64 + cb * 32, ov);
+                }
+                tc_st_wait();
+                l_run *= corr;
+            }
+            if (move) m_ref = m_new;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t prow = sP + row * 128;
+#pragma unroll
+            for (int c8 = 0; c8 < TC_BN / 8; ++c8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = tc_exp2(fmaf(s[c8 * 8 + 2 * e], scale_log2, -m_use));
+                    const float p1 = tc_exp2(fmaf(s[c8 * 8 + 2 * e + 1], scale_log2, -m_use));
+                    rs4[e] += p0 + p1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    w[e] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n"
+                             ::"r"(prow + ((c8 ^ (row & 7)) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            tc_fence_async_smem();
+            tc_fence_before_sync();
+            tm_arrive(wg, 1);
+        }
+        if (n_my > 0) {
+            if (alive && !tm_wait(mb_o, ph_o, dead)) alive = false;
+            tc_fence_after_sync();
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (s_dead) {
+        alive = false;
+        if (tid == 0) atomicExch(status, 3);
+    }
+    // ---- merge the two warpgroups: the second leaves (max, sum, O row) in shared memory (every product
+    // and copy has completed, so the tiles' space is free: (2 + head_dim) x 128 floats from its start)
+    float* mrg = reinterpret_cast<float*>(tm_raw + (base - tc_smem(tm_raw)));
+    const float m_fin = n_my > 0 ? m_ref : -INFINITY;
+    if (alive && !issuer && wg == 1) {
+        mrg[row] = m_fin;
+        mrg[128 + row] = l_run;
+#pragma unroll
+        for (int cb = 0; cb < DB * 2; ++cb) {
+            float ov[32];
+            if (n_my > 0) { tc_ld32(t_row + 64 + cb * 32, ov); tc_ld_wait(); }
+#pragma unroll
+            for (int k = 0; k < 32; ++k) mrg[(2 + cb * 32 + k) * 128 + row] = n_my > 0 ? ov[k] : 0.f;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (alive && !issuer && wg == 0) {   // warp-uniform: tcgen05.ld needs whole warps; only the store looks at the row
+        const float m1 = mrg[row], l1 = mrg[128 + row];
+        const float m = fmaxf(m_fin, m1);
+        const float a0 = m_fin == -INFINITY ? 0.f : tc_exp2(m_fin - m), a1 = m1 == -INFINITY ? 0.f : tc_exp2(m1 - m);
+        const float l = l_run * a0 + l1 * a1;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* orow = out + ((size_t)(tok0 + row) * nh + h) * d;
+#pragma unroll
+        for (int cb = 0; cb < DB * 2; ++cb) {
+            float ov[32];
+            tc_ld32(t_row + 64 + cb * 32, ov);       // warpgroup 0 always has a tile (the first one)
+            tc_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (row >= n_rows) continue;
+                float r[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) r[k] = (ov[c * 8 + k] * a0 + mrg[(2 + cb * 32 + c * 8 + k) * 128 + row] * a1) * inv;
+                uint4 w;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(r[0], r[1]), p1 = __floats2bfloat162_rn(r[2], r[3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(r[4], r[5]), p3 = __floats2bfloat162_rn(r[6], r[7]);
+                w.x = *reinterpret_cast<uint32_t*>(&p0); w.y = *reinterpret_cast<uint32_t*>(&p1);
+                w.z = *reinterpret_cast<uint32_t*>(&p2); w.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(orow + cb * 32 + c * 8) = w;
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid < 32) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side: the pool's tensor map (encoded once per pool and geometry) ---------------------------
+typedef CUresult (*tm_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct TmMapKey {
+    const void* pool;
+    long long rows;
+    int page_size, d;
+};
+struct TmMapEntry {
+    TmMapKey key;
+    CUtensorMap map;
+};
+static std::mutex tm_mutex;
+static TmMapEntry tm_maps[16];
+static int tm_n_maps = 0, tm_next = 0;
+static tm_encode_fn tm_encode = nullptr;
+static bool tm_encode_looked_up = false;
+
+// the driver's cuTensorMapEncodeTiled, found through the runtime (the library does not link libcuda)
+static tm_encode_fn tm_get_encode() {
+    if (!tm_encode_looked_up) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            tm_encode = (tm_encode_fn)fn;
+        else
+            (void)cudaGetLastError();
+        tm_encode_looked_up = true;
+    }
+    return tm_encode;
+}
+
+// rows: pages x layers x 2 x kv_heads, each [page_size][d] bfloat16
+static int tm_pool_map(const void* pool, long long rows, int page_size, int d, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(tm_mutex);
+    for (int i = 0; i < tm_n_maps; ++i) {
+        const TmMapKey& k = tm_maps[i].key;
+        if (k.pool == pool && k.rows == rows && k.page_size == page_size && k.d == d) {
+            *out = tm_maps[i].map;
+            return 0;
+        }
+    }
+    tm_encode_fn enc = tm_get_encode();
+    if (!enc) return ST_ERR_BAD_ARG;
+    const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)page_size * d * 2};       // bytes, dims 1 and 2
+    const cuuint32_t box[3] = {64, (cuuint32_t)page_size, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ST_ERR_BAD_ARG;
+    TmMapEntry& e = tm_maps[tm_next];
+    e.key = TmMapKey{pool, rows, page_size, d};
+    e.map = m;
+    tm_next = (tm_next + 1) % 16;
+    if (tm_n_maps < 16) ++tm_n_maps;
+    *out = m;
+    return 0;
+}
+
+static size_t tm_smem_bytes(int db) {
+    // Q, then per warpgroup two key and two value tiles and P; a kilobyte of slack to reach a 1024-byte boundary
+    return (size_t)db * TC_BM * 128 + 2 * ((size_t)4 * db * TC_BN * 128 + TC_BM * 128) + 1024;
+}
+
+template <int DB>
+static int launch_prefill_tma(const CUtensorMap& map, const void* q, void* out, const int* tiles, int n_tiles,
+                              const int* q_start, const int* start_pos, const int* slots, const int* block_table,
+                              int max_pages, int n_layers, int layer, int nh, int nkv, int page_size, float scale,
+                              int window, int* status, cudaStream_t s) {
+    const size_t smem = tm_smem_bytes(DB);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tma_kernel<DB>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(n_tiles, nh);
+    attention_prefill_tma_kernel<DB><<<grid, TM_THREADS, smem, s>>>(map, (const bf16*)q, (bf16*)out, tiles, q_start,
+        start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, page_size, scale * TC_LOG2E, window, status);
+    return st_launch_status();
+}
+
+// 1 if the TMA-fed kernel takes this head size and page size
+ST_EXPORT int st_attention_prefill_tma_applies(int d, int page_size) {
+    return (d == 64 || d == 128) && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+// Same arguments as st_attention_prefill_tc plus the number of pages in the pool (the tensor map covers the
+// whole pool).  `status` is set to 3 if a wait expired.
+ST_EXPORT int st_attention_prefill_tma(const void* q, const void* pool, long long n_pages, void* out, const int* tiles,
+                                       int n_tiles, const int* q_start, const int* start_pos, const int* slots,
+                                       const int* block_table, int max_pages, int n_layers, int layer, int nh,
+                                       int nkv, int d, int page_size, float scale, int window, int* status,
+                                       void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || nh > 65535 || n_pages <= 0 || !status) return ST_ERR_BAD_ARG;
+    if (!st_attention_prefill_tma_applies(d, page_size)) return ST_ERR_BAD_SIZE;
+    const long long rows = n_pages * n_layers * 2 * nkv;
+    if (rows >= (1ll << 31)) return ST_ERR_TOO_LARGE;          // TMA coordinates are 32-bit
+    if ((reinterpret_cast<uintptr_t>(pool) & 15) != 0) return ST_ERR_BAD_ARG;
+    CUtensorMap map;
+    int r = tm_pool_map(pool, rows, page_size, d, &map);
+    if (r) return r;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64)
+        return launch_prefill_tma<1>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
+                                     n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+    return launch_prefill_tma<2>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
+                                 n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+}

@@ -158,10 +158,20 @@ def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, count: 
 
 
 # ------------------------------------------------------------ matrix products
+def lossless_bf16(v: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """A bfloat16 copy of a float vector if every element survives the rounding unchanged, else None."""
+    if v is None or v.dtype != torch.float32:
+        return None
+    low = v.to(torch.bfloat16)
+    return low if bool(torch.equal(low.float(), v)) else None
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, bias_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(a @ w.T + bias); w is [out, in].  float32: the plain fused-multiply-add kernel (true 32-bit).
-    bfloat16: cuBLAS with float accumulation, then the bias/activation kernel."""
+    bfloat16, few rows: the weight-streaming kernel.  bfloat16, more rows: the library product with float
+    accumulation; bias and ReLU ride in its epilogue when ``bias_bf16`` (a lossless bfloat16 copy of
+    ``bias``, see lossless_bf16) is given, else the bias/activation kernel follows."""
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1] and a.dtype == w.dtype
     out_dtype = out_dtype or a.dtype
     n, m = a.shape[0], w.shape[0]
@@ -175,6 +185,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return gemm_skinny(a, w, bias, act, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(a, w.t(), out_dtype=torch.float32)
+    elif bias_bf16 is not None and act in ("none", "relu"):
+        if act == "relu":
+            return torch._addmm_activation(bias_bf16, a, w.t(), use_gelu=False)
+        return torch.addmm(bias_bf16, a, w.t())
     else:
         y = torch.mm(a, w.t())
     return bias_act(y, bias, act)
@@ -323,13 +337,25 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
     """bfloat16 tensor-core paged attention over tiles of 128 query tokens; tiles: int32 [n_tiles, 2] =
     (request index in the step, offset of the tile among the request's new tokens).
 
-    kernel: "tc" = the tcgen05 kernel (head sizes up to 128), "mma" = the mma.sync kernel (up to 256),
-    "auto" = tcgen05 where it applies.  ``status`` receives 3 if the tcgen05 kernel gave up waiting."""
-    _, n_layers, _, nkv, page_size, d = pool.shape
+    kernel: "tma" = the tcgen05 kernel fed by TMA (head sizes 64 and 128, pages of 8 to 64 positions),
+    "tc" = the tcgen05 kernel fed by asynchronous copies (head sizes up to 128), "mma" = the mma.sync
+    kernel (up to 256), "auto" = the first of these that applies.  ``status`` receives 3 if a tcgen05
+    kernel gave up waiting."""
+    n_pages, n_layers, _, nkv, page_size, d = pool.shape
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill is a bfloat16 kernel")
     if kernel == "auto":
-        kernel = "tc" if d <= 128 else "mma"
+        if lib().st_attention_prefill_tma_applies(d, page_size):
+            kernel = "tma"
+        else:
+            kernel = "tc" if d <= 128 else "mma"
+    if kernel == "tma":
+        st = status if status is not None else _tc_status_word(q.device)
+        _check(lib().st_attention_prefill_tma(_p(q), _p(pool), ctypes.c_longlong(n_pages), _p(out), _p(tiles),
+                                              n_tiles, _p(q_start), _p(start_pos), _p(slots), _p(block_table),
+                                              block_table.shape[1], n_layers, layer, nh, nkv, d, page_size,
+                                              _f(scale), window, _p(st), _stream()), "attention_prefill_tma")
+        return out
     if kernel == "tc":
         st = status if status is not None else _tc_status_word(q.device)
         _check(lib().st_attention_prefill_tc(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start),
@@ -337,6 +363,8 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
                                              n_layers, layer, nh, nkv, d, page_size, _f(scale), window, _p(st),
                                              _stream()), "attention_prefill_tc")
         return out
+    if kernel != "mma":
+        raise KernelError(f"attention_prefill: no kernel named {kernel!r}")
     _check(lib().st_attention_prefill(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start), _p(start_pos),
                                       _p(slots), _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv,
                                       d, page_size, _f(scale), window, _stream()), "attention_prefill")

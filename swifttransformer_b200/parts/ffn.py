@@ -22,7 +22,7 @@ class DenseFFN(FeedForward):
             raise ValueError(f"activation '{activation}' is not supported ({', '.join(ops.ACT_CODES)})")
         self.hidden, self.inner, self.activation, self.bias = hidden, inner, activation, bias
         self.fc1_name, self.fc2_name = fc1_name, fc2_name
-        self.w1 = self.b1 = self.w2 = self.b2 = None
+        self.w1 = self.b1 = self.w2 = self.b2 = self.b1_bf16 = None
 
     def param_specs(self) -> List[ParamSpec]:
         specs = [ParamSpec(self.fc1_name + ".weight", (self.inner, self.hidden), MATRIX),
@@ -36,9 +36,12 @@ class DenseFFN(FeedForward):
         self.w1, self.w2 = tensors[self.fc1_name + ".weight"], tensors[self.fc2_name + ".weight"]
         if self.bias:
             self.b1, self.b2 = tensors[self.fc1_name + ".bias"], tensors[self.fc2_name + ".bias"]
+            if self.w1.dtype == torch.bfloat16:
+                # lets the library product add the bias (and apply ReLU) in its epilogue
+                self.b1_bf16 = ops.lossless_bf16(self.b1)
 
     def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
-        u = ops.linear(h, self.w1, self.b1, self.activation)
+        u = ops.linear(h, self.w1, self.b1, self.activation, bias_bf16=self.b1_bf16)
         return Delta(ops.linear(u, self.w2), self.b2)
 
     def param_bytes(self) -> int:

@@ -181,6 +181,7 @@ def attention_case(dtype, nh, nkv, d, ps, lens, new, seed, window=0):
 
 ATT_SHAPES = [  # nh, nkv, d, page_size
     (4, 4, 16, 8), (3, 3, 32, 16), (5, 5, 48, 32), (6, 2, 64, 16), (2, 1, 80, 4), (4, 4, 128, 16), (2, 2, 256, 64),
+    (3, 1, 64, 8), (2, 2, 128, 64), (5, 5, 64, 32),
 ]
 
 
@@ -217,11 +218,13 @@ def test_attention_decode(shape, window, n_splits):
 
 @pytest.mark.parametrize("shape", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
-@pytest.mark.parametrize("kernel", ["tc", "mma"])
+@pytest.mark.parametrize("kernel", ["tma", "tc", "mma"])
 def test_attention_prefill(shape, window, kernel):
     nh, nkv, d, ps = shape
     if kernel == "tc" and d > 128:
         pytest.skip("the tcgen05 kernel takes head sizes up to 128")
+    if kernel == "tma" and not (d in (64, 128) and ps in (8, 16, 32, 64)):
+        pytest.skip("the TMA-fed kernel takes head sizes 64 and 128 and pages of 8 to 64 positions")
     dtype = torch.bfloat16
     lens, new = [150, 200, 300, 64, 17, 400], [150, 70, 16, 64, 17, 300]
     pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 50, window)
