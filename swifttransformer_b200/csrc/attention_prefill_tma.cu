@@ -292,11 +292,11 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                     if (key > pos || key < lo) s[c] = -INFINITY;
                 }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains of three-input maxima
 #pragma unroll
-            for (int c = 0; c < TC_BN; c += 4) {
-                mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
-                mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            for (int c = 0; c < TC_BN; c += 8) {
+                mx4[0] = tc_max3(mx4[0], s[c], s[c + 1]); mx4[1] = tc_max3(mx4[1], s[c + 2], s[c + 3]);
+                mx4[2] = tc_max3(mx4[2], s[c + 4], s[c + 5]); mx4[3] = tc_max3(mx4[3], s[c + 6], s[c + 7]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m_ref, mx * scale_log2);
@@ -307,13 +307,15 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             // P = exp2(S - reference) as packed bfloat16, still in registers: this runs while O += P V of
             // the previous tile is still on the tensor cores
-            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+            float rs8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};      // four chains of pairwise sums
             uint32_t w[TC_BN / 2];
+            const float neg_m = -m_use;
 #pragma unroll
             for (int c2 = 0; c2 < TC_BN / 2; ++c2) {
-                const float p0 = tc_exp2(fmaf(s[2 * c2], scale_log2, -m_use));
-                const float p1 = tc_exp2(fmaf(s[2 * c2 + 1], scale_log2, -m_use));
-                rs4[c2 & 3] += p0 + p1;
+                float a0, a1;
+                tc_fma2(a0, a1, s[2 * c2], s[2 * c2 + 1], scale_log2, neg_m);
+                const float p0 = tc_exp2(a0), p1 = tc_exp2(a1);
+                tc_add2(rs8[2 * (c2 & 3)], rs8[2 * (c2 & 3) + 1], p0, p1);
                 __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                 w[c2] = *reinterpret_cast<uint32_t*>(&pk);
             }
@@ -346,7 +348,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n"
                              ::"r"(prow + ((c8 ^ (row & 7)) << 4)), "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]),
                                "r"(w[4 * c8 + 3]) : "memory");
-            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            l_run += ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
             tc_fence_async_smem();
             tc_fence_before_sync();
             tm_arrive(wg, 1);

@@ -30,6 +30,23 @@ __device__ __forceinline__ float tc_exp2(float x) {
     return y;
 }
 
+// sm_100 arithmetic on pairs of floats and the three-input maximum: fewer instructions for the softmax threads
+__device__ __forceinline__ void tc_fma2(float& d0, float& d1, float a0, float a1, float b, float c) {   // a * b + c
+    asm("{\n\t.reg .b64 a, b, c, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tmov.b64 c, {%5, %5};\n\t"
+        "fma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}\n"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void tc_add2(float& d0, float& d1, float a0, float a1) {                      // d += a
+    asm("{\n\t.reg .b64 a, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 d, {%0, %1};\n\t"
+        "add.rn.f32x2 d, d, a;\n\tmov.b64 {%0, %1}, d;\n\t}\n"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float tc_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // shared-memory matrix descriptor: 128-byte swizzle, descriptor version 1 (sm_100)
 __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
