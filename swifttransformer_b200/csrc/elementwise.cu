@@ -260,6 +260,22 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[idx[i]] = val[i];
 }
 
+// dst[i] = src[from[i]] where from[i] >= 0: tokens that the previous step sampled become this step's
+// inputs without a trip through the host.
+__global__ void gather_where_i32_kernel(int* __restrict__ dst, const int* __restrict__ from,
+                                        const int* __restrict__ src, int n, int n_src) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int f = from[i];
+    if (f >= 0 && f < n_src) dst[i] = src[f];
+}
+
+ST_EXPORT int st_gather_where_i32(int* dst, const int* from, const int* src, int n, int n_src, void* stream) {
+    if (n <= 0) return 0;
+    gather_where_i32_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(dst, from, src, n, n_src);
+    return st_launch_status();
+}
+
 ST_EXPORT int st_scatter_i32(int* dst, const int* idx, const int* val, const int* count, int max_count, void* stream) {
     if (max_count <= 0) return 0;
     int grid = (max_count + 255) / 256;

@@ -21,7 +21,7 @@ from ..cache.manager import CacheManager
 from ..models.base import CausalLM
 from ..models.registry import load_model
 from ..sampling.sampler import Sampler, SamplingParams
-from .scheduler import Request, Scheduled, Scheduler
+from .scheduler import PENDING, Request, Scheduled, Scheduler
 from .step import ModelRunner, StepEntry
 
 
@@ -34,6 +34,29 @@ class EngineConfig:
     chunk_size: int = 512               # longest prompt portion
     max_num_seqs: int = 256             # most requests running at a time
     use_cuda_graphs: bool = True        # record decode-only steps once per batch size and replay them
+    # launch the next step before the tokens of this one have been read: they reach it on the device, and
+    # the host's work for a step (scheduling, staging, the read itself) overlaps the GPU's
+    pipeline: bool = True
+
+
+class _Launched:
+    """A step that is on the GPU: its plan and where its sampled tokens are."""
+
+    def __init__(self, plan: List[Scheduled]):
+        self.plan = plan
+        self.n_samples = 0
+        self.sampled: Optional[torch.Tensor] = None      # int32 on the device
+        self.host: Optional[torch.Tensor] = None         # its copy in pinned memory, valid after `event`
+        self.event = None
+        self.sample_index: Dict[int, int] = {}           # id(request) -> row of `sampled`
+
+    def fetch(self) -> List[int]:
+        if self.n_samples == 0:
+            return []
+        if self.event is not None:
+            self.event.synchronize()
+            return self.host[:self.n_samples].tolist()
+        return self.sampled.tolist()
 
 
 class LLMEngine:
@@ -58,6 +81,12 @@ class LLMEngine:
         self._ids = itertools.count()
         self.requests: Dict[Any, Request] = {}
         self.stats = dict(steps=0, prompt_tokens=0, decode_tokens=0)
+        self._inflight: Optional[_Launched] = None
+        # sampled tokens come back through pinned buffers used in turn (a step's buffer is read before
+        # the step after next is launched)
+        pin = self.device.type == "cuda"
+        self._token_bufs = [torch.zeros(cfg.max_num_seqs, dtype=torch.int32, pin_memory=pin) for _ in range(3)]
+        self._token_turn = 0
 
     def _pages_that_fit(self, specs, cfg: EngineConfig, max_len: int) -> int:
         from ..parts.base import PagedKVSpec
@@ -89,30 +118,73 @@ class LLMEngine:
         return rid
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ---------------------------------------------------------------- step
-    def step(self) -> List[Request]:
-        """One scheduler decision through the GPU; returns the requests that finished in it."""
-        plan = self.scheduler.schedule()
-        if not plan:
-            return self._drain_finished([])
+    def _launch(self, plan: List[Scheduled], prev: Optional[_Launched]) -> _Launched:
+        """Put one scheduler decision on the GPU (step and sampling); nothing here waits for the GPU.
+        Tokens that are still PENDING are taken on the device from ``prev``, the step that drew them."""
+        out = _Launched(plan)
         entries, samplers, counters = [], [], []
+        token_from: List[int] = []
         for s in plan:
             r = s.request
             toks = r.tokens[r.n_computed:r.n_computed + s.n]
+            for j, t in enumerate(toks):
+                if t == PENDING:
+                    if prev is None or id(r) not in prev.sample_index:
+                        raise RuntimeError("a token that was never drawn is waited for")
+                    token_from.append(prev.sample_index[id(r)])
+                    toks[j] = 0
+                else:
+                    token_from.append(-1)
             entries.append(StepEntry(r.slot, toks, r.n_computed, [s.n - 1] if s.samples else []))
             if s.samples:
+                out.sample_index[id(r)] = len(samplers)
                 samplers.append(r.params)
                 counters.append(len(r.output))
             if s.n == 1 and r.n_computed >= len(r.prompt):
                 self.stats["decode_tokens"] += 1
             else:
                 self.stats["prompt_tokens"] += s.n
-        logits = self.runner.step(entries)
-        sampled = self.sampler.sample(logits, samplers, counters) if samplers else []
+        feedback = (prev.sampled, token_from) if prev is not None and any(f >= 0 for f in token_from) else None
+        logits = self.runner.step(entries, feedback)
         self.stats["steps"] += 1
-        return self._drain_finished(self.scheduler.update(plan, sampled))
+        if samplers:
+            out.n_samples = len(samplers)
+            out.sampled = self.sampler.sample_on_device(logits, samplers, counters)
+            if self.device.type == "cuda":
+                self._token_turn = (self._token_turn + 1) % len(self._token_bufs)
+                out.host = self._token_bufs[self._token_turn]
+                out.host[:out.n_samples].copy_(out.sampled, non_blocking=True)
+                out.event = torch.cuda.Event()
+                out.event.record()
+        return out
+
+    def step(self) -> List[Request]:
+        """One scheduler decision through the GPU; returns the requests that finished in it.
+
+        With ``pipeline`` the step after this one is decided and launched before this one's tokens are
+        read (requests continue from PENDING tokens that the GPU fills in): a request that ends on an
+        end-of-sequence token is then reported one call later than it was computed, and the token the
+        step ahead computed for it is dropped."""
+        cur, self._inflight = self._inflight, None
+        if cur is None:
+            plan = self.scheduler.schedule()
+            if not plan:
+                return self._drain_finished([])
+            cur = self._launch(plan, None)
+        if cur.n_samples == 0:
+            return self._drain_finished(self.scheduler.update(cur.plan, []))
+        if not self.config.pipeline:
+            return self._drain_finished(self.scheduler.update(cur.plan, cur.fetch()))
+        done, handles = self.scheduler.update_pending(cur.plan)
+        if self.scheduler.has_work():
+            ahead = self.scheduler.schedule()
+            if ahead:
+                self._inflight = self._launch(ahead, cur)
+        done += self.scheduler.resolve(handles, cur.fetch())
+        return self._drain_finished(done)
 
     def _drain_finished(self, done: List[Request]) -> List[Request]:
         # requests the scheduler gave up on (cache_full) finish without a step of their own

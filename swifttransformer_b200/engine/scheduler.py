@@ -28,6 +28,7 @@ from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
 from ..sampling.sampler import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1      # stands in a request's output for a token that has been drawn on the GPU but not read yet
 
 
 @dataclasses.dataclass
@@ -206,6 +207,11 @@ class Scheduler:
         for s in plan:
             req = s.request
             draws = s.samples
+            if req.state == FINISHED:
+                # it ended (on a token read later than this step was launched) while the step ran:
+                # what the step computed for it is dropped
+                k += 1 if draws else 0
+                continue
             req.n_computed += s.n
             if not draws:
                 continue
@@ -214,7 +220,7 @@ class Scheduler:
             req.output.append(tok)
             p = req.params
             reason = None
-            if p.eos_id is not None and tok == p.eos_id and not p.ignore_eos:
+            if tok != PENDING and p.eos_id is not None and tok == p.eos_id and not p.ignore_eos:
                 reason = "eos"
             elif len(req.output) >= p.max_new_tokens:
                 reason = "length"
@@ -225,4 +231,45 @@ class Scheduler:
                 done.append(req)
         if k != len(sampled):
             raise ValueError("the number of sampled tokens does not match the plan")
+        return done
+
+    # ------------------------------------- the same in two halves, for steps launched ahead of their tokens
+    def update_pending(self, plan: Sequence[Scheduled]) -> Tuple[List[Request], List[Optional[Tuple[Request, int]]]]:
+        """Account for a step whose sampled tokens are still on the GPU: every drawing request gets a
+        PENDING token (so the next step can be decided and launched) and may finish by length.  Returns
+        the finished requests and, per drawn token in plan order, (request, index of the token in its
+        output), or None where the step's result is dropped; ``resolve`` takes that list."""
+        handles: List[Optional[Tuple[Request, int]]] = []
+        n = 0
+        for s in plan:
+            if s.samples:
+                n += 1
+                handles.append(None if s.request.state == FINISHED else (s.request, len(s.request.output)))
+        return self.update(plan, [PENDING] * n), handles
+
+    def resolve(self, handles: Sequence[Optional[Tuple[Request, int]]], sampled: Sequence[int]) -> List[Request]:
+        """Put the tokens of a step accounted for by ``update_pending`` in their places; a request whose
+        token is its end-of-sequence token finishes now, and what a later step computed for it is
+        dropped.  Returns the requests that finished here."""
+        if len(handles) != len(sampled):
+            raise ValueError("the number of sampled tokens does not match the plan")
+        done: List[Request] = []
+        for h, tok in zip(handles, sampled):
+            if h is None:
+                continue
+            req, idx = h
+            tok = int(tok)
+            req.output[idx] = tok
+            p = req.params
+            if p.eos_id is None or tok != p.eos_id or p.ignore_eos:
+                continue
+            if req.state == FINISHED:
+                req.finish_reason = "eos"        # it also was its last token by length
+                continue
+            del req.output[idx + 1:]
+            if req.state == WAITING:             # preempted meanwhile
+                self.waiting.remove(req)
+            req.n_computed = min(req.n_computed, req.n_tokens)
+            self._finish(req, "eos")
+            done.append(req)
         return done

@@ -135,7 +135,7 @@ class _DecodeGraph:
 
     def __init__(self, runner: "ModelRunner", cap: int):
         self.runner, self.cap = runner, cap
-        self.staging = _Staging(5 * cap, runner.device)
+        self.staging = _Staging(6 * cap, runner.device)
         dev = runner.device
         ar = torch.arange(cap + 1, dtype=torch.int32, device=dev)
         d = self.staging.dev
@@ -143,6 +143,7 @@ class _DecodeGraph:
         ctx.n_tokens = ctx.n_seqs = ctx.n_want = cap
         ctx.token_ids, ctx.positions = d[0:cap], d[cap:2 * cap]
         ctx.start_pos, ctx.kv_len, ctx.slots = d[2 * cap:3 * cap], d[3 * cap:4 * cap], d[4 * cap:5 * cap]
+        self.token_from = d[5 * cap:6 * cap]     # per token: index into the previous step's sampled tokens, or -1
         ctx.seq_of_token, ctx.q_start, ctx.want_rows = ar[:cap], ar, ar[:cap]
         ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, dev
         ctx._plan = AttentionPlan(None, cap, None, 0, runner.cache.max_seq_len)
@@ -162,7 +163,7 @@ class _DecodeGraph:
             self._scratch_buf = torch.empty(max(n, 1), dtype=torch.float32, device=self.runner.device)
         return self._scratch_buf
 
-    def fill(self, entries: Sequence[StepEntry]) -> None:
+    def fill(self, entries: Sequence[StepEntry], token_from: Optional[Sequence[int]] = None) -> None:
         cap, b = self.cap, len(entries)
         h = self.staging.begin()
         h[0:cap] = 0
@@ -174,7 +175,12 @@ class _DecodeGraph:
             h[2 * cap + i] = e.start_pos
             h[3 * cap + i] = e.start_pos + 1
             h[4 * cap + i] = e.slot
-        self.staging.commit(5 * cap)
+        if token_from is not None:
+            h[5 * cap:6 * cap] = -1
+            h[5 * cap:5 * cap + b] = token_from
+            self.staging.commit(6 * cap)
+        else:
+            self.staging.commit(5 * cap)
 
     def record(self) -> None:
         r = self.runner
@@ -199,10 +205,12 @@ class _DecodeGraph:
         self.kernels = ops.launch_count() - before
         self.graph = g
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        self.fill(entries)
+    def run(self, entries: Sequence[StepEntry], feedback=None) -> torch.Tensor:
+        self.fill(entries, feedback[1] if feedback else None)
         if self.graph is None:
             self.record()
+        if feedback:
+            ops.gather_where_i32(self.ctx.token_ids, self.token_from, feedback[0])
         self.graph.replay()
         return self.logits[:len(entries)]
 
@@ -242,7 +250,7 @@ class ModelRunner:
         lay: Dict[str, Any] = {}
         for name, n in (("token_ids", n_cap), ("positions", n_cap), ("seq_of_token", n_cap),
                         ("q_start", b_cap + 1), ("start_pos", b_cap), ("kv_len", b_cap), ("slots", b_cap),
-                        ("want_rows", w_cap), ("items", n_cap),
+                        ("want_rows", w_cap), ("items", n_cap), ("token_from", n_cap),
                         ("tiles", 2 * ((n_cap + self.tile_rows - 1) // self.tile_rows + b_cap))):
             lay[name] = (off, n)
             off += n
@@ -285,12 +293,18 @@ class ModelRunner:
         if len(entries) > self.max_seqs:
             raise StepError(f"{len(entries)} requests in one step exceed the limit of {self.max_seqs}")
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], feedback=None) -> Optional[torch.Tensor]:
         """Run one step; returns float32 logits [number of wanted places, vocab] (None if none wanted).
 
         The returned tensor may be overwritten by the next step: use it (sample from it, copy it) first.
+
+        ``feedback`` = (int32 device tensor of tokens an earlier step sampled, one index into it per token
+        of this step or -1): those tokens are taken from the device, whatever the entries say in their
+        place, so that a step can be launched before the host has seen the tokens it continues from.
         """
         self.validate(entries)
+        if feedback is not None and len(feedback[1]) != sum(len(e.tokens) for e in entries):
+            raise StepError("feedback needs one source index per token of the step")
         # pages for all entries together, or none
         for g in self.cache.groups:
             need = sum(len(g.missing(e.slot, e.start_pos, e.start_pos + len(e.tokens))) for e in entries)
@@ -306,11 +320,11 @@ class ModelRunner:
             if bucket not in self._graphs:
                 self._graphs[bucket] = _DecodeGraph(self, bucket)
             dg = self._graphs[bucket]
-            logits = dg.run(entries)
+            logits = dg.run(entries, feedback)
             self.graph_steps += 1
             self.kernels_last_step = dg.kernels
         else:
-            ctx = self._build_context(entries)
+            ctx = self._build_context(entries, feedback)
             logits = self.model.forward(ctx, self._entries)
             self.kernels_last_step = ops.launch_count() - before
         for e in entries:
@@ -355,7 +369,7 @@ class ModelRunner:
                 d = self._upd_staging.dev
                 ops.scatter_i32(g.block_table, d[1:1 + n], d[1 + n:1 + 2 * n], d[0:1], n)
 
-    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], feedback=None) -> StepContext:
         B = len(entries)
         lens = [len(e.tokens) for e in entries]
         N = sum(lens)
@@ -402,8 +416,14 @@ class ModelRunner:
         tiles.sort(reverse=True)
         put("items", items)
         put("tiles", [v for t in tiles for v in (t[1], t[2])])
+        if feedback is not None:
+            put("token_from", list(feedback[1]))
         self._staging.commit(lay["total"])
         dev = self._staging.dev
+        if feedback is not None:
+            o, _ = lay["token_from"]
+            t0, _ = lay["token_ids"]
+            ops.gather_where_i32(dev[t0:t0 + N], dev[o:o + N], feedback[0])
 
         def view(name):
             o, n = lay[name]

@@ -157,6 +157,13 @@ def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor, count: 
     _check(lib().st_scatter_i32(_p(dst), _p(idx), _p(val), _p(count), max_count, _stream()), "scatter_i32")
 
 
+def gather_where_i32(dst: torch.Tensor, src_index: torch.Tensor, src: torch.Tensor) -> None:
+    """dst[i] = src[src_index[i]] wherever src_index[i] >= 0 (int32 tensors on the device)."""
+    assert dst.dtype == src.dtype == src_index.dtype == torch.int32 and dst.numel() == src_index.numel()
+    _check(lib().st_gather_where_i32(_p(dst), _p(src_index), _p(src), dst.numel(), src.numel(), _stream()),
+           "gather_where_i32")
+
+
 # ------------------------------------------------------------ matrix products
 def lossless_bf16(v: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """A bfloat16 copy of a float vector if every element survives the rounding unchanged, else None."""

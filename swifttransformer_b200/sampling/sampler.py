@@ -43,12 +43,17 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> List[int]:
         """One token per row of ``logits``; ``counters[r]`` is the index of the output token being drawn."""
+        return self.sample_on_device(logits, params, counters).tolist()
+
+    def sample_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                         counters: Sequence[int]) -> torch.Tensor:
+        """The same, left on the device as int32 [rows]: nothing waits for the GPU."""
         if logits.shape[0] != len(params):
             raise ValueError("one set of sampling parameters per row of logits")
         if all(p.temperature <= 0 for p in params):
-            return ops.argmax(logits).tolist()
+            return ops.argmax(logits)
         temps = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=self.device)
         topk = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=self.device)
         seeds = torch.tensor([p.seed for p in params], dtype=torch.int64, device=self.device)
         ctrs = torch.tensor(list(counters), dtype=torch.int64, device=self.device)
-        return ops.sample(logits, temps, topk, seeds, ctrs).tolist()
+        return ops.sample(logits, temps, topk, seeds, ctrs)

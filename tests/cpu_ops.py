@@ -78,6 +78,11 @@ def scatter_i32(dst, idx, val, count, max_count):
     dst.view(-1)[idx[:n].long()] = val[:n]
 
 
+def gather_where_i32(dst, src_index, src):
+    m = src_index >= 0
+    dst[m] = src[src_index[m].long()]
+
+
 def lossless_bf16(v):
     return None
 
@@ -232,7 +237,7 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
     return res
 
 
-ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "linear", "gemm_plain", "gemm_skinny",
+ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny",
        "qkv_linear_to_cache", "qkv_to_cache",
        "attention_plain", "attention_decode_scratch", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]

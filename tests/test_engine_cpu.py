@@ -1,6 +1,8 @@
 """The engine's host logic without a GPU: the device operations are replaced by their plain CPU references
 (tests/cpu_ops.py), everything else - parts, blocks, step building, cache manager, scheduler, sampler - is
 the product's."""
+import dataclasses
+
 import numpy as np
 import pytest
 import torch
@@ -85,6 +87,49 @@ def test_preempted_requests_generate_the_same_tokens(model_dirs, cpu_ops_install
     assert tight.scheduler.num_preemptions > 0 and roomy.scheduler.num_preemptions == 0
     assert a == b
     assert a[1] != a[0][:0] and len(a[1]) == 10
+
+
+@pytest.mark.parametrize("pages", [64, 5])
+def test_steps_launched_ahead_change_nothing(model_dirs, cpu_ops_installed, pages):
+    """The engine launches a step before it has read the tokens of the one before.  Tokens, finish reasons
+    and the order of finishing must be what the engine that waits for every step produces: requests that
+    end on their end-of-sequence token (after a step ahead already ran for them), by length, and with so
+    few pages that some are preempted while a token of theirs is still on its way."""
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    prompts = [helpers.random_tokens(512, n, 120 + i) for i, n in enumerate([9, 14, 11, 3, 20])]
+
+    preempted = []
+
+    def run(pipeline, params):
+        eng = LLMEngine(model, page_size=8, num_pages=pages, max_batch_tokens=48, chunk_size=16, max_num_seqs=3,
+                        pipeline=pipeline)
+        ids = [eng.add_request(p, dataclasses.replace(sp)) for p, sp in zip(prompts, params)]
+        order = []
+        while eng.has_work():
+            order += [r.id for r in eng.step()]
+        assert eng.cache.free_pages == eng.cache.total_pages
+        assert sorted(order) == sorted(ids), "every request is reported exactly once"
+        preempted.append(eng.scheduler.num_preemptions)
+        return [(eng.requests[i].output, eng.requests[i].finish_reason) for i in ids], order
+
+    free = [SamplingParams(max_new_tokens=12), SamplingParams(temperature=0.9, seed=5, max_new_tokens=12),
+            SamplingParams(temperature=1.3, top_k=30, seed=6, max_new_tokens=9), SamplingParams(max_new_tokens=1),
+            SamplingParams(temperature=0.7, seed=8, max_new_tokens=12)]
+    base, _ = run(False, free)
+    # end-of-sequence ids taken from what the requests really generate, at different depths
+    eos = [base[0][0][4], base[1][0][0], base[2][0][8], base[3][0][0], None]      # the last one ends by length
+    params = [dataclasses.replace(sp, eos_id=e) for sp, e in zip(free, eos)]
+    want, want_order = run(False, params)
+    got, got_order = run(True, params)
+    assert got == want
+    assert any(reason == "eos" for _, reason in want) and any(reason == "length" for _, reason in want)
+    for (out, reason), e in zip(want, eos):
+        assert reason != "eos" or (out[-1] == e and e not in out[:-1])
+    assert sorted(got_order) == sorted(want_order)
+    assert all(n > 0 for n in preempted) == (pages < 64), preempted
 
 
 def test_sampler_follows_the_plain_sampler(cpu_ops_installed):

@@ -148,3 +148,32 @@ def test_no_starvation_under_load():
         assert steps < 500
     assert sorted(r.id for r in s.finished) == list(range(10))
     assert all(r.finish_reason == "length" for r in s.finished)
+
+
+def test_update_in_two_halves_for_steps_launched_ahead():
+    """update_pending + resolve: the next step can be decided before the tokens are known; a request that
+    turns out to have ended is finished then, its later token is dropped and its pages come back."""
+    from swifttransformer_b200.engine.scheduler import PENDING
+    cache, s = make()
+    s.add(req(0, 5, max_new=6, eos_id=9))
+    s.add(req(1, 3, max_new=2))
+    s.add(req(2, 4, max_new=6, eos_id=9, ignore_eos=True))
+    plan1 = s.schedule()
+    done, h1 = s.update_pending(plan1)
+    assert done == [] and [r.output for r in s.running] == [[PENDING]] * 3
+    plan2 = s.schedule()                                   # decided while plan1's tokens are unknown
+    assert [(p.request.id, p.n, p.samples) for p in plan2] == [(0, 1, True), (1, 1, True), (2, 1, True)]
+    done = s.resolve(h1, [9, 4, 9])                         # request 0 drew its end-of-sequence token
+    assert [r.id for r in done] == [0] and done[0].output == [9] and done[0].finish_reason == "eos"
+    assert s.running[0].output == [4] and s.running[1].output == [9]      # request 2 ignores it
+    done, h2 = s.update_pending(plan2)                      # the step ahead: request 0's result is dropped
+    assert h2[0] is None and [r.id for r in done] == [1] and done[0].finish_reason == "length"
+    assert s.resolve(h2, [5, 6, 7]) == []
+    assert done[0].output == [4, 6] and s.running[0].output == [9, 7]
+    assert s.finished[0].output == [9]
+    cache.check()
+    while s.has_work():
+        run_step(s)
+    assert cache.free_pages == cache.total_pages
+    with pytest.raises(ValueError):
+        s.resolve([None], [])
