@@ -1,0 +1,386 @@
+// Paged attention for queries that stand alone (decode tokens and very short portions) on the
+// warp-level tensor cores, bfloat16 storage, head sizes that are multiples of 16 up to 128.
+//
+// The lane-per-element kernel (attention_decode.cu) spends about as many issue slots as memory
+// cycles: every 16 bytes of a key or value cost eight conversions and eight multiply-adds.  Here
+// the arithmetic is a handful of m16n8k16 products per 16 keys and the kernel is back to being a
+// copy loop:
+//
+//   * One thread block per (query token, kv head, split of the key range); the rows of the 16-row
+//     query operand are the query heads that share the kv head (one for multi-head attention, the
+//     whole group for grouped-query attention), zero beyond.
+//   * Each of the block's four warps runs its own pipeline, without block-wide barriers: it takes
+//     every fourth group of 16 keys, gathers their key and value rows page by page with 16-byte
+//     asynchronous copies into its own ring of shared-memory stages (xor-swizzled rows), and while
+//     later groups are in flight computes S = Q K^T (ldmatrix + mma.sync), the online softmax in
+//     float, and O += P V (ldmatrix.trans + mma.sync) for the oldest one.
+//   * The four warps' (max, sum, O) are merged through shared memory; with several splits the
+//     block leaves its result in `partial` and the split that arrives last merges them, in split
+//     order (same protocol and layout as attention_decode.cu).
+//
+// Rows of a group past the end of the key range are zero-filled, never read, and masked.
+// Same mathematics as src/csrc/kernel/fused_decoding_stage_attention_mha.cu:159-318 in the
+// reference (scalar arithmetic there, one warp per head).
+#include "mma_sync.cuh"
+
+#define DM_WARPS 4
+#define DM_THREADS (DM_WARPS * 32)
+#define DM_KEYS 16               // keys per group: the k extent of P V and two n-tiles of S
+#define DM_LOG2E 1.4426950408889634f
+
+template <int DMAX> struct DmStages { static constexpr int value = DMAX == 64 ? 3 : 2; };   // 50 / 68 KB per block
+
+template <int DMAX>   // head_dim <= DMAX, a multiple of 16
+__global__ void __launch_bounds__(DM_THREADS)
+attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
+                            float* __restrict__ partial, const int* __restrict__ items,
+                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
+                            int n_layers, int layer, int nh, int nkv, int d, int page_size, int page_shift,
+                            float scale_log2, int window, int n_splits, int* __restrict__ counters) {
+    // page_shift: log2(page_size) if that is a power of two, else -1
+    constexpr int STAGES = DmStages<DMAX>::value;
+    constexpr int STAGE_ELEMS = 2 * DM_KEYS * DMAX;              // keys, then values, of one group
+    extern __shared__ __align__(128) unsigned char dm_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(dm_raw);                  // [16][DMAX]
+    bf16* sKV = sQ + 16 * DMAX;                                  // [DM_WARPS][STAGES][2][DM_KEYS][DMAX]
+    int* s_pages = reinterpret_cast<int*>(sKV + DM_WARPS * STAGES * STAGE_ELEMS);
+    __shared__ float s_m[DM_WARPS][16], s_l[DM_WARPS][16];
+    __shared__ int s_last;
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = items ? items[blockIdx.x] : blockIdx.x;
+    const int group = nh / nkv;                                   // query heads per kv head
+    const int chunks_per_kv = (group + 15) / 16;
+    const int kvh = blockIdx.y / chunks_per_kv;
+    const int h0 = kvh * group + (blockIdx.y % chunks_per_kv) * 16;   // first query head of this block
+    const int n_heads = min(16, kvh * group + group - h0);
+    const int split = blockIdx.z;
+    const int pos = positions[t];
+    if (pos < 0) return;   // padding entry of a fixed-shape launch
+    const int slot = slots[seq_of_token[t]];
+    const int* bt = block_table + (size_t)slot * max_pages;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int hi = pos + 1;
+    int per = (hi - lo + n_splits - 1) / n_splits;
+    per = (per + 15) / 16 * 16;
+    const int k_lo = lo + split * per;
+    const int k_hi = min(hi, k_lo + per);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = d >> 3;
+
+    // the page numbers of this block's key range and the queries, fetched once
+    const int p_lo = k_lo / page_size;
+    if (k_lo < k_hi) {
+        const int n_pages = (k_hi - 1) / page_size - p_lo + 1;
+        for (int i = threadIdx.x; i < n_pages; i += DM_THREADS) s_pages[i] = __ldcg(bt + p_lo + i);
+    }
+    for (int i = threadIdx.x; i < 16 * chunks; i += DM_THREADS) {
+        const int r = i / chunks, c = i - r * chunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_heads) v = __ldcg(reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h0 + r) * d + c * 8));
+        *reinterpret_cast<uint4*>(tile_ptr<DMAX>(sQ, r, c)) = v;
+    }
+    __syncthreads();
+
+    const size_t head_stride = (size_t)page_size * d;
+    const size_t kv_stride = (size_t)nkv * head_stride;
+    const size_t page_stride = (size_t)n_layers * 2 * kv_stride;
+    const bf16* kbase = pool + (size_t)layer * 2 * kv_stride + kvh * head_stride;   // this layer's and head's keys in page 0
+
+    // the query operand: fragments of the 16 x d tile, kept in registers
+    uint32_t qa[DMAX / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+        if (kk * 16 < d)
+            ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3],
+                        tile_ptr<DMAX>(sQ, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
+    }
+    float o_acc[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
+
+    // this warp's groups of 16 keys: warp, warp + 4, ... of the block's range
+    const int n_groups = k_lo < k_hi ? (k_hi - k_lo + DM_KEYS - 1) / DM_KEYS : 0;
+    const int my_n = (n_groups - warp + DM_WARPS - 1) / DM_WARPS;
+    // shared-memory addresses of this warp's stages and, per lane, the offsets its ldmatrix and copy
+    // instructions use inside a stage: nothing of this is recomputed per group
+    const uint32_t my_stages = smem_u32(sKV + warp * STAGES * STAGE_ELEMS);
+    constexpr uint32_t STAGE_BYTES = STAGE_ELEMS * sizeof(bf16), V_BYTES = DM_KEYS * DMAX * sizeof(bf16);
+    uint32_t k_off[DMAX / 16], v_off[DMAX / 16];
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+        k_off[kk] = (uint32_t)(tile_ptr<DMAX>(sQ, (lane & 7) + (lane >> 4) * 8, 2 * kk + ((lane >> 3) & 1)) - sQ) * 2;
+        v_off[kk] = V_BYTES + (uint32_t)(tile_ptr<DMAX>(sQ, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)) - sQ) * 2;
+    }
+    // Consecutive lanes copy consecutive 16-byte chunks of a row (whole 128-byte lines per instruction).
+    // Which (row of the group, chunk) a lane copies in its j-th turn does not depend on the group: worked
+    // out once, with the shared-memory offset (-1: no such turn for this head size).
+    constexpr int TURNS = DM_KEYS * (DMAX / 8) / 32;
+    int ld_row[TURNS], ld_col[TURNS];
+    uint32_t ld_off[TURNS];
+#pragma unroll
+    for (int j = 0; j < TURNS; ++j) {
+        const int idx = lane + 32 * j;
+        const int r = idx / chunks, c = idx - r * chunks;
+        ld_row[j] = r < DM_KEYS ? r : -1;
+        ld_col[j] = c * 8;
+        ld_off[j] = r < DM_KEYS ? (uint32_t)(tile_ptr<DMAX>(sQ, r, c) - sQ) * 2 : 0;
+    }
+    // When pages hold a multiple of 16 positions and the range starts on such a multiple, the 16 keys of a
+    // group lie in one page: one page lookup per group instead of one per copied row.
+    const bool one_page = page_size % DM_KEYS == 0 && k_lo % DM_KEYS == 0;
+    auto load_group = [&](int i, int stage) {
+        const uint32_t dk = my_stages + stage * STAGE_BYTES;
+        const int key0 = k_lo + (warp + i * DM_WARPS) * DM_KEYS;
+        if (one_page) {
+            const int pg = page_shift >= 0 ? key0 >> page_shift : key0 / page_size;
+            const bf16* base = kbase + (size_t)s_pages[pg - p_lo] * page_stride + (key0 - pg * page_size) * d;
+#pragma unroll
+            for (int j = 0; j < TURNS; ++j) {
+                if (ld_row[j] < 0) continue;
+                const bool ok = key0 + ld_row[j] < k_hi;
+                const bf16* src = base + ld_row[j] * d + ld_col[j];
+                cp_async16_s(dk + ld_off[j], ok ? src : pool, ok);
+                cp_async16_s(dk + V_BYTES + ld_off[j], ok ? src + kv_stride : pool, ok);
+            }
+            return;
+        }
+#pragma unroll
+        for (int j = 0; j < TURNS; ++j) {
+            if (ld_row[j] < 0) continue;
+            const int key = key0 + ld_row[j];
+            const bool ok = key < k_hi;
+            const bf16* src = pool;
+            if (ok) {
+                const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
+                src = kbase + (size_t)s_pages[pg - p_lo] * page_stride + (key - pg * page_size) * d + ld_col[j];
+            }
+            cp_async16_s(dk + ld_off[j], src, ok);
+            cp_async16_s(dk + V_BYTES + ld_off[j], ok ? src + kv_stride : pool, ok);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < my_n) load_group(s, s);
+        cp_async_commit();
+    }
+    for (int i = 0; i < my_n; ++i) {
+        if (i + STAGES - 1 < my_n) load_group(i + STAGES - 1, (i + STAGES - 1) % STAGES);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();       // group i has landed (for this lane; the barrier covers the others)
+        __syncwarp();
+        const uint32_t st = my_stages + (i % STAGES) * STAGE_BYTES;
+        // S = Q K^T: 16 rows x 16 keys
+        float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            if (kk * 16 < d) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_s(b0, b1, b2, b3, st + k_off[kk]);
+                mma_bf16(s_acc[0], qa[kk], b0, b1);
+                mma_bf16(s_acc[1], qa[kk], b2, b3);
+            }
+        }
+        const int key0 = k_lo + (warp + i * DM_WARPS) * DM_KEYS;
+        if (key0 + DM_KEYS > k_hi) {       // the range's last group: keys past its end do not count
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    if (key0 + nt * 8 + (lane & 3) * 2 + e >= k_hi) s_acc[nt][e] = s_acc[nt][2 + e] = -INFINITY;
+        }
+        float mx[2];
+        mx[0] = fmaxf(fmaxf(s_acc[0][0], s_acc[0][1]), fmaxf(s_acc[1][0], s_acc[1][1]));
+        mx[1] = fmaxf(fmaxf(s_acc[0][2], s_acc[0][3]), fmaxf(s_acc[1][2], s_acc[1][3]));
+        // The reference maximum of a row only moves when the true maximum has grown by more than 2^8 (or
+        // from "no key yet"): until then P is taken relative to the older reference, which is exact after
+        // the final division by the sum, and O and the sum need no rescaling.
+        float corr[2] = {1.f, 1.f}, m_use[2];
+        bool moved = false;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r] * scale_log2);   // scale > 0: max commutes with it
+            if (m_new > m_run[r] + 8.f) {
+                corr[r] = fast_exp2(m_run[r] - m_new);                // m_run = -inf: 0
+                m_run[r] = m_new;
+                moved = true;
+            }
+            m_use[r] = (m_run[r] == -INFINITY) ? 0.f : m_run[r];
+        }
+        moved = __any_sync(0xffffffffu, moved);
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float pa = fast_exp2(fmaf(s_acc[nt][e], scale_log2, -m_use[0]));
+                const float pb = fast_exp2(fmaf(s_acc[nt][2 + e], scale_log2, -m_use[1]));
+                s_acc[nt][e] = pa; s_acc[nt][2 + e] = pb;
+                rs[0] += pa; rs[1] += pb;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+            l_run[r] = l_run[r] * corr[r] + rs[r];
+        }
+        uint32_t a[4];
+        a[0] = pack_bf16(s_acc[0][0], s_acc[0][1]);
+        a[1] = pack_bf16(s_acc[0][2], s_acc[0][3]);
+        a[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
+        a[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
+        // O = O corr + P V
+#pragma unroll
+        for (int np = 0; np < DMAX / 16; ++np) {
+            if (np * 16 < d) {
+                if (moved) {
+                    o_acc[2 * np][0] *= corr[0]; o_acc[2 * np][1] *= corr[0];
+                    o_acc[2 * np][2] *= corr[1]; o_acc[2 * np][3] *= corr[1];
+                    o_acc[2 * np + 1][0] *= corr[0]; o_acc[2 * np + 1][1] *= corr[0];
+                    o_acc[2 * np + 1][2] *= corr[1]; o_acc[2 * np + 1][3] *= corr[1];
+                }
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans_s(b0, b1, b2, b3, st + v_off[np]);
+                mma_bf16(o_acc[2 * np], a, b0, b1);
+                mma_bf16(o_acc[2 * np + 1], a, b2, b3);
+            }
+        }
+        __syncwarp();                      // every lane is done with the stage before it is refilled
+    }
+    cp_async_wait<0>();
+    __syncthreads();                       // all warps are done with their stages: the space is reused
+
+    // ---- merge the four warps: each leaves (max, sum, O) of its 16 rows in shared memory
+    float* s_o = reinterpret_cast<float*>(sKV);                  // [DM_WARPS][16][d]
+    {
+        const int ra = lane >> 2, rb = ra + 8;
+        if ((lane & 3) == 0) {
+            s_m[warp][ra] = m_run[0]; s_l[warp][ra] = l_run[0];
+            s_m[warp][rb] = m_run[1]; s_l[warp][rb] = l_run[1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < DMAX / 8; ++nt) {
+            const int dim = nt * 8 + (lane & 3) * 2;
+            if (dim < d) {
+                float* pa = s_o + ((size_t)warp * 16 + ra) * d + dim;
+                float* pb = s_o + ((size_t)warp * 16 + rb) * d + dim;
+                pa[0] = o_acc[nt][0]; pa[1] = o_acc[nt][1];
+                pb[0] = o_acc[nt][2]; pb[1] = o_acc[nt][3];
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_heads * d; i += DM_THREADS) {
+        const int r = i / d, e = i - r * d;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DM_WARPS; ++w) mm = fmaxf(mm, s_m[w][r]);
+        float ll = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < DM_WARPS; ++w) {
+            const float f = s_m[w][r] == -INFINITY ? 0.f : exp2f(s_m[w][r] - mm);
+            ll += s_l[w][r] * f;
+            a += s_o[((size_t)w * 16 + r) * d + e] * f;
+        }
+        const int h = h0 + r;
+        if (n_splits == 1) {
+            out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / ll);
+        } else {
+            float* part = partial + (((size_t)blockIdx.x * nh + h) * n_splits + split) * (d + 2);
+            part[2 + e] = a;
+            if (e == 0) { part[0] = mm; part[1] = ll; }
+        }
+    }
+    if (n_splits == 1 || !counters) return;
+    // The split that arrives last at this (token, first head of the block) merges all of them (in split
+    // order, so the result does not depend on which one that was) and resets the counter.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* c = counters + (size_t)blockIdx.x * nh + h0;
+        s_last = atomicAdd(c, 1) == n_splits - 1;
+        if (s_last) *c = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < n_heads * d; i += DM_THREADS) {
+        const int r = i / d, e = i - r * d;
+        const int h = h0 + r;
+        const float* all = partial + ((size_t)blockIdx.x * nh + h) * n_splits * (d + 2);
+        float gm = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) gm = fmaxf(gm, __ldcg(all + (size_t)sp * (d + 2)));
+        float gl = 0.f, a = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float ms = __ldcg(all + (size_t)sp * (d + 2));
+            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - gm);
+            gl += __ldcg(all + (size_t)sp * (d + 2) + 1) * f;
+            a += __ldcg(all + (size_t)sp * (d + 2) + 2 + e) * f;
+        }
+        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / gl);
+    }
+}
+
+template <int DMAX>
+static size_t dm_smem_bytes(int d, int max_pages) {
+    const size_t stages = (size_t)DM_WARPS * DmStages<DMAX>::value * 2 * DM_KEYS * DMAX * sizeof(bf16);
+    const size_t merge = (size_t)DM_WARPS * 16 * d * sizeof(float);        // reuses the stages' space
+    return 16 * DMAX * sizeof(bf16) + (stages > merge ? stages : merge) + (size_t)max_pages * sizeof(int);
+}
+
+ST_EXPORT int st_attention_decode_mma_applies(int d) { return d > 0 && d % 16 == 0 && d <= 128; }
+
+// Same arguments and scratch layout as st_attention_decode.
+ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out, float* partial, const int* items,
+                                      int n_items, const int* positions, const int* seq_of_token, const int* slots,
+                                      const int* block_table, int max_pages, int n_layers, int layer, int nh,
+                                      int nkv, int d, int page_size, float scale, int window, int n_splits,
+                                      int* counters, void* stream) {
+    if (n_items <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
+    if (!st_attention_decode_mma_applies(d)) return ST_ERR_BAD_SIZE;
+    if (n_splits > 1 && !partial) return ST_ERR_BAD_ARG;
+    const int group = nh / nkv;
+    const long long gy = (long long)nkv * ((group + 15) / 16);
+    if (gy > 65535) return ST_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_items, (unsigned)gy, n_splits);
+    const float sl2 = scale * DM_LOG2E;
+    int page_shift = -1;
+    for (int b = 0; b < 30; ++b)
+        if (page_size == (1 << b)) page_shift = b;
+    int rc;
+    if (d <= 64) {
+        const size_t smem = dm_smem_bytes<64>(d, max_pages);
+        if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<64>, grid, dim3(DM_THREADS), smem, s, (const bf16*)q,
+                           (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,
+                           seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift,
+                           sl2, window, n_splits, counters);
+    } else {
+        const size_t smem = dm_smem_bytes<128>(d, max_pages);
+        if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<128>, grid, dim3(DM_THREADS), smem, s, (const bf16*)q,
+                           (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,
+                           seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift,
+                           sl2, window, n_splits, counters);
+    }
+    return rc;
+}

@@ -16,52 +16,12 @@
 // (16x16 wmma tiles over this step's q/k/v buffer only, whole prompts only) and
 // src/csrc/kernel/xformers_attention.cu:313-393.  Chunked prefill over the
 // cache has no counterpart there.
-#include "common.cuh"
+#include "mma_sync.cuh"
 
 #define PF_BM 128            // query rows per thread block (16 per warp)
 #define PF_BN 64             // keys per tile
 #define PF_THREADS 256
 #define LOG2E 1.4426950408889634f
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
-    const uint32_t d = smem_u32(dst);
-    const int n = pred ? 16 : 0;   // src-size 0: the 16 bytes are filled with zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: 2 ulp, exp2(-inf) = 0
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// element (row, 16-byte chunk c) of a tile whose rows hold DMAX bf16: chunks are
-// xor-swizzled with the row so that eight rows at one chunk hit distinct banks
-template <int DMAX>
-__device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
-    return base + row * DMAX + ((chunk ^ (row & 7)) << 3);
-}
 
 // tiles[i] = {index of the request in the step, offset of the tile in the request's new tokens}
 template <int DMAX>

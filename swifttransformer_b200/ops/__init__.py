@@ -304,9 +304,14 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                      items: Optional[torch.Tensor], n_items: int, positions: torch.Tensor,
                      seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
                      scale: float, window: int = 0, n_splits: int = 1,
-                     partial: Optional[torch.Tensor] = None, fused_merge: bool = True) -> torch.Tensor:
+                     partial: Optional[torch.Tensor] = None, fused_merge: bool = True,
+                     kernel: str = "auto") -> torch.Tensor:
     """bfloat16 paged attention for single query tokens; ``items`` lists the token indices it serves
-    (None: tokens 0..n_items-1).  A token whose position is negative is skipped."""
+    (None: tokens 0..n_items-1).  A token whose position is negative is skipped.
+
+    kernel: "mma" = the tensor-core kernel (head sizes that are multiples of 16 up to 128; with several
+    splits it needs the fused merge), "lanes" = the kernel with eight lanes per key (multiples of 8 up to
+    256), "auto" = the first that applies."""
     _, n_layers, _, nkv, page_size, d = pool.shape
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode is a bfloat16 kernel")
@@ -316,10 +321,22 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
             raise KernelError(f"attention_decode: needs {need} floats of scratch for {n_splits} splits")
     counters = _decode_counters(q.device) if (n_splits > 1 and fused_merge
                                               and n_items * nh <= _DECODE_COUNTERS) else None
-    _check(lib().st_attention_decode(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items, _p(positions),
-                                     _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
-                                     n_layers, layer, nh, nkv, d, page_size, _f(scale), window, n_splits,
-                                     _p(counters), _stream()), "attention_decode")
+    mma_ok = bool(lib().st_attention_decode_mma_applies(d)) and (n_splits == 1 or counters is not None)
+    if kernel == "auto":
+        kernel = "mma" if mma_ok else "lanes"
+    if kernel == "mma":
+        if not mma_ok:
+            raise KernelError("attention_decode: the tensor-core kernel takes head sizes that are multiples of "
+                              "16 up to 128 and merges its splits itself")
+        fn, name = lib().st_attention_decode_mma, "attention_decode_mma"
+    elif kernel == "lanes":
+        fn, name = lib().st_attention_decode, "attention_decode"
+    else:
+        raise KernelError(f"attention_decode: no kernel named {kernel!r}")
+    _check(fn(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items, _p(positions),
+              _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
+              n_layers, layer, nh, nkv, d, page_size, _f(scale), window, n_splits,
+              _p(counters), _stream()), name)
     return out
 
 

@@ -156,7 +156,7 @@ def attention_decode_scratch(n_items, nh, d, n_splits):
 
 
 def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_token, slots, block_table, nh,
-                     scale, window=0, n_splits=1, partial=None):
+                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto"):
     idx = items[:n_items].long() if items is not None else torch.arange(n_items)
     tmp = torch.zeros_like(out)
     pos = torch.full_like(positions, -1)

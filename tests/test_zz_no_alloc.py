@@ -52,7 +52,8 @@ def test_no_alloc_entry_point_matches_the_regular_one(shape):
         # the regular entry point: scratch from the caller
         want = torch.zeros(n, nh * d, dtype=torch.bfloat16, device=DEV)
         partial = torch.empty(ops.attention_decode_scratch(n, nh, d, n_splits), device=DEV)
-        ops.attention_decode(dq, dpool, 1, want, None, n, dpos, dseq, dslots, dbt, nh, scale, 0, n_splits, partial)
+        ops.attention_decode(dq, dpool, 1, want, None, n, dpos, dseq, dslots, dbt, nh, scale, 0, n_splits, partial,
+                             kernel="lanes")
         got = torch.zeros_like(want)
         torch.cuda.synchronize()
         held = torch.cuda.memory_allocated()
