@@ -24,10 +24,10 @@
 // `status` gets 3, tensor memory is freed and the kernel returns.
 // Reference counterparts: src/csrc/kernel/fused_context_stage_attention.cu:82-453 and
 // src/csrc/kernel/xformers_attention.cu:313-393.
-#include <cuda.h>
 #include <mutex>
 
 #include "tcgen05.cuh"
+#include "tma_host.h"
 
 #define TM_THREADS 384   // 2 warpgroups of softmax threads, 2 warps that issue products, 2 warps that issue copies
 
@@ -417,10 +417,6 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
 }
 
 // ---- host side: the pool's tensor map (encoded once per pool and geometry) ---------------------------
-typedef CUresult (*tm_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 struct TmMapKey {
     const void* pool;
     long long rows;
@@ -433,23 +429,6 @@ struct TmMapEntry {
 static std::mutex tm_mutex;
 static TmMapEntry tm_maps[16];
 static int tm_n_maps = 0, tm_next = 0;
-static tm_encode_fn tm_encode = nullptr;
-static bool tm_encode_looked_up = false;
-
-// the driver's cuTensorMapEncodeTiled, found through the runtime (the library does not link libcuda)
-static tm_encode_fn tm_get_encode() {
-    if (!tm_encode_looked_up) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &res) == cudaSuccess &&
-            res == cudaDriverEntryPointSuccess)
-            tm_encode = (tm_encode_fn)fn;
-        else
-            (void)cudaGetLastError();
-        tm_encode_looked_up = true;
-    }
-    return tm_encode;
-}
 
 // rows: pages x layers x 2 x kv_heads, each [page_size][d] bfloat16
 static int tm_pool_map(const void* pool, long long rows, int page_size, int d, CUtensorMap* out) {
@@ -461,17 +440,10 @@ static int tm_pool_map(const void* pool, long long rows, int page_size, int d, C
             return 0;
         }
     }
-    tm_encode_fn enc = tm_get_encode();
-    if (!enc) return ST_ERR_BAD_ARG;
-    const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)rows};
-    const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)page_size * d * 2};       // bytes, dims 1 and 2
-    const cuuint32_t box[3] = {64, (cuuint32_t)page_size, 1};
-    const cuuint32_t elem[3] = {1, 1, 1};
+    const unsigned long long dims[3] = {(unsigned long long)d, (unsigned long long)page_size, (unsigned long long)rows};
+    const unsigned box[3] = {64, (unsigned)page_size, 1};
     CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, elem,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return ST_ERR_BAD_ARG;
+    if (st_tma_encode_bf16(&m, pool, 3, dims, box)) return ST_ERR_BAD_ARG;
     TmMapEntry& e = tm_maps[tm_next];
     e.key = TmMapKey{pool, rows, page_size, d};
     e.map = m;

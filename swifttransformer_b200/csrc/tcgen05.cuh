@@ -128,3 +128,8 @@ __device__ __forceinline__ void tc_tma_load_3d(uint32_t dst, const void* tmap, i
                  "[%0], [%1, {%2, %3, %4}], [%5];\n"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(mbar) : "memory");
 }
+__device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(mbar) : "memory");
+}

@@ -346,9 +346,12 @@ class ModelRunner:
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault (a hole in a block table).  Synchronises."""
-        code = int(self.status.item())
+        code = int(self.status.item()) or ops.kernel_status(self.device)
         if code != 0:
             self.status.zero_()
+            if code == 5:
+                raise RuntimeError("the tcgen05 matrix product gave up waiting for its copies or products; "
+                                   "the step's result is invalid")
             if code in (3, 4):
                 raise RuntimeError("the tcgen05 attention kernel gave up waiting for the tensor cores; "
                                    "the step's result is invalid")

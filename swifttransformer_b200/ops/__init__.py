@@ -165,6 +165,16 @@ def gather_where_i32(dst: torch.Tensor, src_index: torch.Tensor, src: torch.Tens
 
 
 # ------------------------------------------------------------ matrix products
+_tc_status = {}
+
+
+def _tc_status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _tc_status:
+        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[key]
+
+
 def lossless_bf16(v: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """A bfloat16 copy of a float vector if every element survives the rounding unchanged, else None."""
     if v is None or v.dtype != torch.float32:
@@ -190,6 +200,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return torch.empty((0, m), dtype=out_dtype, device=a.device)
     if n <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0:
         return gemm_skinny(a, w, bias, act, out_dtype)
+    if n <= min(STREAM_TC_MAX_ROWS, 128) and a.shape[1] % 8 == 0:
+        return gemm_stream_tc(a, w, bias, act, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(a, w.t(), out_dtype=torch.float32)
     elif bias_bf16 is not None and act in ("none", "relu"):
@@ -206,6 +218,42 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 # step, batch 32: 2.17 vs 3.29 ms).
 SKINNY_MAX_ROWS = 8
 SKINNY_KERNEL_MAX_ROWS = 32
+
+
+# Up to this many tokens (and above SKINNY_MAX_ROWS) the tcgen05 weight-streaming kernel serves bfloat16
+# products; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on.  Off by default: measured
+# on OPT-1.3B decode steps it is behind the library at every batch (16: 1.91 against 1.62 ms per step,
+# 64: 4.43 against 2.67): every block re-reads all of x for its 128 features and its epilogue does not
+# overlap the next tile's copies.
+STREAM_TC_MAX_ROWS = 0
+
+
+def gemm_stream_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+                   out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(a @ w.T + bias) for at most 128 rows of bfloat16 ``a`` on tcgen05 fed by TMA; w is [out, in] with
+    in % 8 == 0.  A wait that expires inside the kernel shows in ``kernel_status``."""
+    out_dtype = out_dtype or a.dtype
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_stream_tc is a bfloat16 kernel")
+    a = a.contiguous()
+    assert w.is_contiguous()
+    n, k = a.shape
+    m = w.shape[0]
+    out = torch.empty((n, m), dtype=out_dtype, device=a.device)
+    _check(lib().st_gemm_stream_tc(_p(a), _p(w), _p(bias), _p(out), n, m, k, ACT_CODES[act],
+                                   int(out_dtype == torch.float32), _p(_tc_status_word(a.device)), _stream()),
+           "gemm_stream_tc")
+    return out
+
+
+def kernel_status(device: torch.device) -> int:
+    """The status word of kernels that have no step context to report to (0: fine; 5: the tcgen05 product
+    gave up waiting); reading it synchronises and clears it."""
+    word = _tc_status_word(torch.device(device))
+    code = int(word.item())
+    if code:
+        word.zero_()
+    return code
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
@@ -348,16 +396,6 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
 
 def attention_prefill_tile_rows() -> int:
     return int(lib().st_attention_prefill_tile_rows())
-
-
-_tc_status = {}
-
-
-def _tc_status_word(device: torch.device) -> torch.Tensor:
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    if key not in _tc_status:
-        _tc_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tc_status[key]
 
 
 def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,

@@ -96,6 +96,12 @@ def linear(a, w, bias=None, act="none", out_dtype=None, bias_bf16=None):
 
 gemm_plain = linear
 gemm_skinny = linear
+gemm_stream_tc = linear
+STREAM_TC_MAX_ROWS = 0
+
+
+def kernel_status(device):
+    return 0
 SKINNY_MAX_ROWS = 8
 
 
@@ -237,7 +243,7 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
     return res
 
 
-ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny",
+ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
        "qkv_linear_to_cache", "qkv_to_cache",
        "attention_plain", "attention_decode_scratch", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]

@@ -340,6 +340,28 @@ def test_gemm_skinny(shape):
     assert torch.equal(one[0], full[n - 1])
 
 
+@pytest.mark.parametrize("shape", [(9, 130, 64), (16, 2048, 2048), (33, 777, 520), (48, 300, 8192), (64, 6144, 2048),
+                                   (100, 1000, 264), (128, 4096, 1024), (12, 50272, 512)])
+def test_gemm_stream_tc(shape):
+    """The tcgen05 + TMA weight-streaming product: every count of tokens up to 128, feature counts that are
+    no multiple of its 128-row tiles, k that is no multiple of its 64-wide stages, with and without k slices."""
+    n, m, k = shape
+    dtype = torch.bfloat16
+    a, w, b = rnd((n, k), dtype, 84), rnd((m, k), dtype, 85, 0.1), rnd((m,), torch.float32, 86)
+    for act in ("none", "relu", "gelu"):
+        got = ops.gemm_stream_tc(a.to(DEV), w.to(DEV), b.to(DEV), act, torch.float32)
+        close(got, cpu_ops.linear(a, w, b, act, torch.float32), torch.float32, f"gemm_stream_tc {act}", rel=2e-5)
+    got = ops.gemm_stream_tc(a.to(DEV), w.to(DEV))
+    close(got, cpu_ops.linear(a, w), dtype, "gemm_stream_tc bf16 out", rel=8e-3)
+    assert ops.kernel_status(DEV) == 0
+    with pytest.raises(ops.KernelError):
+        ops.gemm_stream_tc(rnd((129, k), dtype, 87).to(DEV), w.to(DEV))
+    # a row's result does not depend on the other rows in the batch
+    one = ops.gemm_stream_tc(a[n - 1:n].to(DEV).contiguous(), w.to(DEV), b.to(DEV), "none", torch.float32)
+    full = ops.gemm_stream_tc(a.to(DEV), w.to(DEV), b.to(DEV), "none", torch.float32)
+    assert torch.equal(one[0], full[n - 1])
+
+
 @pytest.mark.parametrize("n", [1, 8, 13, 32])
 def test_qkv_linear_to_cache(n):
     dtype = torch.bfloat16
