@@ -92,6 +92,17 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
                                 T* __restrict__ out_act, float* out_f32) {
     extern __shared__ __align__(16) float srow[];
     __shared__ float scratch[32];
+    // gain and shift of this thread's first two vectors are fetched before the wait for the kernel
+    // before this one (no kernel writes them): at the end they would be one more round trip to memory
+    float4 g_pre[2], b_pre[2];
+    if (VEC && kind != 2) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int e = (threadIdx.x + j * blockDim.x) * 4;
+            g_pre[j] = (gamma && e < width) ? load4(gamma + e) : make_float4(1.f, 1.f, 1.f, 1.f);
+            b_pre[j] = (beta && e < width) ? load4(beta + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int r = blockIdx.x;
@@ -153,12 +164,18 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
         __syncthreads();
     }
     if (VEC) {
-        for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+        int turn = 0;
+        for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4, ++turn) {
             float4 y = load4(srow + e);
             if (kind != 2) {
                 y = make_float4((y.x - mean) * rstd, (y.y - mean) * rstd, (y.z - mean) * rstd, (y.w - mean) * rstd);
-                if (gamma) { const float4 g = load4(gamma + e); y = make_float4(y.x * g.x, y.y * g.y, y.z * g.z, y.w * g.w); }
-                if (beta) y = add4(y, load4(beta + e));
+                if (turn < 2) {
+                    const float4 g = turn == 0 ? g_pre[0] : g_pre[1];
+                    y = add4(make_float4(y.x * g.x, y.y * g.y, y.z * g.z, y.w * g.w), turn == 0 ? b_pre[0] : b_pre[1]);
+                } else {
+                    if (gamma) { const float4 g = load4(gamma + e); y = make_float4(y.x * g.x, y.y * g.y, y.z * g.z, y.w * g.w); }
+                    if (beta) y = add4(y, load4(beta + e));
+                }
             }
             if (out_act) store4(out_act + (size_t)r * width + e, y);
             if (out_f32) store4(out_f32 + (size_t)r * width + e, y);

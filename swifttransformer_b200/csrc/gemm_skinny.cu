@@ -132,6 +132,19 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     const int kb_first = kb_begin + warp;
     Round ra, rb;
     issue_w(ra, kb_first);          // out-of-range blocks load nothing
+    // What the epilogue needs and no kernel of the step writes is fetched now, under the weight stream,
+    // instead of at the end, where every dependent load is a round trip on the critical path: the bias
+    // of this thread's output feature (the same in all of its epilogue turns, 256 being a multiple of
+    // 16) and, for key/value features, the page of its first token (a chain of four loads).
+    float bias_pre = 0.f;
+    if (bias && row0 + (int)(threadIdx.x & 15) < N) bias_pre = bias[row0 + (threadIdx.x & 15)];
+    int pos_pre = -1, page_pre = -1;
+    if (QKV && tgt.write_kv && row0 + 15 >= tgt.qw && (int)(threadIdx.x >> 4) < M && threadIdx.x < 16 * 8 * NT) {
+        const int m = threadIdx.x >> 4;
+        pos_pre = tgt.positions[m];
+        if (pos_pre >= 0)
+            page_pre = tgt.block_table[(size_t)tgt.slots[tgt.seq_of_token[m]] * tgt.max_pages + pos_pre / tgt.page_size];
+    }
     ST_PDL_WAIT();
     issue_x(ra, kb_first);
     for (int kb0 = kb_first; kb0 < nkb; kb0 += 2 * STEP) {
@@ -177,7 +190,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
             for (int wi = 0; wi < SK_WARPS; ++wi) v += red[wi][r][m];
         }
         if (m >= M || n >= N) continue;
-        if (bias) v += bias[n];
+        v += bias_pre;
         if (!QKV) {
             v = apply_act(v, act);
             if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
@@ -186,9 +199,11 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
             if (n < tgt.qw) {
                 tgt.q_out[(size_t)m * tgt.qw + n] = __float2bfloat16_rn(v);
             } else if (tgt.write_kv) {
-                const int pos = tgt.positions[m];
+                const bool pre = i == (int)threadIdx.x;     // this thread's first turn: fetched at the start
+                const int pos = pre ? pos_pre : tgt.positions[m];
                 if (pos < 0) continue;                      // padding token of a fixed-shape step
-                const int page = tgt.block_table[(size_t)tgt.slots[tgt.seq_of_token[m]] * tgt.max_pages + pos / tgt.page_size];
+                const int page = pre ? page_pre
+                                     : tgt.block_table[(size_t)tgt.slots[tgt.seq_of_token[m]] * tgt.max_pages + pos / tgt.page_size];
                 if (page < 0 || page >= tgt.num_pages) { atomicExch(tgt.status, 1); continue; }
                 const int kw = tgt.nkv * tgt.d;
                 const int rr = n - tgt.qw;
