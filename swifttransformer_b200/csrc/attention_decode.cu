@@ -43,8 +43,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     __shared__ float s_m[DEC_GROUPS], s_l[DEC_GROUPS];
     __shared__ int s_last;
     extern __shared__ float s_acc[];   // [DEC_GROUPS][d]
-    ST_PDL_WAIT();
     ST_PDL_TRIGGER();
+    // the token's position, slot and page numbers are inputs of the step that no kernel of the step writes:
+    // they are fetched before the wait for the kernel before this one; queries, keys and values after it
     const int t = items ? items[blockIdx.x] : blockIdx.x;
     const int h = blockIdx.y, split = blockIdx.z;
     const int kvh = h / (nh / nkv);
@@ -66,6 +67,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
         const int n_pages = (k_hi - 1) / page_size - p_lo + 1;
         for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) s_pages[i] = __ldcg(bt + p_lo + i);
     }
+    ST_PDL_WAIT();
     __syncthreads();
 
     const int g = threadIdx.x >> 3, l8 = threadIdx.x & 7;

@@ -47,8 +47,10 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     int* s_pages = reinterpret_cast<int*>(sKV + DM_WARPS * STAGES * STAGE_ELEMS);
     __shared__ float s_m[DM_WARPS][16], s_l[DM_WARPS][16];
     __shared__ int s_last;
-    ST_PDL_WAIT();
     ST_PDL_TRIGGER();
+    // Which token, where it stands, its slot and the page numbers of its key range are inputs of the step
+    // that no kernel of the step writes: this chain of dependent loads runs before the wait for the kernel
+    // before this one, under that kernel's tail.  The queries and this step's keys and values come after.
     const int t = items ? items[blockIdx.x] : blockIdx.x;
     const int group = nh / nkv;                                   // query heads per kv head
     const int chunks_per_kv = (group + 15) / 16;
@@ -75,6 +77,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         const int n_pages = (k_hi - 1) / page_size - p_lo + 1;
         for (int i = threadIdx.x; i < n_pages; i += DM_THREADS) s_pages[i] = __ldcg(bt + p_lo + i);
     }
+    ST_PDL_WAIT();
     for (int i = threadIdx.x; i < 16 * chunks; i += DM_THREADS) {
         const int r = i / chunks, c = i - r * chunks;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
