@@ -36,8 +36,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
     bf16* sK = sQ + PF_BM * DMAX;            // [2][PF_BN][DMAX]
     bf16* sV = sK + 2 * PF_BN * DMAX;        // [2][PF_BN][DMAX]
 
-    const int seq = tiles[2 * blockIdx.x], off = tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    // the head is x, the fastest index in the order blocks start: all heads of the longest tile first
+    const int seq = tiles[2 * blockIdx.y], off = tiles[2 * blockIdx.y + 1];
+    const int h = blockIdx.x, kvh = h / (nh / nkv);
     const int tok0 = q_start[seq] + off;
     const int n_rows = min(PF_BM, q_start[seq + 1] - tok0);
     const int pos0 = start_pos[seq] + off;           // position of the tile's first query
@@ -239,7 +240,7 @@ static int launch_prefill(const void* q, const void* pool, void* out, const int*
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, nh);
+    dim3 grid(nh, n_tiles);
     attention_prefill_kernel<DMAX><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,
         tiles, q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size,
         scale * LOG2E, window);
@@ -253,7 +254,7 @@ ST_EXPORT int st_attention_prefill(const void* q, const void* pool, void* out, c
                                    const int* block_table, int max_pages, int n_layers, int layer, int nh, int nkv,
                                    int d, int page_size, float scale, int window, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || nh > 65535) return ST_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_tiles > 65535) return ST_ERR_BAD_ARG;
     if (d <= 0 || d % 16) return ST_ERR_BAD_SIZE;
     if (d > 256) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;

@@ -77,8 +77,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const uint32_t sV = sK + DB * KV_BLK;                                // its value tile
     const uint32_t sP = sV + DB * KV_BLK;                                // one [128][64] block
 
-    const int seq = tiles[2 * blockIdx.x], off = tiles[2 * blockIdx.x + 1];
-    const int h_raw = blockIdx.y * SETS + set;
+    // the head is x, the fastest index in the order blocks start: all heads of the longest tile first
+    const int seq = tiles[2 * blockIdx.y], off = tiles[2 * blockIdx.y + 1];
+    const int h_raw = blockIdx.x * SETS + set;
     const bool active = h_raw < nh;                  // an odd number of heads leaves the last block's second set idle
     const int h = active ? h_raw : nh - 1, kvh = h / (nh / nkv);
     const int tok0 = q_start[seq] + off;
@@ -362,7 +363,7 @@ static int launch_prefill_tc(const void* q, const void* pool, void* out, const i
         configured = true;
     }
     constexpr int SETS = TC_SETS;
-    dim3 grid(n_tiles, (nh + SETS - 1) / SETS);
+    dim3 grid((nh + SETS - 1) / SETS, n_tiles);
     attention_prefill_tc_kernel<DB><<<grid, SETS * TC_SET_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,
         tiles, q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size,
         scale * TC_LOG2E, window, status);
@@ -395,7 +396,7 @@ ST_EXPORT int st_attention_prefill_tc(const void* q, const void* pool, void* out
                                       int nkv, int d, int page_size, float scale, int window, int* status,
                                       void* stream) {
     if (n_tiles <= 0) return 0;
-    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || nh > 65535 || !status) return ST_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_tiles > 65535 || !status) return ST_ERR_BAD_ARG;
     if (d <= 0 || d % 16) return ST_ERR_BAD_SIZE;
     if (d > 128) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;

@@ -97,8 +97,10 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     const uint32_t sV = sK + 2 * BUF;                                    // two value buffers
     const uint32_t sP = sV + 2 * BUF;                                    // one [128][64] block
 
-    const int seq = tiles[2 * blockIdx.x], off = tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    // Blocks start in the order of their linear index, x fastest: the head is x, so that all heads of
+    // the longest tile start first (the host lists the tiles longest key range first).
+    const int seq = tiles[2 * blockIdx.y], off = tiles[2 * blockIdx.y + 1];
+    const int h = blockIdx.x, kvh = h / (nh / nkv);
     const int tok0 = q_start[seq] + off;
     const int n_rows = min(TC_BM, q_start[seq + 1] - tok0);
     const int pos0 = start_pos[seq] + off;
@@ -471,7 +473,7 @@ static int launch_prefill_tma(const CUtensorMap& map, const void* q, void* out, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, nh);
+    dim3 grid(nh, n_tiles);
     attention_prefill_tma_kernel<DB><<<grid, TM_THREADS, smem, s>>>(map, (const bf16*)q, (bf16*)out, tiles, q_start,
         start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, page_size, scale * TC_LOG2E, window, status);
     return st_launch_status();
@@ -490,7 +492,7 @@ ST_EXPORT int st_attention_prefill_tma(const void* q, const void* pool, long lon
                                        int nkv, int d, int page_size, float scale, int window, int* status,
                                        void* stream) {
     if (n_tiles <= 0) return 0;
-    if (nh <= 0 || nkv <= 0 || nh % nkv || nh > 65535 || n_pages <= 0 || !status) return ST_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || n_tiles > 65535 || n_pages <= 0 || !status) return ST_ERR_BAD_ARG;
     if (!st_attention_prefill_tma_applies(d, page_size)) return ST_ERR_BAD_SIZE;
     const long long rows = n_pages * n_layers * 2 * nkv;
     if (rows >= (1ll << 31)) return ST_ERR_TOO_LARGE;          // TMA coordinates are 32-bit
