@@ -132,6 +132,43 @@ def test_steps_launched_ahead_change_nothing(model_dirs, cpu_ops_installed, page
     assert all(n > 0 for n in preempted) == (pages < 64), preempted
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_steps_launched_ahead_with_requests_arriving_at_random(model_dirs, cpu_ops_installed, seed):
+    """Random prompts, limits, end-of-sequence ids and arrival times, a pool that overflows now and then:
+    launching steps ahead never changes what a request generates or why it ends."""
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    rng = np.random.default_rng(1000 + seed)
+    n_req = 9
+    prompts = [helpers.random_tokens(512, int(rng.integers(1, 40)), 700 + 10 * seed + i) for i in range(n_req)]
+    arrive = sorted(int(rng.integers(0, 25)) for _ in range(n_req))
+    # a small set of end-of-sequence ids makes some requests stop early and leaves others to their limit
+    params = [SamplingParams(temperature=float(rng.choice([0.0, 0.8, 1.5])), top_k=int(rng.choice([0, 5, 50])),
+                             seed=int(rng.integers(0, 1 << 30)), max_new_tokens=int(rng.integers(1, 14)),
+                             eos_id=int(rng.integers(0, 512)) if rng.random() < 0.5 else None) for _ in range(n_req)]
+
+    def run(pipeline):
+        eng = LLMEngine(model, page_size=8, num_pages=int(rng_pages), max_batch_tokens=40, chunk_size=16,
+                        max_num_seqs=4, pipeline=pipeline)
+        ids, step, nxt = [], 0, 0
+        while nxt < n_req or eng.has_work():
+            while nxt < n_req and arrive[nxt] <= step:
+                ids.append(eng.add_request(prompts[nxt], dataclasses.replace(params[nxt])))
+                nxt += 1
+            eng.step()
+            step += 1
+            assert step < 2000
+        assert eng.cache.free_pages == eng.cache.total_pages and eng.cache.num_free_slots == 4
+        return [(eng.requests[i].output, eng.requests[i].finish_reason) for i in ids]
+
+    for rng_pages in (64, 9):
+        want, got = run(False), run(True)
+        assert got == want
+        assert all(len(o) >= 1 for o, _ in got)
+
+
 def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
     from swifttransformer_b200 import ops
     from swifttransformer_b200.sampling import Sampler, SamplingParams
