@@ -30,14 +30,16 @@
 
 template <int DMAX> struct DmStages { static constexpr int value = DMAX == 64 ? 3 : 2; };   // 50 / 68 KB per block
 
-template <int DMAX>   // head_dim <= DMAX, a multiple of 16
+// head_dim <= DMAX, a multiple of 16; FULL: head_dim == DMAX, known when compiling (no tests on it in the loops)
+template <int DMAX, bool FULL>
 __global__ void __launch_bounds__(DM_THREADS)
 attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
                             float* __restrict__ partial, const int* __restrict__ items,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
-                            int n_layers, int layer, int nh, int nkv, int d, int page_size, int page_shift,
+                            int n_layers, int layer, int nh, int nkv, int d_arg, int page_size, int page_shift,
                             float scale_log2, int window, int n_splits, int* __restrict__ counters) {
+    const int d = FULL ? DMAX : d_arg;
     // page_shift: log2(page_size) if that is a power of two, else -1
     constexpr int STAGES = DmStages<DMAX>::value;
     constexpr int STAGE_ELEMS = 2 * DM_KEYS * DMAX;              // keys, then values, of one group
@@ -358,32 +360,26 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
     for (int b = 0; b < 30; ++b)
         if (page_size == (1 << b)) page_shift = b;
     int rc;
-    if (d <= 64) {
-        const size_t smem = dm_smem_bytes<64>(d, max_pages);
-        if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (e != cudaSuccess) return (int)e;
-            configured = true;
-        }
-        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<64>, grid, dim3(DM_THREADS), smem, s, (const bf16*)q,
-                           (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,
-                           seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift,
-                           sl2, window, n_splits, counters);
-    } else {
-        const size_t smem = dm_smem_bytes<128>(d, max_pages);
-        if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            if (e != cudaSuccess) return (int)e;
-            configured = true;
-        }
-        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<128>, grid, dim3(DM_THREADS), smem, s, (const bf16*)q,
-                           (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,
-                           seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift,
-                           sl2, window, n_splits, counters);
-    }
+#define LAUNCH_DM(DMAX, FULL)                                                                                        \
+    do {                                                                                                             \
+        const size_t smem = dm_smem_bytes<DMAX>(d, max_pages);                                                       \
+        if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;                                                              \
+        static bool configured = false;                                                                              \
+        if (!configured) {                                                                                           \
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL>,                            \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+            configured = true;                                                                                       \
+        }                                                                                                            \
+        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL>, grid, dim3(DM_THREADS), smem, s,  \
+                           (const bf16*)q, (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr,  \
+                           items, positions, seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv,  \
+                           d, page_size, page_shift, sl2, window, n_splits, counters);                               \
+    } while (0)
+    if (d == 64) LAUNCH_DM(64, true);
+    else if (d < 64) LAUNCH_DM(64, false);
+    else if (d == 128) LAUNCH_DM(128, true);
+    else LAUNCH_DM(128, false);
+#undef LAUNCH_DM
     return rc;
 }
