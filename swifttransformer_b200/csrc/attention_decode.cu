@@ -32,14 +32,16 @@ __device__ __forceinline__ bf16x8 ldg16(const bf16* p) {
     return r;
 }
 
-template <int NCHUNK>   // head_dim <= 64 * NCHUNK, a multiple of 8
+// head_dim <= 64 * NCHUNK, a multiple of 8; FULL: head_dim == 64 * NCHUNK, known when compiling
+template <int NCHUNK, bool FULL>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
                         float* __restrict__ partial, const int* __restrict__ items,
                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                         const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
-                        int n_layers, int layer, int nh, int nkv, int d, int page_size, float scale_log2,
+                        int n_layers, int layer, int nh, int nkv, int d_arg, int page_size, float scale_log2,
                         int window, int n_splits, int* __restrict__ counters) {
+    const int d = FULL ? 64 * NCHUNK : d_arg;
     __shared__ float s_m[DEC_GROUPS], s_l[DEC_GROUPS];
     __shared__ int s_last;
     extern __shared__ float s_acc[];   // [DEC_GROUPS][d]
@@ -291,7 +293,9 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     if (smem > 48 * 1024) return ST_ERR_TOO_LARGE;
     const float sl2 = scale * LOG2E;
 #define LAUNCH_DEC(NC)                                                                                         \
-    st_launch_pdl("decode", attention_decode_kernel<NC>, grid, dim3(DEC_THREADS), smem, s, (const bf16*)q,               \
+    (d == 64 * NC ? LAUNCH_DEC2(NC, true) : LAUNCH_DEC2(NC, false))
+#define LAUNCH_DEC2(NC, FULL)                                                                                  \
+    st_launch_pdl("decode", attention_decode_kernel<NC, FULL>, grid, dim3(DEC_THREADS), smem, s, (const bf16*)q,               \
         (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,              \
         seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, sl2, window,       \
         n_splits, counters)
@@ -301,6 +305,7 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     else if (d <= 192) rc = LAUNCH_DEC(3);
     else rc = LAUNCH_DEC(4);
 #undef LAUNCH_DEC
+#undef LAUNCH_DEC2
     if (rc) return rc;
     if (n_splits > 1 && !counters) {
         dim3 g2(n_items, nh);

@@ -333,7 +333,7 @@ def attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.
 
 
 _DECODE_COUNTERS = 1 << 16
-DECODE_MMA_MIN_BLOCKS = 512      # (token, kv head) pairs from which the tensor-core decode attention serves head sizes above 64
+DECODE_MMA_MIN_BLOCKS = 2048     # (token, kv head) pairs from which the tensor-core decode attention serves head sizes above 64
 _decode_counter_buffers = {}
 
 
@@ -372,10 +372,11 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                                               and n_items * nh <= _DECODE_COUNTERS) else None
     mma_ok = bool(lib().st_attention_decode_mma_applies(d)) and (n_splits == 1 or counters is not None)
     if kernel == "auto":
-        # Measured on OPT sizes: for head sizes up to 64 the tensor-core kernel is ahead everywhere; for 128
-        # it holds three blocks per SM against four and wins from 16 requests of 32 heads on (ms per step
-        # of OPT-6.7B, tensor-core against lanes: batch 1: 3.60 / 3.40, 8: 4.49 / 4.38, 16: 4.12 / 4.72,
-        # 64: 6.19 / 7.49).  Grouped queries always gain: the group shares one read of the keys and values.
+        # Measured on OPT sizes (ms per decode step, tensor-core kernel against lanes kernel): head size 64
+        # (OPT-1.3B): batch 1: 1.150 / 1.147, 8: 1.340 / 1.348, 64: 2.485 / 2.738; head size 128 (OPT-6.7B),
+        # where the tensor-core kernel holds three blocks per SM against four: batch 1: 3.60 / 3.35,
+        # 8: 4.49 / 3.87, 16: 4.12 / 3.92, 64: 6.19 / 6.34.  Grouped queries always gain from it: the group
+        # shares one read of the keys and values.
         busy = n_items * nkv >= DECODE_MMA_MIN_BLOCKS
         kernel = "mma" if mma_ok and (d <= 64 or nh != nkv or busy) else "lanes"
     if kernel == "mma":
