@@ -65,7 +65,8 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
     return r;
 }
 
-template <int NT, bool QKV>
+// KFULL: K is a multiple of 32 (known when compiling: no test on k inside a block of 32)
+template <int NT, bool QKV, bool KFULL>
 __global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 4 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
                    void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt) {
@@ -102,7 +103,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 #pragma unroll
         for (int u = 0; u < SK_UNROLL; ++u) {
             const int kb = kb0 + u * SK_WARPS;
-            const bool ok = kb < nkb && kb * 32 + t * 8 < K;   // K % 8 == 0: a 16-byte piece is inside or outside as a whole
+            const bool ok = kb < nkb && (KFULL || kb * 32 + t * 8 < K);   // K % 8 == 0: a 16-byte piece is inside or outside as a whole
             r.ua[u] = ok ? ldg_stream(wa + kb * 32) : zero;
             r.ub[u] = ok ? ldg_stream(wb + kb * 32) : zero;
         }
@@ -111,7 +112,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 #pragma unroll
         for (int u = 0; u < SK_UNROLL; ++u) {
             const int kb = kb0 + u * SK_WARPS;
-            const bool ok = kb < nkb && kb * 32 + t * 8 < K;
+            const bool ok = kb < nkb && (KFULL || kb * 32 + t * 8 < K);
 #pragma unroll
             for (int j = 0; j < NT; ++j)
                 r.xb[u][j] = (ok && xok[j]) ? __ldcg(reinterpret_cast<const uint4*>(xr[j] + kb * 32)) : zero;
@@ -266,11 +267,15 @@ static int launch_skinny(const void* x, const void* w, const float* bias, void* 
     if (K <= 0 || K % 8) return ST_ERR_BAD_SIZE;
     if (!aligned16(x) || !aligned16(w)) return ST_ERR_BAD_ARG;
     dim3 grid((N + 15) / 16, skinny_slices(N, K));
-    if (M <= 8)
-        return launch_skinny_kernel(gemm_skinny_kernel<1, QKV>, grid, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
-    if (M <= 16)
-        return launch_skinny_kernel(gemm_skinny_kernel<2, QKV>, grid, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
-    return launch_skinny_kernel(gemm_skinny_kernel<4, QKV>, grid, s, (const bf16*)x, (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt);
+#define LAUNCH_SK(NT)                                                                                              \
+    (K % 32 == 0 ? launch_skinny_kernel(gemm_skinny_kernel<NT, QKV, true>, grid, s, (const bf16*)x, (const bf16*)w, \
+                                        bias, out, M, N, K, act, out_f32, tgt)                                      \
+                 : launch_skinny_kernel(gemm_skinny_kernel<NT, QKV, false>, grid, s, (const bf16*)x, (const bf16*)w, \
+                                        bias, out, M, N, K, act, out_f32, tgt))
+    if (M <= 8) return LAUNCH_SK(1);
+    if (M <= 16) return LAUNCH_SK(2);
+    return LAUNCH_SK(4);
+#undef LAUNCH_SK
 }
 
 ST_EXPORT int st_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
