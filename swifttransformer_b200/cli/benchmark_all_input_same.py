@@ -68,8 +68,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     for input_len, batch, block_size, n_steps in experiments(args.exp_params_name):
         prompt = rng.integers(3, model.vocab_size, input_len).tolist()
         pages = batch * ((input_len + n_steps) // block_size + 2)
+        # steps are not launched ahead here: the two stages are timed separately, and a decode step that
+        # is already on the GPU when the context stage is read off would count towards the wrong one
         eng = LLMEngine(model, page_size=block_size, num_pages=pages, max_batch_tokens=max(2048, input_len),
-                        chunk_size=max(2048, input_len), max_num_seqs=batch)
+                        chunk_size=max(2048, input_len), max_num_seqs=batch, pipeline=False)
         sp = SamplingParams(max_new_tokens=n_steps, ignore_eos=True)
         for timed in (False, True):
             for _ in range(batch):

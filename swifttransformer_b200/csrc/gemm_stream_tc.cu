@@ -163,13 +163,29 @@ gemm_stream_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_co
             const int q = warp & 3, f = q * 32 + lane;
             const int n = n0 + f;
             const float b = (bias && n < N) ? bias[n] : 0.f;
-            for (int m = slice; m < M; m += n_slices) {
-                float a = 0.f;
-                for (int sl = 0; sl < n_slices; ++sl) a += cluster.map_shared_rank(part, sl)[m * GS_BM + f];
-                if (n < N) {
-                    const float r = apply_act(a + b, act);
-                    if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = r;
-                    else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(r);
+            // Four tokens per turn with all their remote loads in flight together: a load from another
+            // block's shared memory takes most of a microsecond, and one token at a time made this loop
+            // the longest part of the kernel.  The sum runs in slice order.
+            const float* remote[8];
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) remote[sl] = cluster.map_shared_rank(part, sl < n_slices ? sl : 0);
+            for (int m0 = slice; m0 < M; m0 += 4 * n_slices) {
+                float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int m = m0 + u * n_slices;
+#pragma unroll
+                    for (int sl = 0; sl < 8; ++sl)
+                        if (sl < n_slices && m < M) a[u] += remote[sl][m * GS_BM + f];
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int m = m0 + u * n_slices;
+                    if (m < M && n < N) {
+                        const float r = apply_act(a[u] + b, act);
+                        if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = r;
+                        else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(r);
+                    }
                 }
             }
         }

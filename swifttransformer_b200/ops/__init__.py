@@ -222,9 +222,10 @@ SKINNY_KERNEL_MAX_ROWS = 32
 
 # Up to this many tokens (and above SKINNY_MAX_ROWS) the tcgen05 weight-streaming kernel serves bfloat16
 # products; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on.  Off by default: measured
-# on OPT-1.3B decode steps it is behind the library at every batch (16: 1.91 against 1.62 ms per step,
-# 64: 4.43 against 2.67): every block re-reads all of x for its 128 features and its epilogue does not
-# overlap the next tile's copies.
+# on OPT-1.3B decode steps it is behind the library at every batch (16: 1.71 against 1.57 ms per step,
+# 64: 3.83 against 2.48).  Alone on an 8192 x 2048 matrix it streams at 1.9 TB/s with 16 tokens and 1.4 with
+# 64 (profiler, cold): its six-stage ring of TMA boxes does not keep memory busy, and the reason is open
+# (staggering the blocks' order over k and wider L2 requests changed nothing).
 STREAM_TC_MAX_ROWS = 0
 
 

@@ -125,6 +125,20 @@ def test_seeded_sampling_is_reproducible_and_batch_independent(model_dirs):
     assert tight.scheduler.num_preemptions > 0 and roomy.scheduler.num_preemptions == 0
 
 
+def test_benchmark_all_input_same_command_line(model_dirs):
+    """The reference's benchmark program: same arguments, one line of stage times per experiment."""
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "benchmark_all_input_same"), "tiny", "bf16",
+                        "20,3,8,5;7,2,16,3", "-m", model_dirs["a"]], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l.split() for l in r.stdout.strip().splitlines()]
+    assert lines[0][:4] == ["input_len", "batch", "block", "steps"]
+    assert [l[:4] for l in lines[1:]] == [["20", "3", "8", "5"], ["7", "2", "16", "3"]]
+    assert all(float(v) > 0 for l in lines[1:] for v in l[4:])
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "benchmark_all_input_same"), "tiny", "int4",
+                          "20,3,8,5"], capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0 and "Invalid precision" in bad.stdout
+
+
 def test_run_gpt_command_line(model_dirs, tmp_path):
     inp = tmp_path / "in.txt"
     prompts = [helpers.random_tokens(512, n, 500 + i) for i, n in enumerate([5, 17])]
