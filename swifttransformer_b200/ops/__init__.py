@@ -223,9 +223,9 @@ SKINNY_KERNEL_MAX_ROWS = 32
 # Up to this many tokens (and above SKINNY_MAX_ROWS) the tcgen05 weight-streaming kernel serves bfloat16
 # products; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on.  Off by default: measured
 # on OPT-1.3B decode steps it is behind the library at every batch (16: 1.71 against 1.57 ms per step,
-# 64: 3.83 against 2.48).  Alone on an 8192 x 2048 matrix it streams at 1.9 TB/s with 16 tokens and 1.4 with
-# 64 (profiler, cold): its six-stage ring of TMA boxes does not keep memory busy, and the reason is open
-# (staggering the blocks' order over k and wider L2 requests changed nothing).
+# 64: 3.83 against 2.48).  Of the 18 us an 8192 x 2048 product with 64 tokens takes in a graph, the copy
+# pipeline alone accounts for 8 (4.1 TB/s) and the epilogue for 9, 6 of them the reduction over k slices
+# through distributed shared memory.
 STREAM_TC_MAX_ROWS = 0
 
 
