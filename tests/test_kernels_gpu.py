@@ -181,7 +181,7 @@ def attention_case(dtype, nh, nkv, d, ps, lens, new, seed, window=0):
 
 ATT_SHAPES = [  # nh, nkv, d, page_size
     (4, 4, 16, 8), (3, 3, 32, 16), (5, 5, 48, 32), (6, 2, 64, 16), (2, 1, 80, 4), (4, 4, 128, 16), (2, 2, 256, 64),
-    (3, 1, 64, 8), (2, 2, 128, 64), (5, 5, 64, 32),
+    (3, 1, 64, 8), (2, 2, 128, 64), (5, 5, 64, 32), (40, 2, 32, 16),     # the last: 20 query heads per kv head
 ]
 
 
