@@ -55,6 +55,9 @@ __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __re
                                     const int* __restrict__ slots, const int* __restrict__ block_table,
                                     int max_pages, int num_pages, int n_layers, int layer, int nh, int nkv,
                                     int d, int page_size, int write_kv, int* __restrict__ status) {
+    // the kernel after this one may start its own preparations now (it waits for this one to end before it
+    // touches anything written here)
+    ST_PDL_TRIGGER();
     const int t = blockIdx.x;
     const int qw = nh * d, kw = nkv * d;
     const T* row = qkv + (size_t)t * (qw + 2 * kw);
