@@ -141,11 +141,13 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         const int key0 = k_lo + (warp + i * DM_WARPS) * DM_KEYS;
         if (one_page) {
             const int pg = page_shift >= 0 ? key0 >> page_shift : key0 / page_size;
-            const bf16* base = kbase + (size_t)s_pages[pg - p_lo] * page_stride + (key0 - pg * page_size) * d;
+            const int page = s_pages[pg - p_lo];
+            const bool page_ok = page >= 0;      // a hole in the block table: zeros instead of an access before the pool
+            const bf16* base = kbase + (size_t)(page_ok ? page : 0) * page_stride + (key0 - pg * page_size) * d;
 #pragma unroll
             for (int j = 0; j < TURNS; ++j) {
                 if (ld_row[j] < 0) continue;
-                const bool ok = key0 + ld_row[j] < k_hi;
+                const bool ok = page_ok && key0 + ld_row[j] < k_hi;
                 const bf16* src = base + ld_row[j] * d + ld_col[j];
                 cp_async16_s(dk + ld_off[j], ok ? src : pool, ok);
                 cp_async16_s(dk + V_BYTES + ld_off[j], ok ? src + kv_stride : pool, ok);
@@ -156,11 +158,13 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         for (int j = 0; j < TURNS; ++j) {
             if (ld_row[j] < 0) continue;
             const int key = key0 + ld_row[j];
-            const bool ok = key < k_hi;
+            bool ok = key < k_hi;
             const bf16* src = pool;
             if (ok) {
                 const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
-                src = kbase + (size_t)s_pages[pg - p_lo] * page_stride + (key - pg * page_size) * d + ld_col[j];
+                const int page = s_pages[pg - p_lo];
+                ok = page >= 0;                  // a hole in the block table: zeros instead of an access before the pool
+                if (ok) src = kbase + (size_t)page * page_stride + (key - pg * page_size) * d + ld_col[j];
             }
             cp_async16_s(dk + ld_off[j], src, ok);
             cp_async16_s(dk + V_BYTES + ld_off[j], ok ? src + kv_stride : pool, ok);

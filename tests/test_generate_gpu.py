@@ -58,6 +58,28 @@ def test_greedy_generation_bfloat16_follows_plain_unless_nearly_tied(model_dirs,
             ids.append(tok)
 
 
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+def test_many_requests_decoding_together_bfloat16(model_dirs, name):
+    """More requests than the weight-streaming product serves: library products, the separate cache-write
+    kernel and the decode attention, recorded and replayed as graphs of 16 rows."""
+    from swifttransformer_b200.sampling import SamplingParams
+    vocab = TINY[name]["cfg"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 900 + i) for i, n in enumerate([9, 30, 60, 1, 17, 33, 5, 12, 47, 2, 21, 8, 14])]
+    eng = engine(model_dirs[name], name, "bfloat16", num_pages=200, max_batch_tokens=256, chunk_size=64, max_num_seqs=16)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=10))
+    eng.runner.check_status()
+    assert eng.runner.graph_steps > 0 and eng.cache.free_pages == eng.cache.total_pages
+    cfg, w = plain_opt.load_model(model_dirs[name])
+    for p, o in zip(prompts, outs):
+        ids = list(p)
+        for tok in o:
+            logits = plain_opt.forward(cfg, w, ids)[-1]
+            best = int(np.argmax(logits))
+            if tok != best:
+                assert logits[best] - logits[tok] < 4e-2 * np.abs(logits).max(), (tok, best)
+            ids.append(tok)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_launched_ahead_change_nothing_on_the_gpu(model_dirs, dtype):
     """Launching a step before the tokens of the one before have been read (they reach it on the device)
