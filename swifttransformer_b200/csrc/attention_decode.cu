@@ -113,7 +113,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
             r.valid[u] = kk < k_hi;
             const int key = r.valid[u] ? kk : k_hi - 1;
             const int pg = key / page_size;
-            const int page = s_pages[pg - p_lo];
+            int page = s_pages[pg - p_lo];
+            if (page < 0) { r.valid[u] = false; page = 0; }   // a hole in the block table: the key is dropped, no access before the pool
             const bf16* krow = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
                                + (size_t)(key - pg * page_size) * d;
 #pragma unroll

@@ -46,10 +46,12 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, T* _
         float s = -INFINITY;
         if (j >= lo && j < hi) {
             const int page = bt[j / page_size];
-            const T* krow = pool + (((((size_t)page * n_layers + layer) * 2 + 0) * nkv + kvh) * page_size + j % page_size) * d;
-            float dot = 0.f;
-            for (int e = 0; e < d; ++e) dot += sq[e] * to_f32(krow[e]);
-            s = dot;
+            if (page >= 0) {     // a hole in the block table: the key is dropped, no access before the pool
+                const T* krow = pool + (((((size_t)page * n_layers + layer) * 2 + 0) * nkv + kvh) * page_size + j % page_size) * d;
+                float dot = 0.f;
+                for (int e = 0; e < d; ++e) dot += sq[e] * to_f32(krow[e]);
+                s = dot;
+            }
         }
         const float tile_max = block_max(s, scratch);
         const float m_new = fmaxf(m, tile_max);
@@ -69,6 +71,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, T* _
                 for (int jj = j_begin; jj < j_end; ++jj) {
                     const int key = base + jj;
                     const int page = bt[key / page_size];
+                    if (page < 0) continue;      // dropped above: its weight is zero
                     const T* vrow = pool + (((((size_t)page * n_layers + layer) * 2 + 1) * nkv + kvh) * page_size + key % page_size) * d;
                     a += sp[jj] * to_f32(vrow[e]);
                 }

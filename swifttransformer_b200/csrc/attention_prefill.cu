@@ -61,12 +61,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
         bf16* dk = sK + buf * PF_BN * DMAX;
         bf16* dv = sV + buf * PF_BN * DMAX;
         const int key = kt * PF_BN + kv_r;
-        const bool ok = key >= key_lo && key < kv_hi;   // outside: never read (its page may be gone)
+        bool ok = key >= key_lo && key < kv_hi;         // outside: never read (its page may be gone)
         const bf16* src = pool;
         if (ok) {
             const int page = bt[key / page_size];
-            src = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
-                  + (size_t)(key % page_size) * d;
+            ok = page >= 0;                             // a hole in the block table: zeros, no access before the pool
+            if (ok) src = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
+                          + (size_t)(key % page_size) * d;
         }
         for (int c = kv_c0; c < chunks; c += KV_TPR) {
             cp_async16(tile_ptr<DMAX>(dk, kv_r, c), ok ? src + c * 8 : pool, ok);

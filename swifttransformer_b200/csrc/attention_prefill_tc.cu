@@ -118,12 +118,13 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int kv_r = row >> 1, kv_c0 = row & 1;
     auto load_kv_part = [&](int kt, int which) {               // which: 0 = keys, 1 = values
         const int key = kt * TC_BN + kv_r;
-        const bool ok = key >= key_lo && key < kv_hi;           // outside: never read (its page may be gone)
+        bool ok = key >= key_lo && key < kv_hi;                 // outside: never read (its page may be gone)
         const bf16* src = pool;
         if (ok) {
             const int page = bt[key / page_size];
-            src = pool + (((size_t)page * n_layers + layer) * 2 + which) * kv_stride + kvh * head_stride
-                  + (size_t)(key % page_size) * d;
+            ok = page >= 0;                                     // a hole in the block table: zeros, no access before the pool
+            if (ok) src = pool + (((size_t)page * n_layers + layer) * 2 + which) * kv_stride + kvh * head_stride
+                          + (size_t)(key % page_size) * d;
         }
         const uint32_t dst = which ? sV : sK;
         for (int c = kv_c0; c < chunks; c += 2) tc_cp16(tile_addr(dst, KV_BLK, kv_r, c), ok ? src + c * 8 : pool, ok);

@@ -249,6 +249,42 @@ def test_attention_prefill(shape, window, kernel):
     assert torch.all(out[~keep] == 7.0)
 
 
+def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
+    """A page missing from a request's block table (-1) must not be read through: every attention kernel
+    treats the keys of that page as absent (zeros or dropped), leaves the other requests' results exact and
+    returns finite numbers for the request with the hole."""
+    nh, nkv, d, ps = 4, 2, 64, 16
+    dtype = torch.bfloat16
+    lens, new = [200, 150, 300], [200, 1, 300]
+    pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 70)
+    bt2 = bt.clone()
+    bt2[int(slots[0]), 3] = -1          # request 0, prefill: positions 48..63 missing
+    bt2[int(slots[1]), 5] = -1          # request 1, decode
+    n = q.shape[0]
+    dev = dict(pos=t["pos"].to(DEV), seq=t["seq"].to(DEV), slots=slots.to(DEV), bt=bt2.to(DEV), q=q.to(DEV),
+               pool=pool.to(DEV), q_start=t["q_start"].to(DEV), start=t["start"].to(DEV))
+    keep = t["seq"] == 2
+    tr = ops.attention_prefill_tile_rows()
+    tiles = torch.tensor([v for i in (0, 2) for off in range(0, new[i], tr) for v in (i, off)], dtype=torch.int32).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for kernel in ("tma", "tc", "mma"):
+        out = torch.zeros_like(ref, device=DEV)
+        ops.attention_prefill(dev["q"], dev["pool"], 1, out, tiles, tiles.numel() // 2, dev["q_start"], dev["start"],
+                              dev["slots"], dev["bt"], nh, scale, 0, status=status, kernel=kernel)
+        assert int(status.item()) == 0 and torch.isfinite(out.float()).all()
+        close(out[keep], ref[keep], dtype, f"prefill {kernel} beside a hole", rel=1.5e-2)
+    item = torch.tensor([200], dtype=torch.int32, device=DEV)     # request 1's token
+    for kernel in ("mma", "lanes"):
+        out = torch.zeros_like(ref, device=DEV)
+        ops.attention_decode(dev["q"], dev["pool"], 1, out, item, 1, dev["pos"], dev["seq"], dev["slots"], dev["bt"],
+                             nh, scale, kernel=kernel)
+        assert torch.isfinite(out.float()).all() and float(out[200].float().abs().max()) > 0
+    out = torch.zeros_like(ref, device=DEV)
+    ops.attention_plain(dev["q"], dev["pool"], 1, out, dev["pos"], dev["seq"], dev["slots"], dev["bt"], nh, scale)
+    assert torch.isfinite(out.float()).all()
+    close(out[keep], ref[keep], dtype, "plain beside a hole", rel=1e-2)
+
+
 def test_attention_finds_a_far_key_among_hundreds():
     """One key far back is made to dominate: a kernel that skips or misplaces it shows at once."""
     nh, nkv, d, ps = 2, 2, 64, 16
