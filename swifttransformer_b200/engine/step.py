@@ -52,9 +52,17 @@ class StepEntry:
 SPLIT_TARGET = 2   # blocks per SM the split decode attention aims for
 
 
-def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148) -> int:
-    """Parts the key range of a single-token query is cut into, so that the launch fills the GPU."""
+def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148, head_dim: int = 64) -> int:
+    """Parts the key range of a single-token query is cut into, so that the launch fills the GPU.
+
+    Measured at context ~550 with 32 heads: with head size 64 (OPT-1.3B) one part is best from 256 blocks on
+    (batch 8: 1.299 ms per step against 1.323 with two parts: the merge of the parts costs more than the
+    idle SMs); with head size 128 (OPT-6.7B) a block has twice the bytes to move and two parts still win at
+    256 blocks (3.84 against 3.93).  Below that, two blocks per SM (batch 4: three parts, 1.204 against 1.229
+    with two)."""
     blocks = max(1, n_items * nh)
+    if blocks * 64 >= 250 * head_dim:
+        return 1
     s = max(1, (SPLIT_TARGET * sms + blocks - 1) // blocks)
     return min(s, max(1, max_kv // 128), 32)
 
@@ -66,8 +74,8 @@ class AttentionPlan:
         self.items, self.n_items, self.tiles, self.n_tiles = items, n_items, tiles, n_tiles
         self.max_item_kv = max_item_kv
 
-    def splits(self, nh: int) -> int:
-        return choose_splits(self.n_items, nh, self.max_item_kv)
+    def splits(self, nh: int, head_dim: int = 64) -> int:
+        return choose_splits(self.n_items, nh, self.max_item_kv, head_dim=head_dim)
 
 
 class StepContext:

@@ -40,7 +40,7 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
         ops.attention_prefill(q, cache.pool, cache.layer, out, plan.tiles, plan.n_tiles, ctx.q_start,
                               ctx.start_pos, ctx.slots, cache.block_table, nh, scale, window, status=ctx.status)
     if plan.n_items:
-        n_splits = plan.splits(nh)
+        n_splits = plan.splits(nh, d)
         ops.attention_decode(q, cache.pool, cache.layer, out, plan.items, plan.n_items, ctx.positions,
                              ctx.seq_of_token, ctx.slots, cache.block_table, nh, scale, window,
                              n_splits, ctx.scratch_f32(ops.attention_decode_scratch(plan.n_items, nh, d, n_splits))
