@@ -9,12 +9,13 @@
 //   * One thread block per (query token, kv head, split of the key range); the rows of the 16-row
 //     query operand are the query heads that share the kv head (one for multi-head attention, the
 //     whole group for grouped-query attention), zero beyond.
-//   * Each of the block's four warps runs its own pipeline, without block-wide barriers: it takes
-//     every fourth group of 16 keys, gathers their key and value rows page by page with 16-byte
+//   * Each of the block's warps (four, or eight when the launch has few and long blocks: the chain of
+//     groups a warp works through is then half as long) runs its own pipeline, without block-wide barriers: it takes
+//     every fourth (eighth) group of 16 keys, gathers their key and value rows page by page with 16-byte
 //     asynchronous copies into its own ring of shared-memory stages (xor-swizzled rows), and while
 //     later groups are in flight computes S = Q K^T (ldmatrix + mma.sync), the online softmax in
 //     float, and O += P V (ldmatrix.trans + mma.sync) for the oldest one.
-//   * The four warps' (max, sum, O) are merged through shared memory; with several splits the
+//   * The warps' (max, sum, O) are merged through shared memory; with several splits the
 //     block leaves its result in `partial` and the split that arrives last merges them, in split
 //     order (same protocol and layout as attention_decode.cu).
 //
@@ -23,16 +24,14 @@
 // reference (scalar arithmetic there, one warp per head).
 #include "mma_sync.cuh"
 
-#define DM_WARPS 4
-#define DM_THREADS (DM_WARPS * 32)
 #define DM_KEYS 16               // keys per group: the k extent of P V and two n-tiles of S
 #define DM_LOG2E 1.4426950408889634f
 
 template <int DMAX> struct DmStages { static constexpr int value = DMAX == 64 ? 3 : 2; };   // 50 / 68 KB per block
 
 // head_dim <= DMAX, a multiple of 16; FULL: head_dim == DMAX, known when compiling (no tests on it in the loops)
-template <int DMAX, bool FULL>
-__global__ void __launch_bounds__(DM_THREADS)
+template <int DMAX, bool FULL, int DM_WARPS>
+__global__ void __launch_bounds__(DM_WARPS * 32)
 attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
                             float* __restrict__ partial, const int* __restrict__ items,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -42,6 +41,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int d = FULL ? DMAX : d_arg;
     // page_shift: log2(page_size) if that is a power of two, else -1
     constexpr int STAGES = DmStages<DMAX>::value;
+    constexpr int DM_THREADS = DM_WARPS * 32;
     constexpr int STAGE_ELEMS = 2 * DM_KEYS * DMAX;              // keys, then values, of one group
     extern __shared__ __align__(128) unsigned char dm_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(dm_raw);                  // [16][DMAX]
@@ -336,7 +336,8 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 }
 
 template <int DMAX>
-static size_t dm_smem_bytes(int d, int max_pages) {
+static size_t dm_smem_bytes(int d, int max_pages, int warps) {
+    const int DM_WARPS = warps;
     const size_t stages = (size_t)DM_WARPS * DmStages<DMAX>::value * 2 * DM_KEYS * DMAX * sizeof(bf16);
     const size_t merge = (size_t)DM_WARPS * 16 * d * sizeof(float);        // reuses the stages' space
     return 16 * DMAX * sizeof(bf16) + (stages > merge ? stages : merge) + (size_t)max_pages * sizeof(int);
@@ -344,13 +345,14 @@ static size_t dm_smem_bytes(int d, int max_pages) {
 
 ST_EXPORT int st_attention_decode_mma_applies(int d) { return d > 0 && d % 16 == 0 && d <= 128; }
 
-// Same arguments and scratch layout as st_attention_decode.
+// Same arguments and scratch layout as st_attention_decode, and the number of warps per block (4 or 8).
 ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out, float* partial, const int* items,
                                       int n_items, const int* positions, const int* seq_of_token, const int* slots,
                                       const int* block_table, int max_pages, int n_layers, int layer, int nh,
                                       int nkv, int d, int page_size, float scale, int window, int n_splits,
-                                      int* counters, void* stream) {
+                                      int* counters, int warps, void* stream) {
     if (n_items <= 0) return 0;
+    if (warps != 4 && warps != 8) return ST_ERR_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
     if (!st_attention_decode_mma_applies(d)) return ST_ERR_BAD_SIZE;
     if (n_splits > 1 && !partial) return ST_ERR_BAD_ARG;
@@ -364,26 +366,30 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
     for (int b = 0; b < 30; ++b)
         if (page_size == (1 << b)) page_shift = b;
     int rc;
-#define LAUNCH_DM(DMAX, FULL)                                                                                        \
+#define LAUNCH_DM(DMAX, FULL, WARPS)                                                                                 \
     do {                                                                                                             \
-        const size_t smem = dm_smem_bytes<DMAX>(d, max_pages);                                                       \
+        const size_t smem = dm_smem_bytes<DMAX>(d, max_pages, WARPS);                                                \
         if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;                                                              \
         static bool configured = false;                                                                              \
         if (!configured) {                                                                                           \
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL>,                            \
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL, WARPS>,                     \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
             if (e != cudaSuccess) return (int)e;                                                                     \
             configured = true;                                                                                       \
         }                                                                                                            \
-        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL>, grid, dim3(DM_THREADS), smem, s,  \
-                           (const bf16*)q, (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr,  \
-                           items, positions, seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv,  \
-                           d, page_size, page_shift, sl2, window, n_splits, counters);                               \
+        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL, WARPS>, grid, dim3(WARPS * 32),    \
+                           smem, s, (const bf16*)q, (const bf16*)pool, (bf16*)out,                                   \
+                           n_splits > 1 ? partial : (float*)nullptr, items, positions, seq_of_token, slots,          \
+                           block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift, sl2, window,  \
+                           n_splits, counters);                                                                      \
     } while (0)
-    if (d == 64) LAUNCH_DM(64, true);
-    else if (d < 64) LAUNCH_DM(64, false);
-    else if (d == 128) LAUNCH_DM(128, true);
-    else LAUNCH_DM(128, false);
+#define LAUNCH_DM_W(DMAX, FULL)                                                                                      \
+    do { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8); else LAUNCH_DM(DMAX, FULL, 4); } while (0)
+    if (d == 64) LAUNCH_DM_W(64, true);
+    else if (d < 64) LAUNCH_DM_W(64, false);
+    else if (d == 128) LAUNCH_DM_W(128, true);
+    else LAUNCH_DM_W(128, false);
+#undef LAUNCH_DM_W
 #undef LAUNCH_DM
     return rc;
 }

@@ -41,10 +41,12 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
                               ctx.start_pos, ctx.slots, cache.block_table, nh, scale, window, status=ctx.status)
     if plan.n_items:
         n_splits = plan.splits(nh, d)
+        nkv = cache.pool.shape[3]
         ops.attention_decode(q, cache.pool, cache.layer, out, plan.items, plan.n_items, ctx.positions,
                              ctx.seq_of_token, ctx.slots, cache.block_table, nh, scale, window,
                              n_splits, ctx.scratch_f32(ops.attention_decode_scratch(plan.n_items, nh, d, n_splits))
-                             if n_splits > 1 else None)
+                             if n_splits > 1 else None,
+                             warps=ops.decode_warps(plan.n_items, nkv, d, n_splits, plan.max_item_kv))
     return out
 
 

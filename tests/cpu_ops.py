@@ -157,12 +157,16 @@ def attention_plain(q, pool, layer, out, positions, seq_of_token, slots, block_t
     return out
 
 
+def decode_warps(n_items, nkv, d, n_splits, max_kv):
+    return 4
+
+
 def attention_decode_scratch(n_items, nh, d, n_splits):
     return n_items * nh * n_splits * (d + 2) if n_splits > 1 else 0
 
 
 def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_token, slots, block_table, nh,
-                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto"):
+                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto", warps=4):
     idx = items[:n_items].long() if items is not None else torch.arange(n_items)
     tmp = torch.zeros_like(out)
     pos = torch.full_like(positions, -1)
@@ -245,7 +249,7 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
 
 ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
        "qkv_linear_to_cache", "qkv_to_cache",
-       "attention_plain", "attention_decode_scratch", "attention_decode", "attention_prefill_tile_rows",
+       "attention_plain", "attention_decode_scratch", "decode_warps", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]
 
 

@@ -201,11 +201,13 @@ def test_attention_plain(dtype, shape, window):
 @pytest.mark.parametrize("shape", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
 @pytest.mark.parametrize("n_splits", [1, 3, 8])
-@pytest.mark.parametrize("kernel", ["mma", "lanes"])
+@pytest.mark.parametrize("kernel", ["mma", "mma8", "lanes"])
 def test_attention_decode(shape, window, n_splits, kernel):
     nh, nkv, d, ps = shape
-    if kernel == "mma" and (d % 16 or d > 128):
+    if kernel.startswith("mma") and (d % 16 or d > 128):
         pytest.skip("the tensor-core kernel takes head sizes that are multiples of 16 up to 128")
+    warps = 8 if kernel == "mma8" else 4
+    kernel = kernel[:3] if kernel.startswith("mma") else kernel
     dtype = torch.bfloat16
     lens, new = [150, 9, 700, 1, 64], [1, 2, 1, 1, 3]
     pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 40, window)
@@ -215,7 +217,7 @@ def test_attention_decode(shape, window, n_splits, kernel):
     partial = torch.empty(ops.attention_decode_scratch(len(items), nh, d, n_splits) + 1, device=DEV)
     ops.attention_decode(q.to(DEV), pool.to(DEV), 1, out, items.to(DEV), len(items), t["pos"].to(DEV),
                          t["seq"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window, n_splits, partial,
-                         kernel=kernel)
+                         kernel=kernel, warps=warps)
     close(out[items.long()], ref[items.long()], dtype, "attention_decode", rel=1e-2)
     assert torch.all(out[2] == 7.0), "a token that is not in the item list must not be written"
 
