@@ -313,3 +313,109 @@ def test_toy_mixer_with_state_runs_through_the_engine(tmp_path, dtype):
             scale = np.abs(refs[k]).max()
             bad = helpers.first_bad(got[k], refs[k], helpers.TOL[dtype] * scale)
             assert bad is None, (k, bad)
+
+
+# ---------------------------------------------------------------------------------------------
+# A second toy architecture: attention only, but the layers differ.  Even layers see every key, odd layers
+# a window of them with grouped queries, so the model has two cache groups with pages of their own (the
+# window group's pages are given back while a request runs); the last step of the layer order runs layer 0
+# again and reads layer 0's cache instead of writing one.
+# ---------------------------------------------------------------------------------------------
+@register_config
+@dataclasses.dataclass(frozen=True)
+class ToyWindowConfig(ModelConfig):
+    ARCHITECTURE: ClassVar[str] = "ToyWindowForCausalLM"
+    vocab_size: int
+    width: int
+    layers: int
+    heads: int
+    kv_heads: int
+    window: int
+    inner: int
+    max_positions: int
+
+
+@register_model(ToyWindowConfig.ARCHITECTURE)
+def build_toy_window(cfg):
+    W, d = cfg.width, cfg.width // cfg.heads
+    emb = Embedding(cfg.vocab_size, W, W, "tok.weight")
+    pos = POSITION_ENCODINGS.build("learned", max_positions=cfg.max_positions, width=W, offset=0, name="pos.weight")
+    blocks = []
+    for i in range(cfg.layers):
+        odd = i % 2 == 1
+        mixer = MIXERS.build("attention", hidden=W, num_heads=cfg.heads, head_dim=d, bias=True,
+                             num_kv_heads=cfg.kv_heads if odd else cfg.heads, window=cfg.window if odd else None,
+                             names={k: f"l{i}.{k}" for k in "qkvo"})
+        ffn = FEED_FORWARDS.build("dense", hidden=W, inner=cfg.inner, activation="gelu", fc1_name=f"l{i}.up",
+                                  fc2_name=f"l{i}.down", bias=True)
+        blocks.append(BLOCKS.build("pre_norm", mixer=mixer, feed_forward=ffn,
+                                   norm1=NORMS.build("layernorm", width=W, eps=1e-5, affine=True, prefix=f"l{i}.n1"),
+                                   norm2=NORMS.build("layernorm", width=W, eps=1e-5, affine=True, prefix=f"l{i}.n2")))
+    head = OutputHead(cfg.vocab_size, W, W, "head.weight", tied_to="tok.weight")
+    order = [LayerStep(i, i) for i in range(cfg.layers)] + [LayerStep(0, 0, writes_cache=False)]
+    return ModelDef(cfg, emb, pos, blocks, order, NORMS.build("layernorm", width=W, eps=1e-5, affine=True, prefix="fn"), head)
+
+
+def toy_window_plain(model_dir, cfg, ids):
+    """Whole sequence, no cache.  The repeated layer 0 reads the keys and values its first run wrote."""
+    _, w = plain_opt.load_model(model_dir)
+    ln = lambda x, p: plain_opt.layer_norm(x, w[p + ".weight"], w[p + ".bias"], 1e-5)
+    lin = lambda x, p: x @ w[p + ".weight"].T + w[p + ".bias"]
+    x = w["tok.weight"][ids] + w["pos.weight"][np.arange(len(ids))]
+    kv0 = None
+    for step, i in enumerate(list(range(cfg.layers)) + [0]):
+        odd = i % 2 == 1
+        h = ln(x, f"l{i}.n1")
+        q, k, v = (lin(h, f"l{i}.{n}") for n in "qkv")
+        if step == 0:
+            kv0 = (k, v)
+        if step == cfg.layers:
+            k, v = kv0
+        if odd:      # grouped queries: every kv head serves heads / kv_heads query heads
+            d = cfg.width // cfg.heads
+            rep = cfg.heads // cfg.kv_heads
+            k = np.repeat(k.reshape(len(ids), cfg.kv_heads, d), rep, axis=1).reshape(len(ids), -1)
+            v = np.repeat(v.reshape(len(ids), cfg.kv_heads, d), rep, axis=1).reshape(len(ids), -1)
+        a = plain_opt.causal_attention(q, k, v, cfg.heads, window=cfg.window if odd else None)
+        x = x + lin(a, f"l{i}.o")
+        h = ln(x, f"l{i}.n2")
+        x = x + lin(plain_opt.activation(lin(h, f"l{i}.up"), "gelu"), f"l{i}.down")
+    return ln(x, "fn") @ w["tok.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_and_a_shared_cache_run_through_the_engine(tmp_path, dtype):
+    """Two cache groups (all keys; a window of 40 with two kv heads for four query heads), a layer that runs
+    twice and reads its own first cache: whole, in portions, decoded one by one and mixed with page reuse, the
+    logits match a plain implementation; the window group needs far fewer pages than the tokens it saw."""
+    from swifttransformer_b200.engine.replay import TraceSession
+    cfg = ToyWindowConfig(vocab_size=301, width=128, layers=4, heads=4, kv_heads=2, window=40, inner=200,
+                          max_positions=400)
+    d = write_random_model(str(tmp_path / "toyw"), cfg, seed=5, std=0.1)
+    model = load_model(d, dtype, DEV)
+    specs = model.definition.cache_specs()
+    assert [s.window for s in specs] == [None, 40, None, 40]
+    reqs = {"p": helpers.random_tokens(301, 330, 11), "q": helpers.random_tokens(301, 150, 12),
+            "r": helpers.random_tokens(301, 77, 13), "s": helpers.random_tokens(301, 200, 14)}
+    refs = {k: toy_window_plain(d, cfg, np.array(v)) for k, v in reqs.items()}
+    for build in (helpers.trace_whole, helpers.trace_decode_tail, helpers.trace_portions,
+                  lambda r: helpers.trace_mixed(r, max_live=3, chunk=50)):
+        steps = build(reqs)
+        s = TraceSession(d, dtype, helpers.live_token_need(steps), page_size=16, max_requests=3)
+        got = helpers.replay(s, steps)
+        for k in reqs:
+            scale = np.abs(refs[k]).max()
+            bad = helpers.first_bad(got[k], refs[k], helpers.TOL[dtype] * scale)
+            assert bad is None, (build, k, bad)
+        s.runner.check_status()
+    # the window group gives pages back while a request runs: 330 tokens pass through 6 pages of 16
+    from swifttransformer_b200.cache import CacheManager
+    cm = CacheManager(specs, model.dtype, DEV, 16, 24, 2, 400)
+    g_win = next(g for g in cm.groups if g.spec.window == 40)
+    slot = cm.alloc_slot()
+    peak = 0
+    for start in range(0, 330, 10):
+        assert cm.reserve(slot, start, min(330, start + 10))
+        cm.commit(slot, min(330, start + 10))
+        peak = max(peak, g_win.pool.num_pages - g_win.pool.num_free)
+    assert peak <= 5 and cm.groups[0].pool.num_pages - cm.groups[0].pool.num_free == 21
