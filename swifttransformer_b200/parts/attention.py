@@ -57,6 +57,9 @@ class Attention(Mixer):
     names: checkpoint prefixes of the four projections, e.g.
            {"q": "...self_attn.q_proj", "k": ..., "v": ..., "o": "...self_attn.out_proj"};
            each has ``.weight`` [out, in] and, with ``bias``, ``.bias``.
+    qk_position: a position encoding that acts on queries and keys (``apply_qk(q, k, ctx)``, in place on
+           [tokens, heads, head_dim] views, device operations only so that decode steps can still be recorded),
+           or None.
     """
 
     def __init__(self, hidden: int, num_heads: int, head_dim: int, names: Dict[str, str],
@@ -94,7 +97,17 @@ class Attention(Mixer):
 
     def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:
         q = torch.empty((h.shape[0], self.nh * self.d), dtype=h.dtype, device=h.device)
-        if h.dtype == torch.bfloat16 and h.shape[0] <= ops.SKINNY_MAX_ROWS and self.hidden % 8 == 0:
+        encode = getattr(self.qk_position, "apply_qk", None)
+        if encode is not None:
+            # a position encoding of queries and keys: it sees them with their bias, as [tokens, heads,
+            # head_dim] views of the fused projection, changes them in place, and the keys go to the cache after
+            n, qw, kw = h.shape[0], self.nh * self.d, self.nkv * self.d
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv)
+            encode(qkv[:, :qw].view(n, self.nh, self.d), qkv[:, qw:qw + kw].view(n, self.nkv, self.d), ctx)
+            ops.qkv_to_cache(qkv, None, q, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token,
+                             ctx.slots, cache.block_table, self.nh, self.nkv, self.d, ctx.status,
+                             write_kv=cache.writable)
+        elif h.dtype == torch.bfloat16 and h.shape[0] <= ops.SKINNY_MAX_ROWS and self.hidden % 8 == 0:
             # a few tokens: one weight-streaming kernel does the product, the bias and the cache write
             ops.qkv_linear_to_cache(h, self.w_qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions,
                                     ctx.seq_of_token, ctx.slots, cache.block_table, self.nh, self.nkv, self.d,

@@ -28,7 +28,8 @@ class PositionEncoding(Part):
     def max_positions(self) -> Optional[int]:
         return None
 
-    # encodings of queries / keys override this; q, k: [N, heads, head_dim]
+    # encodings of queries / keys override this: apply_qk(q, k, ctx) changes q [N, heads, head_dim] and
+    # k [N, kv_heads, head_dim] in place (ctx.positions holds each token's position; -1 marks padding rows)
     apply_qk = None
 
 

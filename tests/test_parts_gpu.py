@@ -17,6 +17,8 @@ from swifttransformer_b200.engine.step import ModelRunner, StepEntry
 from swifttransformer_b200.models import LayerStep, ModelDef, load_model, register_model, write_random_model
 from swifttransformer_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Delta, Embedding,
                                          Mixer, OutputHead, ResidualStream, StateSpec)
+from swifttransformer_b200.parts.base import FeedForward
+from swifttransformer_b200.parts.position import PositionEncoding
 from swifttransformer_b200.weights import MATRIX, ParamSpec
 
 pytestmark = pytest.mark.gpu
@@ -419,3 +421,164 @@ def test_layers_with_a_window_and_a_shared_cache_run_through_the_engine(tmp_path
         cm.commit(slot, min(330, start + 10))
         peak = max(peak, g_win.pool.num_pages - g_win.pool.num_free)
     assert peak <= 5 and cm.groups[0].pool.num_pages - cm.groups[0].pool.num_free == 21
+
+
+# ---------------------------------------------------------------------------------------------
+# A third toy architecture, for the two remaining kinds of part: a position encoding that acts on queries and
+# keys (pairs of dimensions turned by an angle that grows with the position; the hidden state gets no
+# position at all), and a feed-forward that routes every token to two of its experts.  Both are defined here
+# with device operations only, registered, and run through the engine; nothing in the package knows them.
+# ---------------------------------------------------------------------------------------------
+@register_config
+@dataclasses.dataclass(frozen=True)
+class ToyRoutedConfig(ModelConfig):
+    ARCHITECTURE: ClassVar[str] = "ToyRoutedForCausalLM"
+    vocab_size: int
+    width: int
+    layers: int
+    heads: int
+    experts: int
+    inner: int
+    turn: float
+
+
+@POSITION_ENCODINGS.register("toy_turn")
+class ToyTurn(PositionEncoding):
+    """Dimension pair (2i, 2i+1) of every query and key head is turned by position * turn / (i + 1)."""
+
+    def __init__(self, turn, head_dim):
+        self.turn, self.head_dim = turn, head_dim
+
+    def apply_qk(self, q, k, ctx):
+        i = torch.arange(self.head_dim // 2, device=q.device, dtype=torch.float32)
+        ang = ctx.positions.to(torch.float32)[:, None] * (self.turn / (i + 1))[None, :]      # [N, d/2], float32
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        for x in (q, k):
+            a, b = x[..., 0::2].float(), x[..., 1::2].float()
+            even, odd = a * c - b * s, a * s + b * c            # both before either is stored: float() may be a view
+            x[..., 0::2] = even.to(x.dtype)
+            x[..., 1::2] = odd.to(x.dtype)
+
+
+@FEED_FORWARDS.register("toy_routed")
+class ToyRouted(FeedForward):
+    """y = sum over the two experts e with the largest router logits of softmax-weight_e * W2_e relu(W1_e h);
+    router logits and weights in float32."""
+
+    def __init__(self, hidden, inner, experts, prefix):
+        self.hidden, self.inner, self.experts, self.prefix = hidden, inner, experts, prefix
+
+    def param_specs(self):
+        p = self.prefix
+        return [ParamSpec(p + ".router.weight", (self.experts, self.hidden), MATRIX),
+                ParamSpec(p + ".w1", (self.experts * self.inner, self.hidden), MATRIX),
+                ParamSpec(p + ".w2", (self.experts * self.hidden, self.inner), MATRIX)]
+
+    def bind(self, tensors):
+        p = self.prefix
+        self.router = tensors[p + ".router.weight"]
+        self.w1 = tensors[p + ".w1"].view(self.experts, self.inner, self.hidden)
+        self.w2 = tensors[p + ".w2"].view(self.experts, self.hidden, self.inner)
+
+    def forward(self, h, ctx):
+        logits = h.float() @ self.router.float().t()                       # [N, E]
+        top, idx = torch.topk(logits, 2, dim=-1)
+        gate = torch.softmax(top, dim=-1)                                   # over the two chosen
+        out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+        for e in range(self.experts):                                       # every expert on all rows, masked: no host sync
+            wgt = (gate * (idx == e)).sum(-1, keepdim=True)
+            u = ops.linear(h, self.w1[e].contiguous(), None, "relu")
+            out += wgt * ops.linear(u, self.w2[e].contiguous(), None, "none", torch.float32)
+        return Delta(out.to(h.dtype))
+
+    def param_bytes(self):
+        return (self.router.numel() + self.w1.numel() + self.w2.numel()) * self.w1.element_size()
+
+
+@register_model(ToyRoutedConfig.ARCHITECTURE)
+def build_toy_routed(cfg):
+    W, d = cfg.width, cfg.width // cfg.heads
+    emb = Embedding(cfg.vocab_size, W, W, "tok.weight")
+    turn = POSITION_ENCODINGS.build("toy_turn", turn=cfg.turn, head_dim=d)
+    blocks = []
+    for i in range(cfg.layers):
+        mixer = MIXERS.build("attention", hidden=W, num_heads=cfg.heads, head_dim=d, bias=True, qk_position=turn,
+                             names={k: f"l{i}.{k}" for k in "qkvo"})
+        ffn = FEED_FORWARDS.build("toy_routed", hidden=W, inner=cfg.inner, experts=cfg.experts, prefix=f"l{i}.moe")
+        blocks.append(BLOCKS.build("pre_norm", mixer=mixer, feed_forward=ffn,
+                                   norm1=NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix=f"l{i}.n1"),
+                                   norm2=NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix=f"l{i}.n2")))
+    head = OutputHead(cfg.vocab_size, W, W, "head.weight", tied_to="tok.weight")
+    return ModelDef(cfg, emb, POSITION_ENCODINGS.build("none"), blocks, [LayerStep(i, i) for i in range(cfg.layers)],
+                    NORMS.build("rmsnorm", width=W, eps=1e-6, affine=True, prefix="fn"), head)
+
+
+def toy_routed_plain(model_dir, cfg, ids):
+    _, w = plain_opt.load_model(model_dir)
+    rms = lambda x, g: x / np.sqrt((x ** 2).mean(-1, keepdims=True) + 1e-6) * g
+    T, d = len(ids), cfg.width // cfg.heads
+    ang = np.arange(T)[:, None] * (cfg.turn / (np.arange(d // 2) + 1))[None, :]
+    c, s = np.cos(ang), np.sin(ang)
+
+    def turn(x):
+        x = x.reshape(T, cfg.heads, d).copy()
+        a, b = x[..., 0::2].copy(), x[..., 1::2].copy()
+        x[..., 0::2] = a * c[:, None, :] - b * s[:, None, :]
+        x[..., 1::2] = a * s[:, None, :] + b * c[:, None, :]
+        return x.reshape(T, -1)
+
+    x = w["tok.weight"][ids]
+    sure = T          # positions before this one are routed with a clear margin in every layer
+    for i in range(cfg.layers):
+        h = rms(x, w[f"l{i}.n1.weight"])
+        q, k, v = (h @ w[f"l{i}.{n}.weight"].T + w[f"l{i}.{n}.bias"] for n in "qkv")
+        a = plain_opt.causal_attention(turn(q), turn(k), v, cfg.heads)
+        x = x + a @ w[f"l{i}.o.weight"].T + w[f"l{i}.o.bias"]
+        h = rms(x, w[f"l{i}.n2.weight"])
+        logits = h @ w[f"l{i}.moe.router.weight"].T
+        w1 = w[f"l{i}.moe.w1"].reshape(cfg.experts, cfg.inner, cfg.width)
+        w2 = w[f"l{i}.moe.w2"].reshape(cfg.experts, cfg.width, cfg.inner)
+        y = np.zeros_like(x)
+        for t in range(T):
+            ranked = np.sort(logits[t])[::-1]
+            if ranked[1] - ranked[2] < 0.02 * np.abs(logits[t]).max():
+                sure = min(sure, t)
+            best = np.argsort(-logits[t], kind="stable")[:2]
+            g = np.exp(logits[t][best] - logits[t][best].max())
+            g = g / g.sum()
+            for e, ge in zip(best, g):
+                y[t] += ge * (w2[e] @ np.maximum(w1[e] @ h[t], 0))
+        x = x + y
+    return rms(x, w["fn.weight"]) @ w["tok.weight"].T, sure
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_routed_feed_forward_and_query_key_positions_run_through_the_engine(tmp_path, dtype):
+    from swifttransformer_b200.engine.replay import TraceSession
+    cfg = ToyRoutedConfig(vocab_size=257, width=64, layers=2, heads=2, experts=4, inner=96, turn=0.37)
+    d = write_random_model(str(tmp_path / "toyr"), cfg, seed=25, std=0.2)     # a seed with late near-ties
+    model = load_model(d, dtype, DEV)
+    assert model.graph_safe()
+    reqs = {"p": helpers.random_tokens(257, 90, 21), "q": helpers.random_tokens(257, 41, 22),
+            "r": helpers.random_tokens(257, 64, 23)}
+    refs = {k: toy_routed_plain(d, cfg, np.array(v)) for k, v in reqs.items()}
+    compared = 0
+    for build in (helpers.trace_whole, helpers.trace_decode_tail, helpers.trace_portions,
+                  lambda r: helpers.trace_mixed(r, max_live=3, chunk=20)):
+        steps = build(reqs)
+        s = TraceSession(d, dtype, helpers.live_token_need(steps), page_size=16, max_requests=3)
+        got = helpers.replay(s, steps)
+        for k in reqs:
+            ref, sure = refs[k]
+            scale = np.abs(ref).max()
+            # bfloat16 may route a token whose second and third router logits are nearly tied to another
+            # expert, and every later position reads that token's keys: a request is compared up to its
+            # first such token.  float32 is compared everywhere.
+            n = len(ref) if dtype == "float32" else sure
+            compared += n
+            bad = helpers.first_bad(got[k][:n], ref[:n], helpers.TOL[dtype] * scale)
+            assert bad is None, (k, bad)
+        s.runner.check_status()
+        if build is helpers.trace_decode_tail:
+            assert s.runner.graph_steps > 0, "decode steps of the toy model are recorded and replayed too"
+    assert compared >= 4 * 100
