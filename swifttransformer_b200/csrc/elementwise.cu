@@ -194,6 +194,103 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
     }
 }
 
+// The vector form (width % 4 == 0): a row lives in its block's registers, VPT vectors of four per thread, and
+// a block walks rows blockIdx.x, blockIdx.x + gridDim.x, ...  With VPT == 2 the next row is loaded while
+// this one is reduced and written, so memory stays busy across the two block-wide reductions.  Gain, shift
+// and the bias of delta are fetched once per block, before the wait for the kernel before this one (no
+// kernel writes them).  Every row is computed by the same code in the same order whatever the number of
+// rows: the result of a token does not depend on the batch.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(512, VPT == 2 ? 2 : 1) add_norm_vec_kernel(const float* x, const int* __restrict__ rows,
+                                    const T* __restrict__ delta, const float* __restrict__ delta_bias,
+                                    float* resid_out, const float* __restrict__ gamma,
+                                    const float* __restrict__ beta, float eps, int kind, int width, int n_rows,
+                                    T* __restrict__ out_act, float* out_f32) {
+    __shared__ float scratch[32];
+    constexpr bool AHEAD = VPT == 2;
+    const int nvec = width >> 2;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool ok[VPT];
+    float4 g[VPT], b[VPT], db[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        ok[j] = v < nvec;
+        g[j] = (kind != 2 && gamma && ok[j]) ? load4(gamma + 4 * v) : make_float4(1.f, 1.f, 1.f, 1.f);
+        b[j] = (kind != 2 && beta && ok[j]) ? load4(beta + 4 * v) : zero4;
+        db[j] = (delta_bias && ok[j]) ? load4(delta_bias + 4 * v) : zero4;
+    }
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    auto fetch = [&](int r, float4* xa, float4* da) -> size_t {
+        const size_t i = rows ? (size_t)rows[r] : (size_t)r;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            xa[j] = ok[j] ? load4_cg(x + i * width + 4 * v) : zero4;
+            da[j] = (delta && ok[j]) ? load4_cg(delta + i * width + 4 * v) : zero4;
+        }
+        return i;
+    };
+    float4 xa[VPT], da[VPT], xn[AHEAD ? VPT : 1], dn[AHEAD ? VPT : 1];
+    int r = blockIdx.x;
+    size_t i = 0, i_next = 0;
+    if (AHEAD && r < n_rows) i = fetch(r, xa, da);
+    for (; r < n_rows; r += gridDim.x) {
+        if (AHEAD) {
+            if (r + (int)gridDim.x < n_rows) i_next = fetch(r + gridDim.x, xn, dn);
+        } else {
+            i = fetch(r, xa, da);
+        }
+        float4 sv[VPT];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            sv[j] = add4(add4(xa[j], da[j]), db[j]);
+            if (ok[j]) {
+                sum += (sv[j].x + sv[j].y) + (sv[j].z + sv[j].w);
+                if (resid_out) store4(resid_out + i * width + 4 * (threadIdx.x + j * blockDim.x), sv[j]);
+            }
+        }
+        float mean = 0.f, rstd = 1.f;
+        if (kind == 0) {
+            mean = block_sum(sum, scratch) / (float)width;
+            float sq = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                if (ok[j]) {
+                    const float d0 = sv[j].x - mean, d1 = sv[j].y - mean, d2 = sv[j].z - mean, d3 = sv[j].w - mean;
+                    sq += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+                }
+            }
+            rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+        } else if (kind == 1) {
+            float sq = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+                if (ok[j]) sq += (sv[j].x * sv[j].x + sv[j].y * sv[j].y) + (sv[j].z * sv[j].z + sv[j].w * sv[j].w);
+            rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+        }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (!ok[j]) continue;
+            float4 y = sv[j];
+            if (kind != 2) {
+                y = make_float4((y.x - mean) * rstd * g[j].x + b[j].x, (y.y - mean) * rstd * g[j].y + b[j].y,
+                                (y.z - mean) * rstd * g[j].z + b[j].z, (y.w - mean) * rstd * g[j].w + b[j].w);
+            }
+            const size_t o = (size_t)r * width + 4 * (threadIdx.x + j * blockDim.x);
+            if (out_act) store4(out_act + o, y);
+            if (out_f32) store4(out_f32 + o, y);
+        }
+        if (AHEAD) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) { xa[j] = xn[j]; da[j] = dn[j]; }
+            i = i_next;
+        }
+    }
+}
+
 template <typename T>
 static int launch_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias,
                            float* resid_out, const float* gamma, const float* beta, float eps, int kind, int n_rows,
@@ -202,6 +299,19 @@ static int launch_add_norm(const float* x, const int* rows, const void* delta, c
     const bool vec = width % 4 == 0 && aligned16(x) && aligned16(delta) && aligned16(delta_bias) &&
                      aligned16(resid_out) && aligned16(gamma) && aligned16(beta) && aligned16(out_act) &&
                      aligned16(out_f32);
+    if (vec && width <= 8192) {
+        // rows in registers: two vectors of four per thread up to 4096 wide, four beyond; a block takes several rows
+        const int vpt = width <= 4096 ? 2 : 4;
+        int block = (width / (4 * vpt) + 31) / 32 * 32;
+        if (block < 64) block = 64;
+        int grid = 148 * (vpt == 2 ? 4 : 2);
+        if (grid > n_rows) grid = n_rows;
+        if (vpt == 2)
+            return st_launch_pdl("norm", add_norm_vec_kernel<T, 2>, dim3(grid), dim3(block), 0, s, x, rows, (const T*)delta,
+                                 delta_bias, resid_out, gamma, beta, eps, kind, width, n_rows, (T*)out_act, out_f32);
+        return st_launch_pdl("norm", add_norm_vec_kernel<T, 4>, dim3(grid), dim3(block), 0, s, x, rows, (const T*)delta,
+                             delta_bias, resid_out, gamma, beta, eps, kind, width, n_rows, (T*)out_act, out_f32);
+    }
     int block = vec ? (width / 8 + 31) / 32 * 32 : 256;   // vector path: two vectors per thread and round
     if (block > 512) block = 512;
     if (block < 64) block = 64;
