@@ -49,22 +49,31 @@ class StepEntry:
     want: Sequence[int] = ()        # places among `tokens` whose logits are wanted
 
 
-SPLIT_TARGET = 2   # blocks per SM the split decode attention aims for
+# Keys one block of the decode attention walks alone before the key range is cut into parts (for head sizes
+# up to 64, where a block has eight warps; half of it beyond).  Recorded decode steps are keyed by the number
+# of such spans the longest request needs, so the cut follows the real lengths, not the longest possible one.
+KEYS_PER_BLOCK = 768
 
 
 def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148, head_dim: int = 64) -> int:
-    """Parts the key range of a single-token query is cut into, so that the launch fills the GPU.
+    """Parts the key range of a single-token query is cut into.
 
-    Measured at context ~550 with 32 heads: with head size 64 (OPT-1.3B) one part is best from 256 blocks on
-    (batch 8: 1.299 ms per step against 1.323 with two parts: the merge of the parts costs more than the
-    idle SMs); with head size 128 (OPT-6.7B) a block has twice the bytes to move and two parts still win at
-    256 blocks (3.84 against 3.93).  Below that, two blocks per SM (batch 4: three parts, 1.204 against 1.229
-    with two)."""
+    Measured on one B200 at context ~550 with 32 heads.  Head size 64 (OPT-1.3B, tensor-core kernel with
+    eight warps per block): cutting costs a merge (a trip through global memory and an atomic) and one part
+    is best at every batch (ms per step, one part against two blocks per SM: batch 1: 1.043 / 1.084,
+    4: 1.116 / 1.167, 8: 1.299 / 1.323); longer ranges are cut so that a block walks about KEYS_PER_BLOCK
+    keys, as long as the launch stays within two blocks per SM.  Head size 128 (OPT-6.7B, lanes kernel, whose
+    blocks walk their keys more slowly): two blocks per SM, parts of at least 128 keys (batch 1: 3.20 with
+    ten parts against 3.28 with two; batch 8: 3.78 with two against 3.86 with one)."""
     blocks = max(1, n_items * nh)
     if blocks * 64 >= 250 * head_dim:
         return 1
-    s = max(1, (SPLIT_TARGET * sms + blocks - 1) // blocks)
-    return min(s, max(1, max_kv // 128), 32)
+    room = max(1, (2 * sms + blocks - 1) // blocks)
+    if head_dim <= 64:
+        want = (max_kv + KEYS_PER_BLOCK - 1) // KEYS_PER_BLOCK
+    else:
+        want = max(1, max_kv // 128)
+    return max(1, min(want, room, 32))
 
 
 class AttentionPlan:
@@ -141,7 +150,7 @@ class _DecodeGraph:
 
     FIELDS = ("token_ids", "positions", "start_pos", "kv_len", "slots")
 
-    def __init__(self, runner: "ModelRunner", cap: int):
+    def __init__(self, runner: "ModelRunner", cap: int, max_kv: int):
         self.runner, self.cap = runner, cap
         self.staging = _Staging(6 * cap, runner.device)
         dev = runner.device
@@ -154,7 +163,7 @@ class _DecodeGraph:
         self.token_from = d[5 * cap:6 * cap]     # per token: index into the previous step's sampled tokens, or -1
         ctx.seq_of_token, ctx.q_start, ctx.want_rows = ar[:cap], ar, ar[:cap]
         ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, dev
-        ctx._plan = AttentionPlan(None, cap, None, 0, runner.cache.max_seq_len)
+        ctx._plan = AttentionPlan(None, cap, None, 0, max_kv)
         ctx._scratch_owner = self
         self.ctx = ctx
         self._keep = ar
@@ -241,7 +250,7 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch_buf: Optional[torch.Tensor] = None
         self._entries = cache.entries()
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[Any, _DecodeGraph] = {}      # (rows, spans of KEYS_PER_BLOCK keys) -> recorded step
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_cuda_graphs else None
         self.steps_run = 0
         self.graph_steps = 0
@@ -325,9 +334,11 @@ class ModelRunner:
         before = ops.launch_count()
         bucket = self._graph_bucket(entries)
         if bucket:
-            if bucket not in self._graphs:
-                self._graphs[bucket] = _DecodeGraph(self, bucket)
-            dg = self._graphs[bucket]
+            spans = max(-(-(e.start_pos + 1) // KEYS_PER_BLOCK) for e in entries)
+            key = (bucket, spans)
+            if key not in self._graphs:
+                self._graphs[key] = _DecodeGraph(self, bucket, min(spans * KEYS_PER_BLOCK, self.cache.max_seq_len))
+            dg = self._graphs[key]
             logits = dg.run(entries, feedback)
             self.graph_steps += 1
             self.kernels_last_step = dg.kernels
