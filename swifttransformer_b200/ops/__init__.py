@@ -401,10 +401,11 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
 
 
 def decode_warps(n_items: int, nkv: int, d: int, n_splits: int, max_kv: int) -> int:
-    """Warps per block for the tensor-core decode attention.  Eight when the launch is one wave of blocks
-    that each walk a long key range alone (measured on OPT-1.3B, batch 8, context 550: 1.256 ms per step
-    against 1.299 with four; batch 64: 2.61 against 2.46, batch 1 with four parts: 1.18 against 1.11)."""
-    return 8 if (n_splits == 1 and d <= 64 and n_items * nkv <= 2 * 148 and max_kv >= 256) else 4
+    """Warps per block for the tensor-core decode attention.  Eight when the launch is at most two blocks per
+    SM and the key ranges are long: a warp's chain of groups is then half as long (measured on OPT-1.3B,
+    ms per step, eight against four: batch 8 at context 550: 1.256 / 1.299; batch 1 at context 1800 with
+    three parts: 1.131 / 1.230; with many blocks four are better, batch 64: 2.61 / 2.46)."""
+    return 8 if (d <= 64 and n_items * nkv * n_splits <= 2 * 148 and max_kv >= 256) else 4
 
 
 def attention_prefill_tile_rows() -> int:
