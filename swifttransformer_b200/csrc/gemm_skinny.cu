@@ -38,7 +38,7 @@ namespace cg = cooperative_groups;
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
-#define SK_UNROLL 2
+#define SK_UNROLL 2      // k-blocks per round with up to 8 tokens; one with more (registers: four blocks per SM either way)
 
 struct QkvTarget {
     bf16* q_out;               // [M, qw]
@@ -67,7 +67,7 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
 
 // KFULL: K is a multiple of 32 (known when compiling: no test on k inside a block of 32)
 template <int NT, bool QKV, bool KFULL>
-__global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 4 : 2)
+__global__ void __launch_bounds__(SK_THREADS, NT <= 2 ? 4 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
                    void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt) {
     __shared__ float red[SK_WARPS][16][8 * NT + 1];
@@ -98,10 +98,11 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     // kernel's own first round of weight loads is issued before it waits for its predecessor
     // (weights are written by no kernel, so the memory system stays busy across the kernel
     // boundary); the activations are read after the wait.
-    struct Round { uint4 ua[SK_UNROLL], ub[SK_UNROLL], xb[SK_UNROLL][NT]; };
+    constexpr int UNR = NT == 1 ? SK_UNROLL : 1;
+    struct Round { uint4 ua[UNR], ub[UNR], xb[UNR][NT]; };
     auto issue_w = [&](Round& r, int kb0) {
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < UNR; ++u) {
             const int kb = kb0 + u * SK_WARPS;
             const bool ok = kb < nkb && (KFULL || kb * 32 + t * 8 < K);   // K % 8 == 0: a 16-byte piece is inside or outside as a whole
             r.ua[u] = ok ? ldg_stream(wa + kb * 32) : zero;
@@ -110,7 +111,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     };
     auto issue_x = [&](Round& r, int kb0) {
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < UNR; ++u) {
             const int kb = kb0 + u * SK_WARPS;
             const bool ok = kb < nkb && (KFULL || kb * 32 + t * 8 < K);
 #pragma unroll
@@ -120,7 +121,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     };
     auto consume = [&](const Round& r) {
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < UNR; ++u) {
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 mma16816(acc[j], r.ua[u].x, r.ub[u].x, r.ua[u].y, r.ub[u].y, r.xb[u][j].x, r.xb[u][j].y);
@@ -129,7 +130,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         }
     };
     ST_PDL_TRIGGER();
-    constexpr int STEP = SK_WARPS * SK_UNROLL;
+    constexpr int STEP = SK_WARPS * UNR;
     const int kb_first = kb_begin + warp;
     Round ra, rb;
     issue_w(ra, kb_first);          // out-of-range blocks load nothing
