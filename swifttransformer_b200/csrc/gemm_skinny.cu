@@ -38,7 +38,7 @@ namespace cg = cooperative_groups;
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
-#define SK_UNROLL 2      // k-blocks per round with up to 8 tokens; one with more (registers: four blocks per SM either way)
+#define SK_UNROLL 1      // k-blocks per round with up to 8 tokens; one with more (registers: four blocks per SM either way)
 
 struct QkvTarget {
     bf16* q_out;               // [M, qw]
