@@ -132,8 +132,9 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     ST_PDL_TRIGGER();
     constexpr int STEP = SK_WARPS * UNR;
     const int kb_first = kb_begin + warp;
-    Round ra, rb;
+    Round ra, rb, rc;
     issue_w(ra, kb_first);          // out-of-range blocks load nothing
+    if (NT == 1) issue_w(rb, kb_first + STEP);
     // What the epilogue needs and no kernel of the step writes is fetched now, under the weight stream,
     // instead of at the end, where every dependent load is a round trip on the critical path: the bias
     // of this thread's output feature (the same in all of its epilogue turns, 256 being a multiple of
@@ -148,13 +149,27 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
             page_pre = tgt.block_table[(size_t)tgt.slots[tgt.seq_of_token[m]] * tgt.max_pages + pos_pre / tgt.page_size];
     }
     ST_PDL_WAIT();
-    issue_x(ra, kb_first);
-    for (int kb0 = kb_first; kb0 < nkb; kb0 += 2 * STEP) {
-        const bool more_b = kb0 + STEP < nkb;
-        if (more_b) { issue_w(rb, kb0 + STEP); issue_x(rb, kb0 + STEP); }
-        consume(ra);
-        if (kb0 + 2 * STEP < nkb) { issue_w(ra, kb0 + 2 * STEP); issue_x(ra, kb0 + 2 * STEP); }
-        if (more_b) consume(rb);
+    if (NT == 1) {
+        // three rounds in flight (two of them asked for before the wait)
+        issue_x(ra, kb_first);
+        issue_x(rb, kb_first + STEP);
+        for (int kb0 = kb_first; kb0 < nkb; kb0 += 3 * STEP) {
+            if (kb0 + 2 * STEP < nkb) { issue_w(rc, kb0 + 2 * STEP); issue_x(rc, kb0 + 2 * STEP); }
+            consume(ra);
+            if (kb0 + 3 * STEP < nkb) { issue_w(ra, kb0 + 3 * STEP); issue_x(ra, kb0 + 3 * STEP); }
+            if (kb0 + STEP < nkb) consume(rb);
+            if (kb0 + 4 * STEP < nkb) { issue_w(rb, kb0 + 4 * STEP); issue_x(rb, kb0 + 4 * STEP); }
+            if (kb0 + 2 * STEP < nkb) consume(rc);
+        }
+    } else {
+        issue_x(ra, kb_first);
+        for (int kb0 = kb_first; kb0 < nkb; kb0 += 2 * STEP) {
+            const bool more_b = kb0 + STEP < nkb;
+            if (more_b) { issue_w(rb, kb0 + STEP); issue_x(rb, kb0 + STEP); }
+            consume(ra);
+            if (kb0 + 2 * STEP < nkb) { issue_w(ra, kb0 + 2 * STEP); issue_x(ra, kb0 + 2 * STEP); }
+            if (more_b) consume(rb);
+        }
     }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
