@@ -64,7 +64,7 @@ def build_parser(prog: str = "run_gpt") -> argparse.ArgumentParser:
     ap.add_argument("--top_k", type=int, default=0)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--max_batch_tokens", type=int, default=2048, help="token budget of one step")
-    ap.add_argument("--chunk_size", type=int, default=512, help="longest prompt portion in one step")
+    ap.add_argument("--chunk_size", type=int, default=2048, help="longest prompt portion in one step")
     return ap
 
 
