@@ -49,6 +49,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     // the token's position, slot and page numbers are inputs of the step that no kernel of the step writes:
     // they are fetched before the wait for the kernel before this one; queries, keys and values after it
     const int t = items ? items[blockIdx.x] : blockIdx.x;
+    if (t < 0) return;            // a padding entry of a fixed-shape step
     const int h = blockIdx.y, split = blockIdx.z;
     const int kvh = h / (nh / nkv);
     const int pos = positions[t];
@@ -250,7 +251,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, bf16
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int t = items ? items[blockIdx.x] : blockIdx.x;
-    if (positions[t] < 0) return;
+    if (t < 0 || positions[t] < 0) return;
     const int h = blockIdx.y;
     const float* part = partial + ((size_t)blockIdx.x * nh + h) * n_splits * (d + 2);
     float mm = -INFINITY;

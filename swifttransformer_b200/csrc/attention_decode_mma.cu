@@ -54,6 +54,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     // that no kernel of the step writes: this chain of dependent loads runs before the wait for the kernel
     // before this one, under that kernel's tail.  The queries and this step's keys and values come after.
     const int t = items ? items[blockIdx.x] : blockIdx.x;
+    if (t < 0) return;            // a padding entry of a fixed-shape step
     const int group = nh / nkv;                                   // query heads per kv head
     const int chunks_per_kv = (group + 15) / 16;
     const int kvh = blockIdx.y / chunks_per_kv;

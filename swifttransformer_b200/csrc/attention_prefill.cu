@@ -41,6 +41,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
     const int h = blockIdx.x, kvh = h / (nh / nkv);
     const int tok0 = q_start[seq] + off;
     const int n_rows = min(PF_BM, q_start[seq + 1] - tok0);
+    if (n_rows <= 0) return;      // a padding tile of a fixed-shape step (the whole block leaves before any barrier)
     const int pos0 = start_pos[seq] + off;           // position of the tile's first query
     const int pos_last = pos0 + n_rows - 1;
     const int* bt = block_table + (size_t)slots[seq] * max_pages;

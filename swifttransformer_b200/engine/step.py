@@ -145,28 +145,11 @@ class _Staging:
 GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 
 
-class _DecodeGraph:
-    """One recorded decode step for up to ``cap`` requests."""
+class _RecordedStep:
+    """A step of fixed shape recorded as a CUDA graph: its context, its scratch memory, the recording."""
 
-    FIELDS = ("token_ids", "positions", "start_pos", "kv_len", "slots")
-
-    def __init__(self, runner: "ModelRunner", cap: int, max_kv: int):
-        self.runner, self.cap = runner, cap
-        self.staging = _Staging(6 * cap, runner.device)
-        dev = runner.device
-        ar = torch.arange(cap + 1, dtype=torch.int32, device=dev)
-        d = self.staging.dev
-        ctx = StepContext()
-        ctx.n_tokens = ctx.n_seqs = ctx.n_want = cap
-        ctx.token_ids, ctx.positions = d[0:cap], d[cap:2 * cap]
-        ctx.start_pos, ctx.kv_len, ctx.slots = d[2 * cap:3 * cap], d[3 * cap:4 * cap], d[4 * cap:5 * cap]
-        self.token_from = d[5 * cap:6 * cap]     # per token: index into the previous step's sampled tokens, or -1
-        ctx.seq_of_token, ctx.q_start, ctx.want_rows = ar[:cap], ar, ar[:cap]
-        ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, dev
-        ctx._plan = AttentionPlan(None, cap, None, 0, max_kv)
-        ctx._scratch_owner = self
-        self.ctx = ctx
-        self._keep = ar
+    def _init_recording(self, runner: "ModelRunner") -> None:
+        self.runner = runner
         self._scratch_buf: Optional[torch.Tensor] = None
         self._frozen = False
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -179,25 +162,6 @@ class _DecodeGraph:
                 raise RuntimeError("a recorded step asked for more scratch memory than when it was recorded")
             self._scratch_buf = torch.empty(max(n, 1), dtype=torch.float32, device=self.runner.device)
         return self._scratch_buf
-
-    def fill(self, entries: Sequence[StepEntry], token_from: Optional[Sequence[int]] = None) -> None:
-        cap, b = self.cap, len(entries)
-        h = self.staging.begin()
-        h[0:cap] = 0
-        h[cap:2 * cap] = -1                      # padding entries: position -1, skipped by every kernel
-        h[2 * cap:5 * cap] = 0
-        for i, e in enumerate(entries):
-            h[i] = e.tokens[0]
-            h[cap + i] = e.start_pos
-            h[2 * cap + i] = e.start_pos
-            h[3 * cap + i] = e.start_pos + 1
-            h[4 * cap + i] = e.slot
-        if token_from is not None:
-            h[5 * cap:6 * cap] = -1
-            h[5 * cap:5 * cap + b] = token_from
-            self.staging.commit(6 * cap)
-        else:
-            self.staging.commit(5 * cap)
 
     def record(self) -> None:
         r = self.runner
@@ -222,6 +186,50 @@ class _DecodeGraph:
         self.kernels = ops.launch_count() - before
         self.graph = g
 
+
+class _DecodeGraph(_RecordedStep):
+    """One recorded decode step for up to ``cap`` requests."""
+
+    FIELDS = ("token_ids", "positions", "start_pos", "kv_len", "slots")
+
+    def __init__(self, runner: "ModelRunner", cap: int, max_kv: int):
+        self._init_recording(runner)
+        self.cap = cap
+        self.staging = _Staging(6 * cap, runner.device)
+        dev = runner.device
+        ar = torch.arange(cap + 1, dtype=torch.int32, device=dev)
+        d = self.staging.dev
+        ctx = StepContext()
+        ctx.n_tokens = ctx.n_seqs = ctx.n_want = cap
+        ctx.token_ids, ctx.positions = d[0:cap], d[cap:2 * cap]
+        ctx.start_pos, ctx.kv_len, ctx.slots = d[2 * cap:3 * cap], d[3 * cap:4 * cap], d[4 * cap:5 * cap]
+        self.token_from = d[5 * cap:6 * cap]     # per token: index into the previous step's sampled tokens, or -1
+        ctx.seq_of_token, ctx.q_start, ctx.want_rows = ar[:cap], ar, ar[:cap]
+        ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, dev
+        ctx._plan = AttentionPlan(None, cap, None, 0, max_kv)
+        ctx._scratch_owner = self
+        self.ctx = ctx
+        self._keep = ar
+
+    def fill(self, entries: Sequence[StepEntry], token_from: Optional[Sequence[int]] = None) -> None:
+        cap, b = self.cap, len(entries)
+        h = self.staging.begin()
+        h[0:cap] = 0
+        h[cap:2 * cap] = -1                      # padding entries: position -1, skipped by every kernel
+        h[2 * cap:5 * cap] = 0
+        for i, e in enumerate(entries):
+            h[i] = e.tokens[0]
+            h[cap + i] = e.start_pos
+            h[2 * cap + i] = e.start_pos
+            h[3 * cap + i] = e.start_pos + 1
+            h[4 * cap + i] = e.slot
+        if token_from is not None:
+            h[5 * cap:6 * cap] = -1
+            h[5 * cap:5 * cap + b] = token_from
+            self.staging.commit(6 * cap)
+        else:
+            self.staging.commit(5 * cap)
+
     def run(self, entries: Sequence[StepEntry], feedback=None) -> torch.Tensor:
         self.fill(entries, feedback[1] if feedback else None)
         if self.graph is None:
@@ -230,6 +238,48 @@ class _DecodeGraph:
             ops.gather_where_i32(self.ctx.token_ids, self.token_from, feedback[0])
         self.graph.replay()
         return self.logits[:len(entries)]
+
+
+class _StepGraph(_RecordedStep):
+    """One recorded step of a padded shape, for steps that are not decode-only: ``n_pad`` tokens (a multiple
+    of the attention tile), ``b_pad`` requests, ``i_pad`` single-token attention entries, ``w_pad`` wanted
+    rows.  What a step does not fill is padding that every kernel skips (see ModelRunner._pack)."""
+
+    def __init__(self, runner: "ModelRunner", n_pad: int, b_pad: int, i_pad: int, w_pad: int, max_kv: int):
+        self._init_recording(runner)
+        self.n_pad = n_pad
+        self.lay = lay = runner._layout(n_pad, b_pad, w_pad)
+        self.staging = _Staging(lay["total"], runner.device)
+        d = self.staging.dev
+
+        def view(name):
+            o, n = lay[name]
+            return d[o:o + n]
+
+        t_pad = lay["tiles"][1] // 2
+        ctx = StepContext()
+        ctx.n_tokens, ctx.n_seqs, ctx.n_want = n_pad, b_pad, w_pad
+        ctx.token_ids, ctx.positions, ctx.seq_of_token = view("token_ids"), view("positions"), view("seq_of_token")
+        ctx.q_start, ctx.start_pos, ctx.kv_len, ctx.slots = (view("q_start"), view("start_pos"), view("kv_len"),
+                                                             view("slots"))
+        ctx.want_rows = view("want_rows") if w_pad else None
+        ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, runner.device
+        ctx._plan = AttentionPlan(view("items")[:i_pad], i_pad, view("tiles"), t_pad, max_kv)
+        ctx._scratch_owner = self
+        self.ctx = ctx
+        self.token_from = view("token_from")
+
+    def run(self, entries: Sequence[StepEntry], feedback=None) -> Optional[torch.Tensor]:
+        r = self.runner
+        h = self.staging.begin()
+        info = r._pack(entries, self.lay, h, feedback)
+        self.staging.commit(self.lay["total"])
+        if self.graph is None:
+            self.record()
+        if feedback is not None:
+            ops.gather_where_i32(self.ctx.token_ids, self.token_from, feedback[0])
+        self.graph.replay()
+        return self.logits[:info["W"]] if info["W"] else None
 
 
 class ModelRunner:
@@ -251,6 +301,11 @@ class ModelRunner:
         self._scratch_buf: Optional[torch.Tensor] = None
         self._entries = cache.entries()
         self._graphs: Dict[Any, _DecodeGraph] = {}      # (rows, spans of KEYS_PER_BLOCK keys) -> recorded step
+        # recorded steps of padded shapes for everything else (prompt portions, mixed steps); bounded in number:
+        # a shape beyond the bound runs eagerly
+        self._step_graphs: Dict[Any, _StepGraph] = {}
+        self.max_step_graphs = 48
+        self.padded_graph_steps = 0
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_cuda_graphs else None
         self.steps_run = 0
         self.graph_steps = 0
@@ -278,7 +333,8 @@ class ModelRunner:
     def h2d_bytes(self) -> int:
         """Bytes of step metadata copied host -> device so far."""
         return (self._staging.bytes_copied + self._upd_staging.bytes_copied
-                + sum(g.staging.bytes_copied for g in self._graphs.values()))
+                + sum(g.staging.bytes_copied for g in self._graphs.values())
+                + sum(g.staging.bytes_copied for g in self._step_graphs.values()))
 
     # --------------------------------------------------------------- step
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -343,9 +399,15 @@ class ModelRunner:
             self.graph_steps += 1
             self.kernels_last_step = dg.kernels
         else:
-            ctx = self._build_context(entries, feedback)
-            logits = self.model.forward(ctx, self._entries)
-            self.kernels_last_step = ops.launch_count() - before
+            sg = self._padded_graph(entries)
+            if sg is not None:
+                logits = sg.run(entries, feedback)
+                self.padded_graph_steps += 1
+                self.kernels_last_step = sg.kernels
+            else:
+                ctx = self._build_context(entries, feedback)
+                logits = self.model.forward(ctx, self._entries)
+                self.kernels_last_step = ops.launch_count() - before
         for e in entries:
             self.cache.commit(e.slot, e.start_pos + len(e.tokens))
         self.steps_run += 1
@@ -362,6 +424,33 @@ class ModelRunner:
             if cap >= b:
                 return cap
         return 0
+
+    def _padded_graph(self, entries: Sequence[StepEntry]) -> Optional[_StepGraph]:
+        """The recorded step whose padded shape takes these entries, made if need be; None: run eagerly.
+        Launching a step's ~190 kernels and library calls one by one costs the host ~2.8 ms whatever the step's
+        size; replaying a recording costs a few tens of microseconds."""
+        if not self.use_cuda_graphs:
+            return None
+        lens = [len(e.tokens) for e in entries]
+        n, b = sum(lens), len(entries)
+        w = sum(len(e.want) for e in entries)
+        n_items = sum(x for x in lens if x < SHORT_PORTION)
+        item_kv = max((e.start_pos + x for e, x in zip(entries, lens) if x < SHORT_PORTION), default=0)
+        n_pad = -(-n // self.tile_rows) * self.tile_rows
+        b_pad = next((c for c in GRAPH_BUCKETS if c >= b), None)
+        if b_pad is None:
+            return None
+        i_pad = -(-n_items // 16) * 16
+        w_pad = 0 if w == 0 else (b_pad if w <= b_pad else n_pad)
+        spans = -(-item_kv // KEYS_PER_BLOCK)
+        key = (n_pad, b_pad, i_pad, w_pad, spans)
+        sg = self._step_graphs.get(key)
+        if sg is None:
+            if len(self._step_graphs) >= self.max_step_graphs:
+                return None
+            sg = self._step_graphs[key] = _StepGraph(self, n_pad, b_pad, i_pad, w_pad,
+                                                     min(max(spans, 1) * KEYS_PER_BLOCK, self.cache.max_seq_len))
+        return sg
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault (a hole in a block table).  Synchronises."""
@@ -391,17 +480,21 @@ class ModelRunner:
                 d = self._upd_staging.dev
                 ops.scatter_i32(g.block_table, d[1:1 + n], d[1 + n:1 + 2 * n], d[0:1], n)
 
-    def _build_context(self, entries: Sequence[StepEntry], feedback=None) -> StepContext:
+    def _pack(self, entries: Sequence[StepEntry], lay: Dict[str, Any], h: np.ndarray, feedback=None):
+        """Write the step's index arrays into the staging buffer ``h`` laid out by ``lay``.  Where the layout
+        has room for more than the step brings (a recorded step of padded shape), the rest is filled with
+        entries every kernel skips: tokens at position -1, requests without tokens, tiles without rows,
+        single-token entries -1.  Returns what describes the step to the host."""
         B = len(entries)
         lens = [len(e.tokens) for e in entries]
         N = sum(lens)
-        W = sum(len(e.want) for e in entries)
-        lay = self._layout(N, B, W)
-        h = self._staging.begin()
 
-        def put(name, values):
-            o, _ = lay[name]
-            h[o:o + len(values)] = values
+        def put(name, values, fill):
+            o, n = lay[name]
+            k = len(values)
+            h[o:o + k] = values
+            if k < n:
+                h[o + k:o + n] = fill
 
         q_start = np.zeros(B + 1, dtype=np.int32)
         np.cumsum(lens, out=q_start[1:])
@@ -416,14 +509,14 @@ class ModelRunner:
             pos[a:b] = np.arange(e.start_pos, e.start_pos + lens[i], dtype=np.int32)
             seq[a:b] = i
             want_rows.extend(int(a) + w for w in e.want)
-        put("token_ids", tok)
-        put("positions", pos)
-        put("seq_of_token", seq)
-        put("q_start", q_start)
-        put("start_pos", start)
-        put("kv_len", start + np.asarray(lens, dtype=np.int32))
-        put("slots", [e.slot for e in entries])
-        put("want_rows", want_rows)
+        put("token_ids", tok, 0)
+        put("positions", pos, -1)
+        put("seq_of_token", seq, 0)
+        put("q_start", q_start, N)
+        put("start_pos", start, 0)
+        put("kv_len", start + np.asarray(lens, dtype=np.int32), 0)
+        put("slots", [e.slot for e in entries], 0)
+        put("want_rows", want_rows, 0)
         # attention plan: short portions token by token, long ones in tiles (longest key range first)
         items: List[int] = []
         tiles: List[tuple] = []
@@ -436,10 +529,22 @@ class ModelRunner:
                 for off in range(0, lens[i], self.tile_rows):
                     tiles.append((e.start_pos + min(off + self.tile_rows, lens[i]), i, off))
         tiles.sort(reverse=True)
-        put("items", items)
-        put("tiles", [v for t in tiles for v in (t[1], t[2])])
-        if feedback is not None:
-            put("token_from", list(feedback[1]))
+        put("items", items, -1)
+        put("tiles", [v for t in tiles for v in (t[1], t[2])], 0)
+        o, n = lay["tiles"]
+        h[o + 2 * len(tiles) + 1:o + n:2] = 1 << 24      # padding tiles: an offset past any request's tokens
+        put("token_from", list(feedback[1]) if feedback is not None else [], -1)
+        return dict(N=N, B=B, W=len(want_rows), lens=lens, q_start=q_start, start=start, n_items=len(items),
+                    n_tiles=len(tiles), max_item_kv=max_item_kv)
+
+    def _build_context(self, entries: Sequence[StepEntry], feedback=None) -> StepContext:
+        B = len(entries)
+        N = sum(len(e.tokens) for e in entries)
+        W = sum(len(e.want) for e in entries)
+        lay = self._layout(N, B, W)
+        h = self._staging.begin()
+        info = self._pack(entries, lay, h, feedback)
+        lens, q_start, start = info["lens"], info["q_start"], info["start"]
         self._staging.commit(lay["total"])
         dev = self._staging.dev
         if feedback is not None:
@@ -461,7 +566,7 @@ class ModelRunner:
         ctx.h_kv_len = [s + n for s, n in zip(ctx.h_start_pos, lens)]
         ctx.h_slots = [e.slot for e in entries]
         ctx.status, ctx.act_dtype, ctx.device = self.status, self.model.dtype, self.device
-        ctx._plan = AttentionPlan(view("items"), len(items), view("tiles"), len(tiles),
-                                  max(max_item_kv, max(ctx.h_kv_len)))
+        ctx._plan = AttentionPlan(view("items"), info["n_items"], view("tiles"), info["n_tiles"],
+                                  max(info["max_item_kv"], max(ctx.h_kv_len)))
         ctx._scratch_owner = self
         return ctx

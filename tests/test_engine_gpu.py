@@ -36,6 +36,7 @@ def test_replay_matches_plain(model_dirs, name, dtype, mode):
     got = helpers.replay(s, steps)
     helpers.check_against_plain(model_dirs[name], reqs, got, dtype, f"{name}/{mode}")
     assert s.cache.free_pages == s.cache.total_pages, "every page must be back in the pool"
+    assert s.runner.padded_graph_steps > 0, "steps that are not decode-only are recorded in padded shapes and replayed"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -53,6 +54,29 @@ def test_cut_does_not_change_float32_logits_beyond_rounding(model_dirs, dtype):
     for o in outs[1:]:
         bad = helpers.first_bad(o, outs[0], tol)
         assert bad is None, f"first differing position {bad}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_recorded_padded_steps_and_eager_steps_agree(model_dirs, dtype):
+    """The same mixed trace with every step launched eagerly, with recorded steps of padded shapes, and with
+    room for only two recordings (the other shapes fall back to eager launches): float32 logits are equal
+    bit for bit (a token's result does not depend on the padding beside it), bfloat16 within rounding."""
+    name = "c"
+    reqs = requests_for(name)
+    steps = helpers.trace_mixed(reqs)
+    outs = []
+    for cap in (0, 48, 2):
+        s = session(model_dirs[name], name, dtype, helpers.live_token_need(steps), max_requests=4)
+        s.runner.max_step_graphs = cap
+        outs.append(helpers.replay(s, steps))
+        assert (s.runner.padded_graph_steps > 0) == (cap > 0) and len(s.runner._step_graphs) <= cap
+        s.runner.check_status()
+    for k in reqs:
+        for o in outs[1:]:
+            if dtype == "float32":
+                assert np.array_equal(o[k], outs[0][k]), k
+            else:
+                assert helpers.first_bad(o[k], outs[0][k], 3e-2 * np.abs(outs[0][k]).max()) is None, k
 
 
 @pytest.mark.parametrize("name", ["a", "c"])
