@@ -22,7 +22,10 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     ST_PDL_TRIGGER();
     const int t = blockIdx.x;
     const T* row = src ? src + (size_t)t * width : table + (size_t)ids[t] * width;
-    const T* prow = pos_table ? pos_table + (size_t)(pos[t] + pos_offset) * width : nullptr;
+    // a padding token of a fixed-shape step stands at position -1: it gets no position row (with an offset of
+    // zero the row would lie before the table), and what is computed for it is never used
+    const int p = pos_table ? pos[t] : 0;
+    const T* prow = (pos_table && p >= 0) ? pos_table + (size_t)(p + pos_offset) * width : nullptr;
     TO* o = out + (size_t)t * width;
     if (VEC) {
         for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {

@@ -25,13 +25,15 @@ def _act(y, act):
 def embed(ids, table, out, positions=None, pos_table=None, pos_offset=0):
     v = table[ids.long()].double()
     if pos_table is not None:
-        v = v + pos_table[positions.long() + pos_offset].double()
+        live = (positions >= 0).unsqueeze(1)       # padding tokens (position -1) get no position row
+        v = v + pos_table[(positions.long() + pos_offset).clamp(min=0)].double() * live
     out.copy_(v.to(out.dtype))
     return out
 
 
 def add_positions(x, positions, pos_table, pos_offset, out):
-    out.copy_((x.double() + pos_table[positions.long() + pos_offset].double()).to(out.dtype))
+    live = (positions >= 0).unsqueeze(1)
+    out.copy_((x.double() + pos_table[(positions.long() + pos_offset).clamp(min=0)].double() * live).to(out.dtype))
     return out
 
 

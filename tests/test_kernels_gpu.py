@@ -45,6 +45,17 @@ def test_embed(dtype, width):
     ref = cpu_ops.add_positions(x, pos, ptab, off, torch.empty(n, width))
     got = ops.add_positions(x.to(DEV), pos.to(DEV), ptab.to(DEV), off, torch.empty(n, width, device=DEV))
     close(got, ref, torch.float32, "add_positions", rel=1e-6)
+    # padding tokens of a fixed-shape step stand at position -1: with an offset of zero their row would lie
+    # before the table, so they get none (the table here is the tail of a larger tensor whose head is huge:
+    # a kernel that read the row before it would show 1e30 in its output)
+    big = torch.cat([torch.full((4, width), 1e30).to(dtype), rnd((50, width), dtype, 4)]).to(DEV)
+    pad_pos = pos.clone(); pad_pos[::3] = -1
+    got = ops.embed(ids.to(DEV), table.to(DEV), torch.empty(n, width, dtype=torch.float32, device=DEV),
+                    pad_pos.to(DEV), big[4:], 0)
+    ref = cpu_ops.embed(ids, table, torch.empty(n, width), pad_pos.clamp(min=0), big[4:].cpu(), 0)
+    keep = pad_pos >= 0
+    close(got[keep], ref[keep], torch.float32, "embed beside padding", rel=1e-6)
+    assert torch.equal(got[~keep].cpu(), table[ids[~keep].long()].float()), "a padding token gets no position row"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
