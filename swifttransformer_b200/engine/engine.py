@@ -198,6 +198,27 @@ class LLMEngine:
             r._reported = True
         return done
 
+    # ------------------------------------------------------------- warm-up
+    def warm_up(self, prompt_lengths: Sequence[int] = (), batch_sizes: Sequence[int] = (1,)) -> int:
+        """Run throw-away requests so that the recorded steps they need exist before real ones arrive
+        (recording a step costs tens of milliseconds, replaying it tens of microseconds): one prompt of each
+        given length, and for each batch size that many one-token prompts decoding together.  Needs an idle
+        engine; leaves cache and statistics as they were.  Returns how many recorded steps were added."""
+        if self.has_work():
+            raise RuntimeError("warm_up needs an engine without requests")
+        r = self.runner
+        before = len(r._graphs) + len(r._step_graphs)
+        stats = dict(self.stats)
+        limit = self.model.max_positions
+        for n in prompt_lengths:
+            n = max(1, min(int(n), limit - 2 if limit else int(n)))
+            self.generate([[0] * n], SamplingParams(max_new_tokens=2, ignore_eos=True))
+        for b in batch_sizes:
+            b = max(1, min(int(b), self.config.max_num_seqs))
+            self.generate([[0]] * b, SamplingParams(max_new_tokens=3, ignore_eos=True))
+        self.stats = stats
+        return len(r._graphs) + len(r._step_graphs) - before
+
     # ------------------------------------------------------------ generate
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> List[List[int]]:

@@ -169,6 +169,22 @@ def test_steps_launched_ahead_with_requests_arriving_at_random(model_dirs, cpu_o
         assert all(len(o) >= 1 for o, _ in got)
 
 
+def test_warm_up_leaves_the_engine_as_it_was(model_dirs, cpu_ops_installed):
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    eng = LLMEngine(model, page_size=8, num_pages=40, max_batch_tokens=48, chunk_size=32, max_num_seqs=4)
+    assert eng.warm_up(prompt_lengths=[5, 70, 1000], batch_sizes=[1, 4, 100]) == 0     # nothing is recorded on the CPU
+    assert eng.cache.free_pages == eng.cache.total_pages and eng.stats["steps"] == 0 and not eng.requests
+    prompt = helpers.random_tokens(512, 9, 77)
+    cfg, w = plain_opt.load_model(model_dirs["a"])
+    assert eng.generate([prompt], SamplingParams(max_new_tokens=5)) == [plain_opt.greedy_generate(cfg, w, prompt, 5)]
+    eng.add_request(prompt)
+    with pytest.raises(RuntimeError, match="without requests"):
+        eng.warm_up(batch_sizes=[1])
+
+
 def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
     from swifttransformer_b200 import ops
     from swifttransformer_b200.sampling import Sampler, SamplingParams

@@ -125,6 +125,23 @@ def test_steps_launched_ahead_change_nothing_on_the_gpu(model_dirs, dtype):
     assert e0.scheduler.num_preemptions > 0 and e1.scheduler.num_preemptions > 0
 
 
+def test_warm_up_records_the_steps_that_requests_then_replay(model_dirs):
+    from swifttransformer_b200.sampling import SamplingParams
+    vocab = TINY["a"]["cfg"]["vocab_size"]
+    eng = engine(model_dirs["a"], "a", "bfloat16")
+    added = eng.warm_up(prompt_lengths=[20], batch_sizes=[1, 3])
+    assert added >= 3
+    assert eng.cache.free_pages == eng.cache.total_pages and eng.stats["steps"] == 0 and not eng.requests
+    r = eng.runner
+    known = len(r._graphs) + len(r._step_graphs)
+    prompts = [helpers.random_tokens(vocab, 20, 900)]
+    first = eng.generate(prompts, SamplingParams(max_new_tokens=3))
+    assert len(r._graphs) + len(r._step_graphs) == known, "a warmed-up shape is replayed, not recorded again"
+    fresh = engine(model_dirs["a"], "a", "bfloat16")
+    assert fresh.generate(prompts, SamplingParams(max_new_tokens=3)) == first
+    eng.runner.check_status()
+
+
 def test_seeded_sampling_is_reproducible_and_batch_independent(model_dirs):
     from swifttransformer_b200.sampling import SamplingParams
     name = "b"
