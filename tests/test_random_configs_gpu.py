@@ -1,0 +1,57 @@
+"""Randomly drawn OPT configurations through the step function on the GPU, against the plain implementation:
+head sizes in steps of 8 up to 128, 1 to 24 heads, widths and vocabularies that are no power of two, with and
+without projections, biases and affine norms, pre- and post-norm, pages of 8 to 64 positions, prompts up to the
+model's last position.  Each case replays its requests whole, with a decoded tail, in portions of changing size
+and mixed with page reuse, in float32 and in bfloat16."""
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def random_case(case):
+    rng = np.random.default_rng(1000 + case)
+    d = int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 24, 40, 8]))
+    nh = int(rng.integers(1, 9)) if rng.random() < 0.7 else int(rng.integers(9, 25))
+    hidden = nh * d
+    proj = rng.random() < 0.4
+    cfg = dict(vocab_size=int(rng.integers(50, 3000)), hidden_size=hidden, num_hidden_layers=int(rng.integers(1, 4)),
+               ffn_dim=int(rng.integers(2, 60)) * 8 + (int(rng.integers(0, 8)) if rng.random() < 0.3 else 0),
+               num_attention_heads=nh, max_position_embeddings=int(rng.integers(300, 900)),
+               do_layer_norm_before=bool(rng.random() < 0.7),
+               word_embed_proj_dim=(int(rng.integers(2, 20)) * 8 if proj else hidden),
+               enable_bias=bool(rng.random() < 0.7), layer_norm_elementwise_affine=bool(rng.random() < 0.7),
+               activation_function=str(rng.choice(["relu", "gelu"])),
+               layer_norm_eps=float(rng.choice([1e-5, 1e-6, 3e-4])))
+    page = int(rng.choice([8, 16, 32, 64]))
+    std = float(rng.choice([0.05, 0.08, 0.1]))
+    lens = [int(x) for x in rng.integers(1, min(280, cfg["max_position_embeddings"] - 2), 5)]
+    lens[0] = int(rng.integers(130, 280))
+    if case % 3 == 0:
+        lens[1] = cfg["max_position_embeddings"] - int(rng.integers(0, 3))     # up to the last position
+    return cfg, page, std, lens
+
+
+# drawn once and kept: head sizes 64 and 128 with pages of 8, 32 and 64 (the TMA-fed attention), 11 to 21 heads,
+# a prompt longer than one span of the decode attention's key range, odd widths
+@pytest.mark.parametrize("case", [3, 4, 10, 106, 114, 119, 129])
+def test_random_configuration_replays_like_plain(tmp_path, case):
+    from swifttransformer_b200.config import OptConfig
+    from swifttransformer_b200.engine.replay import TraceSession
+    from swifttransformer_b200.models import write_random_model
+    cfg, page, std, lens = random_case(case)
+    model_dir = str(tmp_path)
+    write_random_model(model_dir, OptConfig.from_dict(dict(cfg)), seed=case, std=std)
+    reqs = {f"r{i}": helpers.random_tokens(cfg["vocab_size"], n, 7 * case + i) for i, n in enumerate(lens)}
+    for dtype in ("float32", "bfloat16"):
+        for mode, build in (("whole", helpers.trace_whole), ("tail", helpers.trace_decode_tail),
+                            ("portions", helpers.trace_portions),
+                            ("mixed", lambda r: helpers.trace_mixed(r, seed=case))):
+            steps = build(reqs)
+            need = helpers.live_token_need(steps, round_to=max(64, page))
+            s = TraceSession(model_dir, dtype, need, page_size=page, device="cuda", max_requests=4)
+            got = helpers.replay(s, steps)
+            helpers.check_against_plain(model_dir, reqs, got, dtype, f"case {case} {cfg} page {page}/{mode}")
+            assert s.cache.free_pages == s.cache.total_pages
