@@ -9,6 +9,10 @@ events on the device; ``e2e`` is the same through ``LLMEngine.step`` (host token
 out, wall clock).  Also reported: a 2,048-token prefill, the decode step's HBM roofline fraction, and
 decode at batch 1 and 64.  Prints ONE JSON line.  For --gpus > 1 it says that the engine is
 single-GPU and exits with 2.
+
+``--only decode|prefill`` run one small measurement (for profiling); ``--only mixed`` runs a continuous
+batch of requests of random lengths (prompt portions of 512 tokens beside decoded tokens) through
+``LLMEngine.generate`` and reports tokens per second, steps and preemptions.
 """
 import argparse
 import json
@@ -105,8 +109,12 @@ def main():
     ap.add_argument("--launch-floor", action="store_true",
                     help="with --only decode: same number of layers and kernels, but hidden size 64, so that the "
                          "step time is what the chain of dependent launches costs by itself")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
-                    help="run just the device-timed decode loop or just the prefill (for profiling small cases)")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed"],
+                    help="run just the device-timed decode loop or just the prefill (for profiling small cases), or "
+                         "the mixed continuous batch: --requests requests with prompt lengths uniform in [16,1536] "
+                         "and output lengths uniform in [16,512], prompt portions of 512 tokens beside decoded "
+                         "tokens, through LLMEngine.generate (host token ids in and out, wall clock)")
+    ap.add_argument("--requests", type=int, default=64, help="requests of the mixed continuous batch")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -225,12 +233,49 @@ def main():
         fl = prefill_flops(cfg, cfg.num_hidden_layers, n)
         return dict(value=n / ms * 1e3, tokens=n, ms=ms, frac=fl / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12))
 
+    def mixed(n_req):
+        """Continuous batching: every request is admitted at once, prompts run in portions of 512 tokens beside
+        the decoded tokens of the others.  Run twice with different tokens of the same lengths; the second
+        run (whose step shapes are mostly recorded already) is timed."""
+        chunk = 512
+        lens = [(int(rng.integers(16, 1537)), int(rng.integers(16, 513))) for _ in range(n_req)]
+        lens = [(p, min(o, ctx_max - p)) for p, o in lens]
+        pages = sum((p + o + 15) // 16 + 1 for p, o in lens)
+        eng = LLMEngine(model, page_size=16, num_pages=pages, max_batch_tokens=chunk + n_req, chunk_size=chunk,
+                        max_num_seqs=n_req)
+        result = {}
+        for rep in range(2):
+            ps = [rng.integers(3, cfg.vocab_size, p).tolist() for p, _ in lens]
+            sp = [SamplingParams(max_new_tokens=o, ignore_eos=True) for _, o in lens]
+            steps0, pre0 = eng.stats["steps"], eng.scheduler.num_preemptions
+            graphs0, eager0 = eng.runner.graph_steps + eng.runner.padded_graph_steps, eng.runner.steps_run
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            outs = eng.generate(ps, sp)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            n_in, n_out = sum(p for p, _ in lens), sum(len(o) for o in outs)
+            steps = eng.stats["steps"] - steps0
+            replayed = eng.runner.graph_steps + eng.runner.padded_graph_steps - graphs0
+            result = {"only": "mixed", "model": args.model_name, "requests": n_req, "prompt_tokens": n_in,
+                      "generated_tokens": n_out, "seconds": round(dt, 4), "total_tok_s": round((n_in + n_out) / dt, 1),
+                      "generated_tok_s": round(n_out / dt, 1), "steps": steps, "ms_per_step": round(dt / steps * 1e3, 3),
+                      "preemptions": eng.scheduler.num_preemptions - pre0, "replayed_steps": replayed,
+                      "eager_steps": eng.runner.steps_run - eager0 - replayed,
+                      "recorded_shapes": len(eng.runner._graphs) + len(eng.runner._step_graphs),
+                      "first_run_seconds": result.get("seconds")}
+        eng.runner.check_status()
+        return result
+
     if args.only == "decode":
         r = decode_device(args.batch, K, W)
         print(json.dumps({"only": "decode", "ms_per_step": round(r["ms"], 4), "tok_s": round(r["tok_s"], 1)}))
         return 0
     if args.only == "prefill":
         print(json.dumps(dict(prefill(2048), only="prefill")))
+        return 0
+    if args.only == "mixed":
+        print(json.dumps(mixed(args.requests)))
         return 0
     with ClockSampler(0) as clocks:
         dev = decode_device(args.batch, K, W)

@@ -1,0 +1,48 @@
+"""bench.py: what it answers without a GPU, and its small modes on one."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BENCH = os.path.join(ROOT, "bench.py")
+
+
+def run(*args, timeout=600):
+    return subprocess.run([sys.executable, BENCH, *args], capture_output=True, text=True, timeout=timeout)
+
+
+def test_more_than_one_gpu_is_refused_in_one_line():
+    r = run("--gpus", "2")
+    assert r.returncode == 2
+    assert len(r.stdout.strip().splitlines()) == 1 and "one GPU" in r.stdout
+
+
+def test_reference_arm_says_why_it_is_unavailable():
+    r = run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
+    assert r.returncode == 0
+    line = json.loads(r.stdout.strip())
+    assert line["impl"] == "reference" and line["unavailable"]
+
+
+@pytest.mark.gpu
+def test_mixed_continuous_batch_mode():
+    r = run("--only", "mixed", "--layers", "1", "--requests", "5")
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["only"] == "mixed" and line["requests"] == 5
+    assert line["generated_tokens"] > 0 and line["total_tok_s"] > 0 and line["preemptions"] == 0
+    assert line["replayed_steps"] + line["eager_steps"] == line["steps"]
+
+
+@pytest.mark.gpu
+def test_small_decode_and_prefill_modes():
+    r = run("--only", "decode", "--layers", "1", "--steps", "4", "--warmup", "3", "--batch", "2")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["tok_s"] > 0
+    r = run("--only", "prefill", "--layers", "1")
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["tokens"] == 2048 and 0 < line["frac"] < 1.2
