@@ -11,8 +11,8 @@
 //     barrier completes when they have landed.  No multicast; only pages that hold a key the tile
 //     may see are fetched (the others may have been given back): the rest of a tile, which is
 //     masked, is filled from the tile's first live page so that it holds finite numbers.
-//   * Each of the two warpgroups (alternate key tiles of one (query tile, head), merged at the end)
-//     has two extra warps: one issues the products (its first lane), one the copies (lane j fetches
+//   * Each of the two (optionally three) warpgroups (every second or third key tile of one (query tile,
+//     head), merged at the end) has two extra warps: one issues the products (its first lane), one the copies (lane j fetches
 //     the number of page j of the tile after next and issues that page's copies).  Keys and values
 //     are double-buffered, with a "landed" and a "free" mbarrier per buffer (the latter completed by
 //     tcgen05.commit after the product that reads the buffer).  S of the next tile is issued as soon
@@ -29,7 +29,17 @@
 #include "tcgen05.cuh"
 #include "tma_host.h"
 
-#define TM_THREADS 384   // 2 warpgroups of softmax threads, 2 warps that issue products, 2 warps that issue copies
+// threads of a block with NWG softmax warpgroups: the softmax threads, then NWG warps that issue products and NWG
+// warps that issue copies, filled up to whole warpgroups (setmaxnreg works on warpgroups)
+#define TM_THREADS(NWG) (128 * (NWG) + ((NWG) == 2 ? 128 : 256))
+// Registers per thread after a block of three warpgroups has redistributed them.  setmaxnreg moves registers
+// inside what the block was given at launch (threads x the kernel's register count, 640 x 96), not inside the
+// SM's whole file: a request beyond that waits forever.  The sum below must fit; the launcher checks it against
+// the compiled kernel's register count and falls back to two warpgroups otherwise.
+#define TM_REGS_SOFTMAX 136
+#define TM_REGS_ISSUE 32
+#define TM_REGS_AFTER(NWG) (128 * (NWG) * TM_REGS_SOFTMAX + (TM_THREADS(NWG) - 128 * (NWG)) * TM_REGS_ISSUE)
+static_assert(TM_REGS_AFTER(3) <= TM_THREADS(3) * 96, "setmaxnreg asks for more registers than a block of 640 threads x 96 owns");
 
 // bounded wait that also ends when the block has been marked dead
 __device__ __forceinline__ bool tm_wait(uint32_t mbar, uint32_t parity, volatile int* dead) {
@@ -49,17 +59,30 @@ __device__ __forceinline__ bool tm_wait(uint32_t mbar, uint32_t parity, volatile
 // named barriers of a warpgroup and the warp that issues its products (160 threads): A = "S has been read",
 // B = "P has been written".  Softmax threads only arrive, the issuing warp waits.
 __device__ __forceinline__ void tm_arrive(int wg, int which) {
-    if (wg == 0) { if (which == 0) asm volatile("bar.arrive 1, 160;\n" ::: "memory"); else asm volatile("bar.arrive 2, 160;\n" ::: "memory"); }
-    else         { if (which == 0) asm volatile("bar.arrive 3, 160;\n" ::: "memory"); else asm volatile("bar.arrive 4, 160;\n" ::: "memory"); }
+    const int id = 2 * wg + which;
+    if (id == 0) asm volatile("bar.arrive 1, 160;\n" ::: "memory");
+    else if (id == 1) asm volatile("bar.arrive 2, 160;\n" ::: "memory");
+    else if (id == 2) asm volatile("bar.arrive 3, 160;\n" ::: "memory");
+    else if (id == 3) asm volatile("bar.arrive 4, 160;\n" ::: "memory");
+    else if (id == 4) asm volatile("bar.arrive 5, 160;\n" ::: "memory");
+    else asm volatile("bar.arrive 6, 160;\n" ::: "memory");
 }
 __device__ __forceinline__ void tm_sync(int wg, int which) {
-    if (wg == 0) { if (which == 0) asm volatile("bar.sync 1, 160;\n" ::: "memory"); else asm volatile("bar.sync 2, 160;\n" ::: "memory"); }
-    else         { if (which == 0) asm volatile("bar.sync 3, 160;\n" ::: "memory"); else asm volatile("bar.sync 4, 160;\n" ::: "memory"); }
+    const int id = 2 * wg + which;
+    if (id == 0) asm volatile("bar.sync 1, 160;\n" ::: "memory");
+    else if (id == 1) asm volatile("bar.sync 2, 160;\n" ::: "memory");
+    else if (id == 2) asm volatile("bar.sync 3, 160;\n" ::: "memory");
+    else if (id == 3) asm volatile("bar.sync 4, 160;\n" ::: "memory");
+    else if (id == 4) asm volatile("bar.sync 5, 160;\n" ::: "memory");
+    else asm volatile("bar.sync 6, 160;\n" ::: "memory");
 }
 
-// DB: 64-wide blocks of the head dimension (head_dim == 64 DB)
-template <int DB>
-__global__ void __launch_bounds__(TM_THREADS, 1)
+// DB: 64-wide blocks of the head dimension (head_dim == 64 DB).  NWG: softmax warpgroups (2 or 3), each with
+// its own key tiles (every NWG-th one), buffers, accumulators, issuing warps and barriers.  Three of them give
+// each scheduler three softmax warps to choose from instead of two; their registers come from the issuing
+// warps (setmaxnreg), and tensor memory has room for three accumulators only at head size 64.
+template <int DB, int NWG>
+__global__ void __launch_bounds__(TM_THREADS(NWG), 1)
 attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q,
                              bf16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ q_start,
                              const int* __restrict__ start_pos, const int* __restrict__ slots,
@@ -67,7 +90,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                              int nh, int nkv, int page_size, float scale_log2, int window, int* status) {
     extern __shared__ unsigned char tm_raw[];
     // per warpgroup: S done, O done, then "landed" for the buffers K0, K1, V0, V1, then "free" for the same four
-    __shared__ __align__(8) unsigned long long s_mbar[2][10];
+    __shared__ __align__(8) unsigned long long s_mbar[NWG][10];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
     constexpr int d = 64 * DB;
@@ -75,14 +98,18 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     constexpr uint32_t BUF = DB * KV_BLK;                               // one key or value tile
     constexpr uint32_t WG_BYTES = 4 * BUF + Q_BLK;                      // K x2, V x2, P
     constexpr int WG_COLS = 64 + 64 * DB;                               // S, then O
-    constexpr uint32_t ALL_BYTES = DB * Q_BLK + 2 * WG_BYTES;
-    constexpr int TMEM_COLS = 2 * WG_COLS <= 256 ? 256 : 512;
+    constexpr uint32_t ALL_BYTES = DB * Q_BLK + NWG * WG_BYTES;
+    constexpr int TMEM_COLS = NWG * WG_COLS <= 256 ? 256 : 512;
+    static_assert(NWG * WG_COLS <= 512, "tensor memory has 512 columns");
+    static_assert((NWG - 1) * (2 + 64 * DB) * 128 * 4 <= ALL_BYTES, "the merge reuses the tiles' space");
+    constexpr int N_SOFTMAX = 128 * NWG;
     const uint32_t base = (tc_smem(tm_raw) + 1023u) & ~1023u;           // swizzled tiles start on 1024-byte boundaries
 
     const int tid = threadIdx.x;
-    const int role = tid < 256 ? 0 : tid < 320 ? 1 : 2;                  // softmax, products, copies
+    // softmax, products, copies, and (three warpgroups) two warps that only fill the last warpgroup
+    const int role = tid < N_SOFTMAX ? 0 : tid < N_SOFTMAX + 32 * NWG ? 1 : tid < N_SOFTMAX + 64 * NWG ? 2 : 3;
     const bool issuer = role != 0;
-    const int wg = role == 0 ? tid >> 7 : ((tid - 256) >> 5) & 1;
+    const int wg = role == 0 ? tid >> 7 : role == 1 ? (tid - N_SOFTMAX) >> 5 : role == 2 ? (tid - N_SOFTMAX - 32 * NWG) >> 5 : 0;
     const int row = tid & 127, warp4 = (tid >> 5) & 3;
     {
         uint32_t dyn;
@@ -110,13 +137,13 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int kt_begin = key_lo / TC_BN, kt_end = pos_last / TC_BN + 1;
     const int kv_hi = pos_last + 1;
-    const int n_my = (kt_end - kt_begin - wg + 1) / 2;                   // this warpgroup's tiles: every second one
-    auto my_kt = [&](int i) { return kt_begin + wg + 2 * i; };
+    const int n_my = (kt_end - kt_begin - wg + NWG - 1) / NWG;           // this warpgroup's tiles: every NWG-th one
+    auto my_kt = [&](int i) { return kt_begin + wg + NWG * i; };
 
     const uint32_t mb_s = tc_smem(&s_mbar[wg][0]), mb_o = tc_smem(&s_mbar[wg][1]);
     const uint32_t mb_full = tc_smem(&s_mbar[wg][2]), mb_free = tc_smem(&s_mbar[wg][6]);   // four each, 8 bytes apart
     if (tid == 0) {
-        for (int w = 0; w < 2; ++w)
+        for (int w = 0; w < NWG; ++w)
             for (int k = 0; k < 10; ++k) tc_mbar_init(tc_smem(&s_mbar[w][k]), 1);
         tc_mbar_init_fence();
         s_dead = 0;
@@ -129,10 +156,10 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     auto tile_addr = [](uint32_t tile, uint32_t blk_bytes, int r, int c) -> uint32_t {
         return tile + (c >> 3) * blk_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
     };
-    if (!issuer) {   // the tile's queries: two threads per row (rows past the portion's end are zero)
+    if (!issuer) {   // the tile's queries: NWG threads per row (rows past the portion's end are zero)
         const bool ok = row < n_rows;
         const bf16* src = q + ((size_t)(tok0 + (ok ? row : 0)) * nh + h) * d;
-        for (int c = wg; c < d / 8; c += 2) tc_cp16(tile_addr(sQ, Q_BLK, row, c), src + c * 8, ok);
+        for (int c = wg; c < d / 8; c += NWG) tc_cp16(tile_addr(sQ, Q_BLK, row, c), src + c * 8, ok);
         tc_cp_commit();
         tc_cp_wait<0>();
     }
@@ -143,6 +170,12 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     const uint32_t tmem = s_tmem;
     const uint32_t t_wg = tmem + wg * WG_COLS;                               // S at +0, O at +64
     volatile int* dead = &s_dead;
+    // barrier of the whole block, by name and count so that the issuing warps and the softmax warps can meet
+    // from different places in the code
+    auto block_sync = [&]() { asm volatile("bar.sync 7, %0;\n" ::"n"(TM_THREADS(NWG)) : "memory"); };
+    // Three warpgroups: every warp of the block is here (the only returns above are taken by the whole block).
+    // The issuing warpgroups give registers back, the softmax warpgroups' request below waits until they are there.
+    if (issuer && NWG == 3) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(TM_REGS_ISSUE));
 
     if (role == 1) {
         // ---- the warp that issues the products (its first lane; the others only keep the named barriers' count)
@@ -256,6 +289,16 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
         }
         __syncwarp();
     }
+    if (issuer) {
+        // the issuing warps (and the warps that only fill a warpgroup) are done: they meet the softmax warps at
+        // the block's three last barriers and leave
+        tc_fence_before_sync();
+        block_sync();
+        block_sync();
+        block_sync();
+        return;
+    }
+    if (NWG == 3) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(TM_REGS_SOFTMAX));
 
     // ---- softmax threads: thread `row` of the warpgroup owns query row `row` = TMEM lane `row`
     const uint32_t t_row = t_wg + ((uint32_t)(warp4 * 32) << 16);
@@ -363,16 +406,18 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
         }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    block_sync();
     if (s_dead) {
         alive = false;
         if (tid == 0) atomicExch(status, 3);
     }
-    // ---- merge the two warpgroups: the second leaves (max, sum, O row) in shared memory (every product
-    // and copy has completed, so the tiles' space is free: (2 + head_dim) x 128 floats from its start)
-    float* mrg = reinterpret_cast<float*>(tm_raw + (base - tc_smem(tm_raw)));
+    // ---- merge the warpgroups: all but the first leave (max, sum, O row) in shared memory (every product
+    // and copy has completed, so the tiles' space is free: (2 + head_dim) x 128 floats each from its start)
+    float* mrg_all = reinterpret_cast<float*>(tm_raw + (base - tc_smem(tm_raw)));
+    constexpr int MRG = (2 + d) * 128;
     const float m_fin = n_my > 0 ? m_ref : -INFINITY;
-    if (alive && !issuer && wg == 1) {
+    if (alive && !issuer && wg > 0) {
+        float* mrg = mrg_all + (wg - 1) * MRG;
         mrg[row] = m_fin;
         mrg[128 + row] = l_run;
 #pragma unroll
@@ -384,12 +429,19 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
         }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    block_sync();
     if (alive && !issuer && wg == 0) {   // warp-uniform: tcgen05.ld needs whole warps; only the store looks at the row
-        const float m1 = mrg[row], l1 = mrg[128 + row];
-        const float m = fmaxf(m_fin, m1);
-        const float a0 = m_fin == -INFINITY ? 0.f : tc_exp2(m_fin - m), a1 = m1 == -INFINITY ? 0.f : tc_exp2(m1 - m);
-        const float l = l_run * a0 + l1 * a1;
+        float m = m_fin, a[NWG], l;
+#pragma unroll
+        for (int w = 1; w < NWG; ++w) m = fmaxf(m, mrg_all[(w - 1) * MRG + row]);
+        a[0] = m_fin == -INFINITY ? 0.f : tc_exp2(m_fin - m);
+        l = l_run * a[0];
+#pragma unroll
+        for (int w = 1; w < NWG; ++w) {
+            const float mw = mrg_all[(w - 1) * MRG + row];
+            a[w] = mw == -INFINITY ? 0.f : tc_exp2(mw - m);
+            l += mrg_all[(w - 1) * MRG + 128 + row] * a[w];
+        }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* orow = out + ((size_t)(tok0 + row) * nh + h) * d;
 #pragma unroll
@@ -402,7 +454,12 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                 if (row >= n_rows) continue;
                 float r[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) r[k] = (ov[c * 8 + k] * a0 + mrg[(2 + cb * 32 + c * 8 + k) * 128 + row] * a1) * inv;
+                for (int k = 0; k < 8; ++k) {
+                    float v = ov[c * 8 + k] * a[0];
+#pragma unroll
+                    for (int w = 1; w < NWG; ++w) v += mrg_all[(w - 1) * MRG + (2 + cb * 32 + c * 8 + k) * 128 + row] * a[w];
+                    r[k] = v * inv;
+                }
                 uint4 w;
                 __nv_bfloat162 p0 = __floats2bfloat162_rn(r[0], r[1]), p1 = __floats2bfloat162_rn(r[2], r[3]);
                 __nv_bfloat162 p2 = __floats2bfloat162_rn(r[4], r[5]), p3 = __floats2bfloat162_rn(r[6], r[7]);
@@ -413,7 +470,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
         }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    block_sync();
     if (tid < 32) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -456,28 +513,49 @@ static int tm_pool_map(const void* pool, long long rows, int page_size, int d, C
     return 0;
 }
 
-static size_t tm_smem_bytes(int db) {
+static size_t tm_smem_bytes(int db, int nwg) {
     // Q, then per warpgroup two key and two value tiles and P; a kilobyte of slack to reach a 1024-byte boundary
-    return (size_t)db * TC_BM * 128 + 2 * ((size_t)4 * db * TC_BN * 128 + TC_BM * 128) + 1024;
+    return (size_t)db * TC_BM * 128 + nwg * ((size_t)4 * db * TC_BN * 128 + TC_BM * 128) + 1024;
 }
 
-template <int DB>
+// Softmax warpgroups per block for head size 64: two, or three when asked for (head size 128 always runs two:
+// tensor memory holds no third accumulator of that size).  Measured on 32 heads x 64, one request: three
+// warpgroups take 60.9 instead of 64.2 us at 2048 tokens and 541 instead of 619 us at 8192, and a whole
+// 2048-token prefill of OPT-1.3B takes 5.94 ms either way; the positions of this architecture end at 2048, so
+// two stay the rule.
+static int tm_wg_d64 = 2;
+ST_EXPORT void st_attention_prefill_tma_warpgroups(int n) { tm_wg_d64 = n == 3 ? 3 : 2; }
+
+template <int DB, int NWG>
 static int launch_prefill_tma(const CUtensorMap& map, const void* q, void* out, const int* tiles, int n_tiles,
                               const int* q_start, const int* start_pos, const int* slots, const int* block_table,
                               int max_pages, int n_layers, int layer, int nh, int nkv, int page_size, float scale,
                               int window, int* status, cudaStream_t s) {
-    const size_t smem = tm_smem_bytes(DB);
+    const size_t smem = tm_smem_bytes(DB, NWG);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tma_kernel<DB>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tma_kernel<DB, NWG>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(nh, n_tiles);
-    attention_prefill_tma_kernel<DB><<<grid, TM_THREADS, smem, s>>>(map, (const bf16*)q, (bf16*)out, tiles, q_start,
-        start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, page_size, scale * TC_LOG2E, window, status);
+    attention_prefill_tma_kernel<DB, NWG><<<grid, TM_THREADS(NWG), smem, s>>>(map, (const bf16*)q, (bf16*)out, tiles,
+        q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, page_size, scale * TC_LOG2E, window,
+        status);
     return st_launch_status();
+}
+
+// The three-warpgroup kernel may only run if the registers it asks for with setmaxnreg are within what its
+// blocks own at launch (checked once against the compiled kernel).
+static bool tm_three_warpgroups_fit() {
+    static int fit = -1;
+    if (fit < 0) {
+        cudaFuncAttributes a;
+        fit = cudaFuncGetAttributes(&a, attention_prefill_tma_kernel<1, 3>) == cudaSuccess &&
+              (long long)a.numRegs * TM_THREADS(3) >= TM_REGS_AFTER(3) && a.numRegs >= TM_REGS_ISSUE ? 1 : 0;
+    }
+    return fit == 1;
 }
 
 // 1 if the TMA-fed kernel takes this head size and page size
@@ -502,9 +580,12 @@ ST_EXPORT int st_attention_prefill_tma(const void* q, const void* pool, long lon
     int r = tm_pool_map(pool, rows, page_size, d, &map);
     if (r) return r;
     cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64 && tm_wg_d64 == 3 && tm_three_warpgroups_fit())
+        return launch_prefill_tma<1, 3>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
+                                        n_layers, layer, nh, nkv, page_size, scale, window, status, s);
     if (d == 64)
-        return launch_prefill_tma<1>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                     n_layers, layer, nh, nkv, page_size, scale, window, status, s);
-    return launch_prefill_tma<2>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                 n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+        return launch_prefill_tma<1, 2>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
+                                        n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+    return launch_prefill_tma<2, 2>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
+                                    n_layers, layer, nh, nkv, page_size, scale, window, status, s);
 }

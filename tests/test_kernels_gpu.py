@@ -235,13 +235,15 @@ def test_attention_decode(shape, window, n_splits, kernel):
 
 @pytest.mark.parametrize("shape", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
-@pytest.mark.parametrize("kernel", ["tma", "tc", "mma"])
+@pytest.mark.parametrize("kernel", ["tma", "tma3", "tc", "mma"])
 def test_attention_prefill(shape, window, kernel):
     nh, nkv, d, ps = shape
     if kernel == "tc" and d > 128:
         pytest.skip("the tcgen05 kernel takes head sizes up to 128")
-    if kernel == "tma" and not (d in (64, 128) and ps in (8, 16, 32, 64)):
+    if kernel in ("tma", "tma3") and not (d in (64, 128) and ps in (8, 16, 32, 64)):
         pytest.skip("the TMA-fed kernel takes head sizes 64 and 128 and pages of 8 to 64 positions")
+    if kernel == "tma3" and d != 64:
+        pytest.skip("three warpgroups fit tensor memory at head size 64 only")
     dtype = torch.bfloat16
     lens, new = [150, 200, 300, 64, 17, 400], [150, 70, 16, 64, 17, 300]
     pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 50, window)
@@ -280,7 +282,7 @@ def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
     tr = ops.attention_prefill_tile_rows()
     tiles = torch.tensor([v for i in (0, 2) for off in range(0, new[i], tr) for v in (i, off)], dtype=torch.int32).to(DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for kernel in ("tma", "tc", "mma"):
+    for kernel in ("tma", "tma3", "tc", "mma"):
         out = torch.zeros_like(ref, device=DEV)
         ops.attention_prefill(dev["q"], dev["pool"], 1, out, tiles, tiles.numel() // 2, dev["q_start"], dev["start"],
                               dev["slots"], dev["bt"], nh, scale, 0, status=status, kernel=kernel)
