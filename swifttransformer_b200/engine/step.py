@@ -155,6 +155,7 @@ class _RecordedStep:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.kernels = 0
+        self.last_used = 0               # the runner's step count when this recording last ran
 
     def _scratch(self, n: int) -> torch.Tensor:
         if self._scratch_buf is None or self._scratch_buf.numel() < n:
@@ -302,9 +303,13 @@ class ModelRunner:
         self._entries = cache.entries()
         self._graphs: Dict[Any, _DecodeGraph] = {}      # (rows, spans of KEYS_PER_BLOCK keys) -> recorded step
         # recorded steps of padded shapes for everything else (prompt portions, mixed steps); bounded in number:
-        # a shape beyond the bound runs eagerly
+        # a shape beyond the bound takes the place of the recording that has not been used for the longest
+        # time if that is more than `evict_idle_steps` steps ago, and runs eagerly otherwise (a working set
+        # larger than the bound must not be recorded over and over: recording costs ~15 eager steps)
         self._step_graphs: Dict[Any, _StepGraph] = {}
         self.max_step_graphs = 48
+        self.evict_idle_steps = 512
+        self._retired_h2d_bytes = 0
         self.padded_graph_steps = 0
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_cuda_graphs else None
         self.steps_run = 0
@@ -332,7 +337,7 @@ class ModelRunner:
     @property
     def h2d_bytes(self) -> int:
         """Bytes of step metadata copied host -> device so far."""
-        return (self._staging.bytes_copied + self._upd_staging.bytes_copied
+        return (self._staging.bytes_copied + self._upd_staging.bytes_copied + self._retired_h2d_bytes
                 + sum(g.staging.bytes_copied for g in self._graphs.values())
                 + sum(g.staging.bytes_copied for g in self._step_graphs.values()))
 
@@ -447,9 +452,13 @@ class ModelRunner:
         sg = self._step_graphs.get(key)
         if sg is None:
             if len(self._step_graphs) >= self.max_step_graphs:
-                return None
+                oldest = min(self._step_graphs, key=lambda k: self._step_graphs[k].last_used, default=None)
+                if oldest is None or self.steps_run - self._step_graphs[oldest].last_used <= self.evict_idle_steps:
+                    return None
+                self._retired_h2d_bytes += self._step_graphs.pop(oldest).staging.bytes_copied
             sg = self._step_graphs[key] = _StepGraph(self, n_pad, b_pad, i_pad, w_pad,
                                                      min(max(spans, 1) * KEYS_PER_BLOCK, self.cache.max_seq_len))
+        sg.last_used = self.steps_run
         return sg
 
     def check_status(self) -> None:

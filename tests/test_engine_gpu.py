@@ -58,18 +58,29 @@ def test_cut_does_not_change_float32_logits_beyond_rounding(model_dirs, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_recorded_padded_steps_and_eager_steps_agree(model_dirs, dtype):
-    """The same mixed trace with every step launched eagerly, with recorded steps of padded shapes, and with
-    room for only two recordings (the other shapes fall back to eager launches): float32 logits are equal
-    bit for bit (a token's result does not depend on the padding beside it), bfloat16 within rounding."""
+    """The same mixed trace with every step launched eagerly, with recorded steps of padded shapes, with
+    room for only two recordings (the other shapes fall back to eager launches), and with two recordings of
+    which the one unused for more than three steps gives way to a new shape: float32 logits are equal bit for
+    bit (a token's result does not depend on the padding beside it), bfloat16 within rounding."""
     name = "c"
     reqs = requests_for(name)
     steps = helpers.trace_mixed(reqs)
     outs = []
-    for cap in (0, 48, 2):
+    for cap, idle in ((0, 512), (48, 512), (2, 512), (2, 3)):
         s = session(model_dirs[name], name, dtype, helpers.live_token_need(steps), max_requests=4)
-        s.runner.max_step_graphs = cap
-        outs.append(helpers.replay(s, steps))
-        assert (s.runner.padded_graph_steps > 0) == (cap > 0) and len(s.runner._step_graphs) <= cap
+        s.runner.max_step_graphs, s.runner.evict_idle_steps = cap, idle
+        seen = set()
+        outs.append({})
+        for st in steps:                       # helpers.replay, watching which shapes are held
+            for k, v in helpers.replay(s, [st]).items():
+                outs[-1][k] = np.concatenate([outs[-1][k], v]) if k in outs[-1] else v
+            seen |= set(s.runner._step_graphs)
+            assert len(s.runner._step_graphs) <= cap
+        assert (s.runner.padded_graph_steps > 0) == (cap > 0)
+        if idle == 3:
+            assert len(seen) > cap, "recordings that lay idle were replaced"
+        elif cap == 2:
+            assert len(seen) == cap
         s.runner.check_status()
     for k in reqs:
         for o in outs[1:]:
