@@ -119,6 +119,15 @@ class LLMEngine:
         self.requests[rid] = req
         return rid
 
+    def pop_request(self, request_id) -> Request:
+        """Hand a finished request over (tokens in ``output``, why it ended in ``finish_reason``) and forget it;
+        ``generate`` does this itself, a caller of ``add_request`` and ``step`` does it when ``step`` has
+        returned the request."""
+        req = self.requests[request_id]
+        if req.finish_reason is None:
+            raise ValueError(f"request {request_id!r} has not finished")
+        return self.requests.pop(request_id)
+
     def has_work(self) -> bool:
         return self.scheduler.has_work() or self._inflight is not None
 

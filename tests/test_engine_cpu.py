@@ -180,9 +180,17 @@ def test_warm_up_leaves_the_engine_as_it_was(model_dirs, cpu_ops_installed):
     prompt = helpers.random_tokens(512, 9, 77)
     cfg, w = plain_opt.load_model(model_dirs["a"])
     assert eng.generate([prompt], SamplingParams(max_new_tokens=5)) == [plain_opt.greedy_generate(cfg, w, prompt, 5)]
-    eng.add_request(prompt)
+    rid = eng.add_request(prompt, SamplingParams(max_new_tokens=3))
     with pytest.raises(RuntimeError, match="without requests"):
         eng.warm_up(batch_sizes=[1])
+    with pytest.raises(ValueError, match="has not finished"):
+        eng.pop_request(rid)
+    done = []
+    while eng.has_work():
+        done += eng.step()
+    assert [r.id for r in done] == [rid]
+    r = eng.pop_request(rid)
+    assert r.output == plain_opt.greedy_generate(cfg, w, prompt, 3) and r.finish_reason == "length" and not eng.requests
 
 
 def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
