@@ -193,6 +193,38 @@ def test_warm_up_leaves_the_engine_as_it_was(model_dirs, cpu_ops_installed):
     assert r.output == plain_opt.greedy_generate(cfg, w, prompt, 3) and r.finish_reason == "length" and not eng.requests
 
 
+def test_a_step_packed_into_a_padded_shape_is_padded_with_what_kernels_skip(model_dirs, cpu_ops_installed):
+    """The index arrays of a step written into a layout with room to spare: the step's own part is what an exact
+    layout gets, the rest are tokens at position -1, requests without tokens, single-token entries -1 and tiles
+    whose offset lies past every request."""
+    from swifttransformer_b200.engine.step import StepEntry
+    s = session(model_dirs["c"], "c", 1024, max_requests=8, max_batch_tokens=1024)
+    r = s.runner
+    slots = [s.cache.alloc_slot() for _ in range(3)]
+    entries = [StepEntry(slots[0], list(range(3, 203)), 0, [199]),      # a portion of 200 tokens: two tiles
+               StepEntry(slots[1], [7], 0, [0]),                        # single tokens: attention entries
+               StepEntry(slots[2], [8, 9, 10], 0, [])]
+    exact, padded = r._layout(204, 3, 2), r._layout(256, 4, 4)
+    he, hp = np.zeros(exact["total"], np.int32), np.full(padded["total"], -77, np.int32)
+    ie, ip = r._pack(entries, exact, he), r._pack(entries, padded, hp)
+    assert ie["N"] == ip["N"] == 204 and ip["n_items"] == 4 and ip["n_tiles"] == 2
+
+    def part(h, lay, name):
+        o, n = lay[name]
+        return h[o:o + n]
+    for name in exact:
+        if name != "total":
+            k = exact[name][1]
+            assert np.array_equal(part(hp, padded, name)[:k], part(he, exact, name)), name
+    assert np.all(part(hp, padded, "positions")[204:] == -1)
+    assert np.all(part(hp, padded, "q_start")[4:] == 204), "a padding request has no tokens"
+    assert np.all(part(hp, padded, "items")[4:] == -1) and list(part(hp, padded, "items")[:4]) == [200, 201, 202, 203]
+    tiles = part(hp, padded, "tiles").reshape(-1, 2)
+    assert [tuple(t) for t in tiles[:2]] == [(0, 0), (0, 128)] or [tuple(t) for t in tiles[:2]] == [(0, 128), (0, 0)]
+    assert np.all(tiles[2:, 1] >= 1 << 24) and np.all(part(hp, padded, "token_from") == -1)
+    assert -77 not in hp, "every word of the padded layout is written"
+
+
 def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
     from swifttransformer_b200 import ops
     from swifttransformer_b200.sampling import Sampler, SamplingParams
