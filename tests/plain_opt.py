@@ -4,7 +4,11 @@ This file is the tests' oracle.  It shares no code with the package: it has
 its own safetensors reader, its own config handling and computes with numpy
 (float64 by default).  It rests on the reference's formulas (the reference's
 model code needs a GPU, MPI and a missing submodule, so it cannot be run or
-compiled on a CPU); each function cites the lines it restates.  Where the
+compiled on a CPU); each function cites the lines it restates.  What of the
+reference does run on a CPU is its offline weight converter: its output for a
+tiny random model is kept under tests/golden/, and tests/test_golden_converter.py
+checks that this file's logits equal those of the reference's order of
+operations on the converter's tensors (fused q|k|v, transposes, cut positions).  Where the
 reference has no code for an option (post-LN, project_in/out, no bias, no
 affine), the definition used is stated in the function.
 """
