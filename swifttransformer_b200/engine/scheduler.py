@@ -105,10 +105,14 @@ class Scheduler:
             if plan or not self.has_work():
                 return plan
             # nothing could be scheduled although there is work: no running request can move and
-            # none can be admitted.  Free the pages of the request admitted last, or give up on a
-            # request that cannot even start in an empty pool.
-            if self.running:
+            # none can be admitted.  Free the pages of the request admitted last; or give up on a
+            # request that cannot move although it is the only one that holds pages (preempted, it
+            # would start again and come to the same place for ever), or that cannot even start in
+            # an empty pool.
+            if len(self.running) > 1:
                 self._preempt(max(self.running, key=lambda r: r.admitted_at))
+            elif self.running:
+                self._finish(self.running[0], "cache_full")
             else:
                 req = self.waiting.popleft()
                 self._finish(req, "cache_full")

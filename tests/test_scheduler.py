@@ -177,3 +177,58 @@ def test_update_in_two_halves_for_steps_launched_ahead():
     assert cache.free_pages == cache.total_pages
     with pytest.raises(ValueError):
         s.resolve([None], [])
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_invariants_under_random_load(seed):
+    """Random pools, budgets, arrivals and lengths: a step never exceeds the token budget or the number of
+    requests, names a request once, continues each request exactly where it stands, samples only at the end of
+    what the request holds; requests arrive while others run; nothing is lost, every request ends with the tokens
+    it was drawn (whatever was preempted in between), and the pool is whole again."""
+    import random
+    rnd = random.Random(seed)
+    page = rnd.choice([2, 4, 8])
+    max_seqs = rnd.randint(1, 6)
+    budget = rnd.randint(4, 40)
+    chunk = rnd.randint(1, budget)
+    num_pages = rnd.randint(8, 40)
+    cache, s = make(num_pages=num_pages, page_size=page, max_seqs=max_seqs, budget=budget, chunk=chunk, max_positions=120)
+    todo = [(i, rnd.randint(1, 60), rnd.randint(1, 12)) for i in range(rnd.randint(3, 14))]
+    drawn = {}                                   # request id -> tokens it was handed, in order
+    steps = 0
+    while todo or s.has_work():
+        while todo and (not s.has_work() or rnd.random() < 0.4):
+            i, n, m = todo.pop(0)
+            s.add(req(i, n, max_new=m))
+        plan = s.schedule()
+        assert sum(p.n for p in plan) <= budget and len(plan) <= max_seqs
+        assert len({p.request.id for p in plan}) == len(plan)
+        for p in plan:
+            r = p.request
+            assert r.state == RUNNING and p.n >= 1 and r.n_computed + p.n <= len(r.tokens)
+            assert p.samples == (r.n_computed + p.n == len(r.tokens))
+            assert cache.lengths[r.slot] == r.n_computed
+        toks = []
+        for p in plan:
+            if p.samples:
+                t = 1000 * p.request.id + len(p.request.output)      # a token that says whose it is and which
+                drawn.setdefault(p.request.id, []).append(t)
+                toks.append(t)
+        # the step "runs": pages for its tokens exist, lengths move on
+        for p in plan:
+            assert cache.reserve(p.request.slot, p.request.n_computed, p.request.n_computed + p.n)
+            cache.commit(p.request.slot, p.request.n_computed + p.n)
+        s.update(plan, toks)
+        cache.check()
+        steps += 1
+        assert steps < 5000
+    assert cache.free_pages == cache.total_pages and cache.num_free_slots == max_seqs
+    assert len(s.finished) == len(drawn) + sum(1 for r in s.finished if not r.output)
+    for r in s.finished:
+        # the tokens a request keeps in the cache: all but the one drawn last
+        fits_alone = len(r.prompt) + r.params.max_new_tokens - 1 <= num_pages * page
+        assert (r.finish_reason == "cache_full") == (not fits_alone), (r.id, r.finish_reason, len(r.prompt))
+        if fits_alone:
+            assert r.finish_reason == "length" and r.output == drawn[r.id]
+        else:
+            assert r.output == drawn.get(r.id, [])
