@@ -89,6 +89,14 @@ class PagedGroup:
             return 0
         return max(0, start - self.spec.window + 1) // self.page_size
 
+    def peak_pages(self, end: int, portion: int) -> int:
+        """The most pages a request holds at any time while it is brought to ``end`` tokens in portions of at
+        most ``portion``: all of them, or what a window and one portion span."""
+        total = (end + self.page_size - 1) // self.page_size
+        if self.spec.window is None:
+            return total
+        return min(total, (self.spec.window - 1 + portion + self.page_size - 1) // self.page_size + 1)
+
     def missing(self, slot: int, start: int, end: int) -> List[int]:
         """Logical pages that positions start..end-1 need and the slot does not hold."""
         if end <= start:
@@ -198,6 +206,12 @@ class CacheManager:
     def pages_missing(self, slot: int, start: int, end: int) -> int:
         """How many pages (summed over groups) positions start..end-1 still need."""
         return sum(len(g.missing(slot, start, end)) for g in self.groups)
+
+    def pages_to_come(self, slot: Optional[int], end: int, portion: int) -> List[int]:
+        """Per group: the pages a request will still ask for until it holds ``end`` tokens, beyond those its
+        slot holds now (slot None: a request that holds nothing yet)."""
+        return [max(0, g.peak_pages(end, portion) - (len(g.pages[slot]) if slot is not None else 0))
+                for g in self.groups]
 
     def can_reserve(self, slot: int, start: int, end: int) -> bool:
         return all(len(g.missing(slot, start, end)) <= g.pool.num_free for g in self.groups)

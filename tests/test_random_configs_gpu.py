@@ -62,12 +62,14 @@ def test_random_configuration_replays_like_plain(tmp_path, case):
             assert s.cache.free_pages == s.cache.total_pages
 
 
-# kept from a draw of sixteen: head size 128 with a pool of five pages, 21 and 22 heads, head size 8; one to six
-# preemptions each, steps launched ahead or not
-@pytest.mark.parametrize("case", [2, 12, 13, 15])
+# kept from a draw of forty: head size 128 with pages of 64 positions, head sizes 8, 16 and 48, 3 to 24 heads, steps
+# launched ahead or not; in all but the first the pool, which holds the prompts and no more, runs out while the
+# requests decode and one of them is preempted
+@pytest.mark.parametrize("case", [2, 15, 17, 38])
 def test_random_configuration_generates_like_plain(tmp_path, case):
-    """Greedy generation through LLMEngine in float32 (scheduler, portions, recorded steps, preemption when
-    the pool is a third of what the requests need) equals the plain implementation's token for token."""
+    """Greedy generation through LLMEngine in float32 (scheduler, portions, recorded steps, admission held
+    back and preemption when the pool holds little more than the prompts) equals the plain implementation's
+    token for token."""
     import plain_opt
     from swifttransformer_b200.config import OptConfig
     from swifttransformer_b200.engine.engine import LLMEngine
@@ -84,7 +86,7 @@ def test_random_configuration_generates_like_plain(tmp_path, case):
     prompts = [helpers.random_tokens(cfg["vocab_size"], n, 11 * case + i) for i, n in enumerate(lens)]
     per_request = [(n + m + page - 1) // page + 1 for n, m in zip(lens, news)]
     tight = rng.random() < 0.5
-    num_pages = max(max(per_request) + 1, sum(per_request) // 3) if tight else sum(per_request) + 4
+    num_pages = max(max(per_request), sum((n + page - 1) // page for n in lens)) if tight else sum(per_request) + 4
     budget = int(rng.choice([48, 64, 100, 256]))
     eng = LLMEngine(model_dir, dtype="float32", device="cuda", page_size=page, num_pages=num_pages,
                     max_batch_tokens=budget, chunk_size=int(rng.choice([16, 32, budget])),
@@ -95,4 +97,4 @@ def test_random_configuration_generates_like_plain(tmp_path, case):
     for p, o, m in zip(prompts, outs, news):
         assert o == plain_opt.greedy_generate(w_cfg, w, p, m), (case, len(p), m)
     assert eng.cache.free_pages == eng.cache.total_pages
-    assert eng.scheduler.num_preemptions > 0, "these cases were kept because their pools run out"
+    assert tight and (eng.scheduler.num_preemptions > 0 or case == 2), "these cases were kept because their pools run out"

@@ -232,3 +232,43 @@ def test_invariants_under_random_load(seed):
             assert r.finish_reason == "length" and r.output == drawn[r.id]
         else:
             assert r.output == drawn.get(r.id, [])
+
+
+def test_a_newcomer_waits_until_the_pool_holds_all_its_tokens():
+    """10 pages of 4 positions.  A (30 tokens, portions of 8) runs; B (20 tokens) would get its first portion
+    at once, but not the pages for all its tokens beside what A will still ask for: admitted on the strength of
+    that portion it would be preempted half-way and start again.  It waits; nothing is computed twice."""
+    cache, s = make(num_pages=10, page_size=4, max_seqs=4, budget=16, chunk=8)
+    s.add(req("A", 30, max_new=2))
+    s.add(req("B", 20, max_new=2))
+    s.add(req("C", 3, max_new=2))              # small enough to fit beside A, but behind B: first come first served
+    computed = 0
+    admitted_b_at = None
+    steps = 0
+    while s.has_work():
+        plan, _ = run_step(s)
+        computed += sum(p.n for p in plan)
+        ids = [p.request.id for p in plan]
+        if "B" in ids and admitted_b_at is None:
+            admitted_b_at = steps
+            a = next(r for r in s.finished + s.running if r.id == "A")
+            assert a.remaining <= 1, "A had all its prompt pages before B came in"
+        steps += 1
+    assert s.num_preemptions == 0
+    assert computed == sum(len(r.prompt) + len(r.output) - 1 for r in s.finished) == 30 + 20 + 3 + 3
+    assert sorted(r.id for r in s.finished) == ["A", "B", "C"]
+    assert admitted_b_at is not None and admitted_b_at >= 3
+
+
+def test_a_request_larger_than_the_pool_does_not_hold_the_queue():
+    cache, s = make(num_pages=6, page_size=4, max_seqs=4, budget=16, chunk=8)
+    s.add(req("small", 5, max_new=2))
+    s.add(req("big", 40, max_new=2))           # 40 tokens never fit into 24 positions
+    s.add(req("next", 6, max_new=2))
+    plan, _ = run_step(s)
+    assert [p.request.id for p in plan] == ["small", "next"]
+    big = next(r for r in s.finished if r.id == "big")
+    assert big.finish_reason == "cache_full" and big.output == []
+    while s.has_work():
+        run_step(s)
+    assert sorted(r.id for r in s.finished) == ["big", "next", "small"] and s.num_preemptions == 0
