@@ -35,10 +35,20 @@ class EngineConfig:
     # of 512: every step reads all weights once)
     chunk_size: int = 2048
     max_num_seqs: int = 256             # most requests running at a time
+    # most tokens one request may hold (prompt and output): block tables have room for this many.  None: the
+    # model's own limit (its context length or what its position encoding can encode), and for a model
+    # that sets none, DEFAULT_MAX_SEQ_LEN
+    max_seq_len: Optional[int] = None
     use_cuda_graphs: bool = True        # record decode-only steps once per batch size and replay them
     # launch the next step before the tokens of this one have been read: they reach it on the device, and
     # the host's work for a step (scheduling, staging, the read itself) overlaps the GPU's
     pipeline: bool = True
+    # NVTX ranges around every step and, in steps that are launched kernel by kernel, around every layer
+    # (a profiler's timeline then shows them; recorded steps replay as one graph launch)
+    nvtx: bool = False
+
+
+DEFAULT_MAX_SEQ_LEN = 4096
 
 
 class _Launched:
@@ -69,7 +79,11 @@ class LLMEngine:
         self.model = load_model(model, dtype, device) if isinstance(model, str) else model
         self.device = self.model.device
         specs = self.model.definition.cache_specs()
-        max_len = self.model.max_positions or 1 << 20
+        limits = [n for n in (self.model.max_positions, cfg.max_seq_len) if n is not None]
+        max_len = min(limits) if limits else DEFAULT_MAX_SEQ_LEN
+        if max_len < 1:
+            raise ValueError("max_seq_len must be positive")
+        self.max_seq_len = max_len
         num_pages = cfg.num_pages
         if num_pages is None:
             num_pages = self._pages_that_fit(specs, cfg, max_len)
@@ -77,12 +91,12 @@ class LLMEngine:
                                   cfg.max_num_seqs, max_len)
         self.runner = ModelRunner(self.model, self.cache, cfg.max_batch_tokens,
                                   use_cuda_graphs=cfg.use_cuda_graphs)
-        self.scheduler = Scheduler(self.cache, cfg.max_batch_tokens, cfg.chunk_size, cfg.max_num_seqs,
-                                   self.model.max_positions)
+        self.runner.nvtx = cfg.nvtx
+        self.scheduler = Scheduler(self.cache, cfg.max_batch_tokens, cfg.chunk_size, cfg.max_num_seqs, max_len)
         self.sampler = Sampler(self.device)
         self._ids = itertools.count()
         self.requests: Dict[Any, Request] = {}
-        self.stats = dict(steps=0, prompt_tokens=0, decode_tokens=0)
+        self._stats = dict(steps=0, prompt_tokens=0, decode_tokens=0)
         self._inflight: Optional[_Launched] = None
         # sampled tokens come back through pinned buffers used in turn (a step's buffer is read before
         # the step after next is launched)
@@ -91,18 +105,36 @@ class LLMEngine:
         self._token_turn = 0
 
     def _pages_that_fit(self, specs, cfg: EngineConfig, max_len: int) -> int:
-        from ..parts.base import PagedKVSpec
+        """Pages per group so that the cache (every group's pages, and the fixed-size state of every
+        request slot) takes ``memory_fraction`` of the free device memory, and no more than all slots
+        filled to the length limit would need."""
+        from ..parts.base import PagedKVSpec, StateSpec
         esize = torch.empty((), dtype=self.model.dtype).element_size()
         per_page = sum(2 * s.num_kv_heads * s.head_dim * cfg.page_size * esize
                        for s in specs if isinstance(s, PagedKVSpec))
         if per_page == 0:
             return 1
+        state_bytes = 0
+        for s in specs:
+            if isinstance(s, StateSpec):
+                n = cfg.max_num_seqs * torch.empty((), dtype=s.dtype).element_size()
+                for k in s.shape:
+                    n *= k
+                state_bytes += n
         if self.device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(self.device)
         else:
             free = 1 << 30
         want = cfg.max_num_seqs * ((max_len + cfg.page_size - 1) // cfg.page_size)
-        return max(1, min(want, int(free * cfg.memory_fraction) // per_page))
+        return max(1, min(want, (int(free * cfg.memory_fraction) - state_bytes) // per_page))
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        """Counters since the engine was made: steps, prompt and decode tokens run, requests preempted;
+        and the page pool now (pages free and in all; the smallest group's where there are several)."""
+        return dict(self._stats, preemptions=self.scheduler.num_preemptions, pages_free=self.cache.free_pages,
+                    pages_total=self.cache.total_pages, running=len(self.scheduler.running),
+                    waiting=len(self.scheduler.waiting))
 
     # ------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None):
@@ -127,6 +159,19 @@ class LLMEngine:
         if req.finish_reason is None:
             raise ValueError(f"request {request_id!r} has not finished")
         return self.requests.pop(request_id)
+
+    def abort_request(self, request_id) -> Request:
+        """Take a request out, wherever it is: waiting, running, or with a token still on its way from a
+        step that has been launched ahead.  Its pages and slot are free when this returns (a step in
+        flight may still write the pages; whoever gets them next writes them after it, in stream
+        order, and reads only what it wrote itself), what steps in flight compute for it is dropped, and
+        no later ``step`` reports it.  Returns the request with the tokens it had got (``finish_reason``
+        "aborted", or what it finished with if it already had).  The reference's nearest thing is the
+        removal of finished requests from its static batch (src/examples/lib/inference_batch.cc:196-218)."""
+        req = self.requests.pop(request_id)
+        if req.finish_reason is None:
+            self.scheduler.abort(req)
+        return req
 
     def has_work(self) -> bool:
         return self.scheduler.has_work() or self._inflight is not None
@@ -155,12 +200,20 @@ class LLMEngine:
                 samplers.append(r.params)
                 counters.append(len(r.output))
             if s.n == 1 and r.n_computed >= len(r.prompt):
-                self.stats["decode_tokens"] += 1
+                self._stats["decode_tokens"] += 1
             else:
-                self.stats["prompt_tokens"] += s.n
+                self._stats["prompt_tokens"] += s.n
         feedback = (prev.sampled, token_from) if prev is not None and any(f >= 0 for f in token_from) else None
-        logits = self.runner.step(entries, feedback)
-        self.stats["steps"] += 1
+        if self.config.nvtx and self.device.type == "cuda":
+            torch.cuda.nvtx.range_push(f"step {self._stats['steps']}: {len(entries)} requests, "
+                                       f"{sum(len(e.tokens) for e in entries)} tokens")
+            try:
+                logits = self.runner.step(entries, feedback)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        else:
+            logits = self.runner.step(entries, feedback)
+        self._stats["steps"] += 1
         if samplers:
             out.n_samples = len(samplers)
             out.sampled = self.sampler.sample_on_device(logits, samplers, counters)
@@ -198,14 +251,14 @@ class LLMEngine:
         return self._drain_finished(done)
 
     def _drain_finished(self, done: List[Request]) -> List[Request]:
-        # requests the scheduler gave up on (cache_full) finish without a step of their own
+        """``done`` and whatever else the scheduler finished since the last call (requests it gave up on
+        with cache_full finish without a step of their own); aborted requests are not reported."""
         seen = {id(r) for r in done}
-        for r in self.scheduler.finished:
-            if id(r) not in seen and r.id in self.requests and not getattr(r, "_reported", False):
+        for r in self.scheduler.take_finished():
+            if id(r) not in seen and self.requests.get(r.id) is r:
+                seen.add(id(r))
                 done.append(r)
-        for r in done:
-            r._reported = True
-        return done
+        return [r for r in done if self.requests.get(r.id) is r]
 
     # ------------------------------------------------------------- warm-up
     def warm_up(self, prompt_lengths: Sequence[int] = (), batch_sizes: Sequence[int] = (1,)) -> int:
@@ -217,15 +270,15 @@ class LLMEngine:
             raise RuntimeError("warm_up needs an engine without requests")
         r = self.runner
         before = len(r._graphs) + len(r._step_graphs)
-        stats = dict(self.stats)
-        limit = self.model.max_positions
+        stats = dict(self._stats)
+        limit = self.max_seq_len
         for n in prompt_lengths:
             n = max(1, min(int(n), limit - 2 if limit else int(n)))
             self.generate([[0] * n], SamplingParams(max_new_tokens=2, ignore_eos=True))
         for b in batch_sizes:
             b = max(1, min(int(b), self.config.max_num_seqs))
             self.generate([[0]] * b, SamplingParams(max_new_tokens=3, ignore_eos=True))
-        self.stats = stats
+        self._stats = stats
         return len(r._graphs) + len(r._step_graphs) - before
 
     # ------------------------------------------------------------ generate

@@ -90,12 +90,27 @@ class Scheduler:
             raise ValueError("a request needs at least one prompt token")
         limit = self.max_positions
         if limit is not None and len(req.prompt) > limit:
-            raise ValueError(f"a prompt of {len(req.prompt)} tokens exceeds the model's {limit} positions")
+            raise ValueError(f"a prompt of {len(req.prompt)} tokens exceeds the limit of {limit} positions per request")
         req.state = WAITING
         self.waiting.append(req)
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
+
+    def take_finished(self) -> List[Request]:
+        """The requests that finished since the last call (the scheduler keeps none of them)."""
+        done, self.finished = self.finished, []
+        return done
+
+    def abort(self, req: Request) -> None:
+        """Take a request out of the queues now; its slot and pages are free when this returns.  Tokens a
+        step in flight draws for it are dropped (``update`` and ``resolve`` skip it)."""
+        if req.state == FINISHED:
+            return
+        if req.state == WAITING:
+            self.waiting.remove(req)
+        req.output = [t for t in req.output if t != PENDING]
+        self._finish(req, "aborted")
 
     # ----------------------------------------------------------- one step
     def schedule(self) -> List[Scheduled]:
@@ -280,6 +295,8 @@ class Scheduler:
             if h is None:
                 continue
             req, idx = h
+            if req.finish_reason == "aborted":
+                continue
             tok = int(tok)
             req.output[idx] = tok
             p = req.params

@@ -22,7 +22,8 @@ from __future__ import annotations
 
 import dataclasses
 import gc
-from typing import Any, Dict, List, Optional, Sequence
+from math import gcd
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -30,7 +31,7 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager
 from ..models.base import CausalLM
-from ..parts.attention import SHORT_PORTION
+from ..parts.base import StepPlan
 
 
 class OutOfPages(RuntimeError):
@@ -49,44 +50,6 @@ class StepEntry:
     want: Sequence[int] = ()        # places among `tokens` whose logits are wanted
 
 
-# Keys one block of the decode attention walks alone before the key range is cut into parts (for head sizes
-# up to 64, where a block has eight warps; half of it beyond).  Recorded decode steps are keyed by the number
-# of such spans the longest request needs, so the cut follows the real lengths, not the longest possible one.
-KEYS_PER_BLOCK = 768
-
-
-def choose_splits(n_items: int, nh: int, max_kv: int, sms: int = 148, head_dim: int = 64) -> int:
-    """Parts the key range of a single-token query is cut into.
-
-    Measured on one B200 at context ~550 with 32 heads.  Head size 64 (OPT-1.3B, tensor-core kernel with
-    eight warps per block): cutting costs a merge (a trip through global memory and an atomic) and one part
-    is best at every batch (ms per step, one part against two blocks per SM: batch 1: 1.043 / 1.084,
-    4: 1.116 / 1.167, 8: 1.299 / 1.323); longer ranges are cut so that a block walks about KEYS_PER_BLOCK
-    keys, as long as the launch stays within two blocks per SM.  Head size 128 (OPT-6.7B, lanes kernel, whose
-    blocks walk their keys more slowly): two blocks per SM, parts of at least 128 keys (batch 1: 3.20 with
-    ten parts against 3.28 with two; batch 8: 3.78 with two against 3.86 with one)."""
-    blocks = max(1, n_items * nh)
-    if blocks * 64 >= 250 * head_dim:
-        return 1
-    room = max(1, (2 * sms + blocks - 1) // blocks)
-    if head_dim <= 64:
-        want = (max_kv + KEYS_PER_BLOCK - 1) // KEYS_PER_BLOCK
-    else:
-        want = max(1, max_kv // 128)
-    return max(1, min(want, room, 32))
-
-
-class AttentionPlan:
-    """Which of the step's tokens go to which attention kernel (bfloat16 path)."""
-
-    def __init__(self, items, n_items, tiles, n_tiles, max_item_kv):
-        self.items, self.n_items, self.tiles, self.n_tiles = items, n_items, tiles, n_tiles
-        self.max_item_kv = max_item_kv
-
-    def splits(self, nh: int, head_dim: int = 64) -> int:
-        return choose_splits(self.n_items, nh, self.max_item_kv, head_dim=head_dim)
-
-
 class StepContext:
     """Everything a part may ask about the running step.
 
@@ -94,6 +57,7 @@ class StepContext:
     start_pos[B], kv_len[B] (length after the step), slots[B], want_rows[n_want].
     Host lists of the same names with an ``h_`` prefix (None while a graph is recorded
     or replayed: a part that needs them is not ``graph_safe``).
+    ``plan(name)``: what the step plan of that name (parts.base.StepPlan) made of this step.
     """
 
     def __init__(self):
@@ -107,11 +71,12 @@ class StepContext:
         self.status: Optional[torch.Tensor] = None
         self.act_dtype: torch.dtype = torch.float32
         self.device: Optional[torch.device] = None
-        self._plan: Optional[AttentionPlan] = None
+        self.nvtx = False                # the model wraps every layer in an NVTX range
+        self._plans: Dict[str, Any] = {}
         self._scratch_owner: Any = None
 
-    def attention_plan(self) -> AttentionPlan:
-        return self._plan
+    def plan(self, name: str) -> Any:
+        return self._plans[name]
 
     def scratch_f32(self, n: int) -> torch.Tensor:
         return self._scratch_owner._scratch(n)
@@ -144,18 +109,46 @@ class _Staging:
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 
+# tokens of a recorded step that is not decode-only are padded to a multiple of this (and of what the
+# model's step plans ask for), so that prompts of any length share a few recordings
+PADDED_TOKEN_STEP = 64
+
 
 class _RecordedStep:
-    """A step of fixed shape recorded as a CUDA graph: its context, its scratch memory, the recording."""
+    """A step of fixed shape recorded as a CUDA graph and replayed: ``n_cap`` tokens, ``b_cap`` requests,
+    ``w_cap`` wanted rows, and for every step plan of the model the key it gave.  What a step does not fill
+    is padding that every kernel skips: tokens at position -1, requests without tokens (see
+    ModelRunner._pack).  ``decode``: every request brings one token and wants its logits; the arrays that
+    are then the same in every step are written once."""
 
-    def _init_recording(self, runner: "ModelRunner") -> None:
+    def __init__(self, runner: "ModelRunner", n_cap: int, b_cap: int, w_cap: int, plan_keys: Dict[str, Tuple],
+                 decode: bool = False):
         self.runner = runner
+        self.n_cap, self.b_cap, self.w_cap, self.decode = n_cap, b_cap, w_cap, decode
         self._scratch_buf: Optional[torch.Tensor] = None
         self._frozen = False
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.kernels = 0
         self.last_used = 0               # the runner's step count when this recording last ran
+        self.lay = lay = runner._layout(n_cap, b_cap, w_cap)
+        self.staging = _Staging(lay["total"], runner.device)
+        self.ctx = runner._context_over(self.staging.dev, lay, n_cap, b_cap, w_cap, plan_keys, self)
+        self.token_from = self._view("token_from")
+        if decode:
+            assert n_cap == b_cap == w_cap
+            ar = np.arange(n_cap + 1, dtype=np.int32)
+            self._ones = np.ones(n_cap, dtype=np.int32)
+            self._arange = ar
+            for host in self.staging.hosts:
+                h = host.numpy()
+                for name, values in (("seq_of_token", ar[:-1]), ("q_start", ar), ("want_rows", ar[:-1])):
+                    o, n = lay[name]
+                    h[o:o + n] = values
+
+    def _view(self, name: str) -> torch.Tensor:
+        o, n = self.lay[name]
+        return self.staging.dev[o:o + n]
 
     def _scratch(self, n: int) -> torch.Tensor:
         if self._scratch_buf is None or self._scratch_buf.numel() < n:
@@ -164,9 +157,45 @@ class _RecordedStep:
             self._scratch_buf = torch.empty(max(n, 1), dtype=torch.float32, device=self.runner.device)
         return self._scratch_buf
 
+    def fill(self, entries: Sequence[StepEntry], feedback=None) -> int:
+        """Stage the step's index arrays and start their copy; returns the number of wanted rows."""
+        r = self.runner
+        h = self.staging.begin()
+        if not self.decode:
+            info = r._pack(entries, self.lay, h, self.n_cap, self.b_cap, feedback)
+            self.staging.commit(self.lay["total"])
+            return info["W"]
+        cap, b, lay = self.n_cap, len(entries), self.lay
+        start = np.fromiter((e.start_pos for e in entries), dtype=np.int32, count=b)
+        for name, values, pad in (("token_ids", [e.tokens[0] for e in entries], 0), ("positions", start, -1),
+                                  ("start_pos", start, 0), ("kv_len", start + 1, 0),
+                                  ("slots", [e.slot for e in entries], 0),
+                                  ("token_from", feedback[1] if feedback is not None else (), -1)):
+            o = lay[name][0]
+            k = len(values)
+            h[o:o + k] = values
+            h[o + k:o + cap] = pad
+        for p in r.plans:
+            o, n = lay["plan:" + p.name]
+            p.fill(self._ones[:b], self._arange[:b + 1], start, h[o:o + n], cap, cap)
+        self.staging.commit(lay["total"])
+        return b
+
+    def run(self, entries: Sequence[StepEntry], feedback=None) -> Optional[torch.Tensor]:
+        if self.graph is None:
+            self.record()
+        w = self.fill(entries, feedback)
+        if feedback is not None:
+            ops.gather_where_i32(self.ctx.token_ids, self.token_from, feedback[0])
+        self.graph.replay()
+        return self.logits[:w] if w else None
+
     def record(self) -> None:
         r = self.runner
-        # once without recording: sizes the scratch memory and lets libraries set themselves up
+        # Once without recording, on a step that is all padding: it sizes the scratch memory and lets
+        # libraries set themselves up, and it writes nothing - neither pages nor per-request state - so a
+        # shape's first use runs the real step once, like every later use.
+        self.fill([])
         r.model.forward(self.ctx, r._entries)
         torch.cuda.synchronize()
         self._frozen = True
@@ -188,103 +217,11 @@ class _RecordedStep:
         self.graph = g
 
 
-class _DecodeGraph(_RecordedStep):
-    """One recorded decode step for up to ``cap`` requests."""
-
-    FIELDS = ("token_ids", "positions", "start_pos", "kv_len", "slots")
-
-    def __init__(self, runner: "ModelRunner", cap: int, max_kv: int):
-        self._init_recording(runner)
-        self.cap = cap
-        self.staging = _Staging(6 * cap, runner.device)
-        dev = runner.device
-        ar = torch.arange(cap + 1, dtype=torch.int32, device=dev)
-        d = self.staging.dev
-        ctx = StepContext()
-        ctx.n_tokens = ctx.n_seqs = ctx.n_want = cap
-        ctx.token_ids, ctx.positions = d[0:cap], d[cap:2 * cap]
-        ctx.start_pos, ctx.kv_len, ctx.slots = d[2 * cap:3 * cap], d[3 * cap:4 * cap], d[4 * cap:5 * cap]
-        self.token_from = d[5 * cap:6 * cap]     # per token: index into the previous step's sampled tokens, or -1
-        ctx.seq_of_token, ctx.q_start, ctx.want_rows = ar[:cap], ar, ar[:cap]
-        ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, dev
-        ctx._plan = AttentionPlan(None, cap, None, 0, max_kv)
-        ctx._scratch_owner = self
-        self.ctx = ctx
-        self._keep = ar
-
-    def fill(self, entries: Sequence[StepEntry], token_from: Optional[Sequence[int]] = None) -> None:
-        cap, b = self.cap, len(entries)
-        h = self.staging.begin()
-        h[0:cap] = 0
-        h[cap:2 * cap] = -1                      # padding entries: position -1, skipped by every kernel
-        h[2 * cap:5 * cap] = 0
-        for i, e in enumerate(entries):
-            h[i] = e.tokens[0]
-            h[cap + i] = e.start_pos
-            h[2 * cap + i] = e.start_pos
-            h[3 * cap + i] = e.start_pos + 1
-            h[4 * cap + i] = e.slot
-        if token_from is not None:
-            h[5 * cap:6 * cap] = -1
-            h[5 * cap:5 * cap + b] = token_from
-            self.staging.commit(6 * cap)
-        else:
-            self.staging.commit(5 * cap)
-
-    def run(self, entries: Sequence[StepEntry], feedback=None) -> torch.Tensor:
-        self.fill(entries, feedback[1] if feedback else None)
-        if self.graph is None:
-            self.record()
-        if feedback:
-            ops.gather_where_i32(self.ctx.token_ids, self.token_from, feedback[0])
-        self.graph.replay()
-        return self.logits[:len(entries)]
-
-
-class _StepGraph(_RecordedStep):
-    """One recorded step of a padded shape, for steps that are not decode-only: ``n_pad`` tokens (a multiple
-    of the attention tile), ``b_pad`` requests, ``i_pad`` single-token attention entries, ``w_pad`` wanted
-    rows.  What a step does not fill is padding that every kernel skips (see ModelRunner._pack)."""
-
-    def __init__(self, runner: "ModelRunner", n_pad: int, b_pad: int, i_pad: int, w_pad: int, max_kv: int):
-        self._init_recording(runner)
-        self.n_pad = n_pad
-        self.lay = lay = runner._layout(n_pad, b_pad, w_pad)
-        self.staging = _Staging(lay["total"], runner.device)
-        d = self.staging.dev
-
-        def view(name):
-            o, n = lay[name]
-            return d[o:o + n]
-
-        t_pad = lay["tiles"][1] // 2
-        ctx = StepContext()
-        ctx.n_tokens, ctx.n_seqs, ctx.n_want = n_pad, b_pad, w_pad
-        ctx.token_ids, ctx.positions, ctx.seq_of_token = view("token_ids"), view("positions"), view("seq_of_token")
-        ctx.q_start, ctx.start_pos, ctx.kv_len, ctx.slots = (view("q_start"), view("start_pos"), view("kv_len"),
-                                                             view("slots"))
-        ctx.want_rows = view("want_rows") if w_pad else None
-        ctx.status, ctx.act_dtype, ctx.device = runner.status, runner.model.dtype, runner.device
-        ctx._plan = AttentionPlan(view("items")[:i_pad], i_pad, view("tiles"), t_pad, max_kv)
-        ctx._scratch_owner = self
-        self.ctx = ctx
-        self.token_from = view("token_from")
-
-    def run(self, entries: Sequence[StepEntry], feedback=None) -> Optional[torch.Tensor]:
-        r = self.runner
-        h = self.staging.begin()
-        info = r._pack(entries, self.lay, h, feedback)
-        self.staging.commit(self.lay["total"])
-        if self.graph is None:
-            self.record()
-        if feedback is not None:
-            ops.gather_where_i32(self.ctx.token_ids, self.token_from, feedback[0])
-        self.graph.replay()
-        return self.logits[:info["W"]] if info["W"] else None
-
-
 class ModelRunner:
     """Owns the model, its cache and the staging buffers; runs steps."""
+
+    BASE_ARRAYS = ("token_ids", "positions", "seq_of_token", "q_start", "start_pos", "kv_len", "slots",
+                   "want_rows", "token_from")
 
     def __init__(self, model: CausalLM, cache: CacheManager, max_batch_tokens: int = 8192,
                  use_cuda_graphs: bool = True):
@@ -293,20 +230,25 @@ class ModelRunner:
         self.max_batch_tokens = max_batch_tokens
         self.use_cuda_graphs = use_cuda_graphs and self.device.type == "cuda" and model.graph_safe()
         self.max_seqs = cache.max_seqs
-        self.tile_rows = ops.attention_prefill_tile_rows()   # query rows one attention tile covers
-        self._upd_cap = self.max_seqs * cache.max_pages_per_seq + 16
+        # the step plans of the model's mixers, one per name
+        self.plans: List[StepPlan] = model.step_plans()
+        self.token_multiple = PADDED_TOKEN_STEP
+        for p in self.plans:
+            self.token_multiple = self.token_multiple * p.token_multiple // gcd(self.token_multiple, p.token_multiple)
+        self._upd_cap = min(self.max_seqs * cache.max_pages_per_seq, 1 << 16) + 16
         words = self._layout(max_batch_tokens, self.max_seqs, max_batch_tokens)["total"]
         self._staging = _Staging(words, self.device)
         self._upd_staging = _Staging(1 + 2 * self._upd_cap, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch_buf: Optional[torch.Tensor] = None
         self._entries = cache.entries()
-        self._graphs: Dict[Any, _DecodeGraph] = {}      # (rows, spans of KEYS_PER_BLOCK keys) -> recorded step
-        # recorded steps of padded shapes for everything else (prompt portions, mixed steps); bounded in number:
-        # a shape beyond the bound takes the place of the recording that has not been used for the longest
-        # time if that is more than `evict_idle_steps` steps ago, and runs eagerly otherwise (a working set
-        # larger than the bound must not be recorded over and over: recording costs ~15 eager steps)
-        self._step_graphs: Dict[Any, _StepGraph] = {}
+        # Recorded steps by shape.  Decode-only steps: (bucket of requests, the plans' keys).  Everything else
+        # (prompt portions, mixed steps): (padded tokens, requests, wanted rows, the plans' keys); those are
+        # bounded in number: a shape beyond the bound takes the place of the recording that has not been
+        # used for the longest time if that is more than `evict_idle_steps` steps ago, and runs eagerly
+        # otherwise (a working set larger than the bound must not be recorded over and over).
+        self._graphs: Dict[Any, _RecordedStep] = {}
+        self._step_graphs: Dict[Any, _RecordedStep] = {}
         self.max_step_graphs = 48
         self.evict_idle_steps = 512
         self._retired_h2d_bytes = 0
@@ -315,6 +257,7 @@ class ModelRunner:
         self.steps_run = 0
         self.graph_steps = 0
         self.kernels_last_step = 0
+        self.nvtx = False                # NVTX ranges around the layers of steps that are launched kernel by kernel
 
     # ------------------------------------------------------------ buffers
     def _scratch(self, n: int) -> torch.Tensor:
@@ -323,16 +266,41 @@ class ModelRunner:
         return self._scratch_buf
 
     def _layout(self, n_cap: int, b_cap: int, w_cap: int) -> Dict[str, Any]:
+        """Where each index array of a step of at most n_cap tokens, b_cap requests and w_cap wanted rows
+        lies in the staging buffer: name -> (offset, words); the step plans' arrays follow the step's own."""
         off = 0
         lay: Dict[str, Any] = {}
-        for name, n in (("token_ids", n_cap), ("positions", n_cap), ("seq_of_token", n_cap),
-                        ("q_start", b_cap + 1), ("start_pos", b_cap), ("kv_len", b_cap), ("slots", b_cap),
-                        ("want_rows", w_cap), ("items", n_cap), ("token_from", n_cap),
-                        ("tiles", 2 * ((n_cap + self.tile_rows - 1) // self.tile_rows + b_cap))):
-            lay[name] = (off, n)
+        sizes = dict(token_ids=n_cap, positions=n_cap, seq_of_token=n_cap, q_start=b_cap + 1, start_pos=b_cap,
+                     kv_len=b_cap, slots=b_cap, want_rows=w_cap, token_from=n_cap)
+        for name in self.BASE_ARRAYS:
+            lay[name] = (off, sizes[name])
+            off += sizes[name]
+        for p in self.plans:
+            n = p.words(n_cap, b_cap)
+            lay["plan:" + p.name] = (off, n)
             off += n
         lay["total"] = off
         return lay
+
+    def _context_over(self, dev: torch.Tensor, lay: Dict[str, Any], n: int, b: int, w: int,
+                      plan_keys: Dict[str, Tuple], scratch_owner: Any) -> StepContext:
+        """A step context whose arrays are views of ``dev`` laid out by ``lay``."""
+        def view(name):
+            o, k = lay[name]
+            return dev[o:o + k]
+
+        ctx = StepContext()
+        ctx.n_tokens, ctx.n_seqs, ctx.n_want = n, b, w
+        ctx.token_ids, ctx.positions, ctx.seq_of_token = view("token_ids"), view("positions"), view("seq_of_token")
+        ctx.q_start, ctx.start_pos, ctx.kv_len, ctx.slots = (view("q_start"), view("start_pos"), view("kv_len"),
+                                                             view("slots"))
+        ctx.want_rows = view("want_rows") if w else None
+        ctx.status, ctx.act_dtype, ctx.device = self.status, self.model.dtype, self.device
+        ctx.nvtx = self.nvtx
+        for p in self.plans:
+            ctx._plans[p.name] = p.view(view("plan:" + p.name), plan_keys[p.name], n, b)
+        ctx._scratch_owner = scratch_owner
+        return ctx
 
     @property
     def h2d_bytes(self) -> int:
@@ -359,6 +327,9 @@ class ModelRunner:
                 raise StepError(f"slot {e.slot} holds {self.cache.lengths[e.slot]} tokens, the step says {e.start_pos}")
             if maxpos is not None and e.start_pos + n > maxpos:
                 raise StepError(f"a request would reach {e.start_pos + n} tokens; the model's positions end at {maxpos}")
+            if e.start_pos + n > self.cache.max_seq_len:
+                raise StepError(f"a request would reach {e.start_pos + n} tokens; the cache holds "
+                                f"{self.cache.max_seq_len} per request")
             lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= vocab:
                 raise StepError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
@@ -393,73 +364,56 @@ class ModelRunner:
             assert ok
         self._flush_block_tables()
         before = ops.launch_count()
-        bucket = self._graph_bucket(entries)
-        if bucket:
-            spans = max(-(-(e.start_pos + 1) // KEYS_PER_BLOCK) for e in entries)
-            key = (bucket, spans)
-            if key not in self._graphs:
-                self._graphs[key] = _DecodeGraph(self, bucket, min(spans * KEYS_PER_BLOCK, self.cache.max_seq_len))
-            dg = self._graphs[key]
-            logits = dg.run(entries, feedback)
-            self.graph_steps += 1
-            self.kernels_last_step = dg.kernels
-        else:
-            sg = self._padded_graph(entries)
-            if sg is not None:
-                logits = sg.run(entries, feedback)
-                self.padded_graph_steps += 1
-                self.kernels_last_step = sg.kernels
+        rec = self._recording_for(entries)
+        if rec is not None:
+            logits = rec.run(entries, feedback)
+            if rec.decode:
+                self.graph_steps += 1
             else:
-                ctx = self._build_context(entries, feedback)
-                logits = self.model.forward(ctx, self._entries)
-                self.kernels_last_step = ops.launch_count() - before
+                self.padded_graph_steps += 1
+            self.kernels_last_step = rec.kernels
+        else:
+            ctx = self._build_context(entries, feedback)
+            logits = self.model.forward(ctx, self._entries)
+            self.kernels_last_step = ops.launch_count() - before
         for e in entries:
             self.cache.commit(e.slot, e.start_pos + len(e.tokens))
         self.steps_run += 1
         return logits
 
-    def _graph_bucket(self, entries: Sequence[StepEntry]) -> int:
+    def _recording_for(self, entries: Sequence[StepEntry]) -> Optional[_RecordedStep]:
+        """The recorded step whose shape takes these entries, made if need be; None: run eagerly.
+        Launching a step's kernels and library calls one by one costs the host milliseconds whatever the
+        step's size; replaying a recording costs a few tens of microseconds."""
         if not self.use_cuda_graphs:
-            return 0
-        for e in entries:
-            if len(e.tokens) != 1 or len(e.want) != 1:
-                return 0
+            return None
         b = len(entries)
-        for cap in GRAPH_BUCKETS:
-            if cap >= b:
-                return cap
-        return 0
-
-    def _padded_graph(self, entries: Sequence[StepEntry]) -> Optional[_StepGraph]:
-        """The recorded step whose padded shape takes these entries, made if need be; None: run eagerly.
-        Launching a step's ~190 kernels and library calls one by one costs the host ~2.8 ms whatever the step's
-        size; replaying a recording costs a few tens of microseconds."""
-        if not self.use_cuda_graphs:
+        b_cap = next((c for c in GRAPH_BUCKETS if c >= b), None)
+        if b_cap is None:
             return None
-        lens = [len(e.tokens) for e in entries]
-        n, b = sum(lens), len(entries)
-        w = sum(len(e.want) for e in entries)
-        n_items = sum(x for x in lens if x < SHORT_PORTION)
-        item_kv = max((e.start_pos + x for e, x in zip(entries, lens) if x < SHORT_PORTION), default=0)
-        n_pad = -(-n // self.tile_rows) * self.tile_rows
-        b_pad = next((c for c in GRAPH_BUCKETS if c >= b), None)
-        if b_pad is None:
-            return None
-        i_pad = -(-n_items // 16) * 16
-        w_pad = 0 if w == 0 else (b_pad if w <= b_pad else n_pad)
-        spans = -(-item_kv // KEYS_PER_BLOCK)
-        key = (n_pad, b_pad, i_pad, w_pad, spans)
-        sg = self._step_graphs.get(key)
-        if sg is None:
-            if len(self._step_graphs) >= self.max_step_graphs:
-                oldest = min(self._step_graphs, key=lambda k: self._step_graphs[k].last_used, default=None)
-                if oldest is None or self.steps_run - self._step_graphs[oldest].last_used <= self.evict_idle_steps:
+        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=b)
+        start = np.fromiter((e.start_pos for e in entries), dtype=np.int32, count=b)
+        n = int(lens.sum())
+        decode = n == b and all(len(e.want) == 1 for e in entries)
+        if decode:
+            n_cap = w_cap = b_cap
+        else:
+            w = sum(len(e.want) for e in entries)
+            n_cap = -(-n // self.token_multiple) * self.token_multiple
+            w_cap = 0 if w == 0 else (b_cap if w <= b_cap else n_cap)
+        plan_keys = {p.name: p.shape_key(lens, start, n_cap, b_cap) for p in self.plans}
+        key = (n_cap, b_cap, w_cap) + tuple(plan_keys[p.name] for p in self.plans)
+        held = self._graphs if decode else self._step_graphs
+        rec = held.get(key)
+        if rec is None:
+            if not decode and len(held) >= self.max_step_graphs:
+                oldest = min(held, key=lambda k: held[k].last_used, default=None)
+                if oldest is None or self.steps_run - held[oldest].last_used <= self.evict_idle_steps:
                     return None
-                self._retired_h2d_bytes += self._step_graphs.pop(oldest).staging.bytes_copied
-            sg = self._step_graphs[key] = _StepGraph(self, n_pad, b_pad, i_pad, w_pad,
-                                                     min(max(spans, 1) * KEYS_PER_BLOCK, self.cache.max_seq_len))
-        sg.last_used = self.steps_run
-        return sg
+                self._retired_h2d_bytes += held.pop(oldest).staging.bytes_copied
+            rec = held[key] = _RecordedStep(self, n_cap, b_cap, w_cap, plan_keys, decode=decode)
+        rec.last_used = self.steps_run
+        return rec
 
     def check_status(self) -> None:
         """Raise if a kernel recorded a fault (a hole in a block table).  Synchronises."""
@@ -489,14 +443,15 @@ class ModelRunner:
                 d = self._upd_staging.dev
                 ops.scatter_i32(g.block_table, d[1:1 + n], d[1 + n:1 + 2 * n], d[0:1], n)
 
-    def _pack(self, entries: Sequence[StepEntry], lay: Dict[str, Any], h: np.ndarray, feedback=None):
+    def _pack(self, entries: Sequence[StepEntry], lay: Dict[str, Any], h: np.ndarray, n_cap: int, b_cap: int,
+              feedback=None):
         """Write the step's index arrays into the staging buffer ``h`` laid out by ``lay``.  Where the layout
         has room for more than the step brings (a recorded step of padded shape), the rest is filled with
-        entries every kernel skips: tokens at position -1, requests without tokens, tiles without rows,
-        single-token entries -1.  Returns what describes the step to the host."""
+        entries every kernel skips: tokens at position -1, requests without tokens; the step plans pad
+        their own arrays.  Returns what describes the step to the host."""
         B = len(entries)
-        lens = [len(e.tokens) for e in entries]
-        N = sum(lens)
+        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
+        N = int(lens.sum())
 
         def put(name, values, fill):
             o, n = lay[name]
@@ -523,59 +478,32 @@ class ModelRunner:
         put("seq_of_token", seq, 0)
         put("q_start", q_start, N)
         put("start_pos", start, 0)
-        put("kv_len", start + np.asarray(lens, dtype=np.int32), 0)
+        put("kv_len", start + lens, 0)
         put("slots", [e.slot for e in entries], 0)
         put("want_rows", want_rows, 0)
-        # attention plan: short portions token by token, long ones in tiles (longest key range first)
-        items: List[int] = []
-        tiles: List[tuple] = []
-        max_item_kv = 0
-        for i, e in enumerate(entries):
-            if lens[i] < SHORT_PORTION:
-                items.extend(range(int(q_start[i]), int(q_start[i + 1])))
-                max_item_kv = max(max_item_kv, e.start_pos + lens[i])
-            else:
-                for off in range(0, lens[i], self.tile_rows):
-                    tiles.append((e.start_pos + min(off + self.tile_rows, lens[i]), i, off))
-        tiles.sort(reverse=True)
-        put("items", items, -1)
-        put("tiles", [v for t in tiles for v in (t[1], t[2])], 0)
-        o, n = lay["tiles"]
-        h[o + 2 * len(tiles) + 1:o + n:2] = 1 << 24      # padding tiles: an offset past any request's tokens
         put("token_from", list(feedback[1]) if feedback is not None else [], -1)
-        return dict(N=N, B=B, W=len(want_rows), lens=lens, q_start=q_start, start=start, n_items=len(items),
-                    n_tiles=len(tiles), max_item_kv=max_item_kv)
+        plan_keys = {}
+        for p in self.plans:
+            o, n = lay["plan:" + p.name]
+            plan_keys[p.name] = p.fill(lens, q_start, start, h[o:o + n], n_cap, b_cap)
+        return dict(N=N, B=B, W=len(want_rows), lens=lens, q_start=q_start, start=start, plan_keys=plan_keys)
 
     def _build_context(self, entries: Sequence[StepEntry], feedback=None) -> StepContext:
+        """The context of a step that runs eagerly: arrays of exactly the step's sizes."""
         B = len(entries)
         N = sum(len(e.tokens) for e in entries)
         W = sum(len(e.want) for e in entries)
         lay = self._layout(N, B, W)
         h = self._staging.begin()
-        info = self._pack(entries, lay, h, feedback)
-        lens, q_start, start = info["lens"], info["q_start"], info["start"]
+        info = self._pack(entries, lay, h, N, B, feedback)
         self._staging.commit(lay["total"])
         dev = self._staging.dev
         if feedback is not None:
             o, _ = lay["token_from"]
             t0, _ = lay["token_ids"]
             ops.gather_where_i32(dev[t0:t0 + N], dev[o:o + N], feedback[0])
-
-        def view(name):
-            o, n = lay[name]
-            return dev[o:o + n]
-
-        ctx = StepContext()
-        ctx.n_tokens, ctx.n_seqs, ctx.n_want = N, B, W
-        ctx.token_ids, ctx.positions, ctx.seq_of_token = view("token_ids"), view("positions"), view("seq_of_token")
-        ctx.q_start, ctx.start_pos, ctx.kv_len, ctx.slots = (view("q_start"), view("start_pos"), view("kv_len"),
-                                                             view("slots"))
-        ctx.want_rows = view("want_rows") if W else None
-        ctx.h_q_start, ctx.h_start_pos = q_start.tolist(), start.tolist()
-        ctx.h_kv_len = [s + n for s, n in zip(ctx.h_start_pos, lens)]
+        ctx = self._context_over(dev, lay, N, B, W, info["plan_keys"], self)
+        ctx.h_q_start, ctx.h_start_pos = info["q_start"].tolist(), info["start"].tolist()
+        ctx.h_kv_len = [s + int(n) for s, n in zip(ctx.h_start_pos, info["lens"])]
         ctx.h_slots = [e.slot for e in entries]
-        ctx.status, ctx.act_dtype, ctx.device = self.status, self.model.dtype, self.device
-        ctx._plan = AttentionPlan(view("items"), info["n_items"], view("tiles"), info["n_tiles"],
-                                  max(info["max_item_kv"], max(ctx.h_kv_len)))
-        ctx._scratch_owner = self
         return ctx

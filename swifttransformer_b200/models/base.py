@@ -45,6 +45,9 @@ class ModelDef:
     # maps a tensor name found in a checkpoint to the name the parts use
     # (None: ignore the tensor)
     canonical_name: Optional[Callable[[str], Optional[str]]] = None
+    # the most tokens a request may hold (the architecture's context length, from its configuration);
+    # None: whatever the position encoding allows, and where that has no limit, the engine's own setting
+    max_seq_len: Optional[int] = None
 
     def parts(self) -> List[Part]:
         out: List[Part] = [self.embedding, self.position]
@@ -122,17 +125,34 @@ class CausalLM:
 
     @property
     def max_positions(self) -> Optional[int]:
-        return self.position.max_positions()
+        """The most tokens a request may hold: the smaller of the architecture's context length and what
+        the position encoding can encode (None: neither sets a limit)."""
+        limits = [n for n in (self.definition.max_seq_len, self.position.max_positions()) if n is not None]
+        return min(limits) if limits else None
 
     def graph_safe(self) -> bool:
         return all(b.mixer.graph_safe for b in self.blocks)
+
+    def step_plans(self) -> List[Any]:
+        """The step plans (parts.base.StepPlan) of the model's mixers, one per name, in layer order."""
+        plans: Dict[str, Any] = {}
+        for st in self.layer_order:
+            p = self.blocks[st.block].mixer.step_plan()
+            if p is not None and p.name not in plans:
+                plans[p.name] = p
+        return list(plans.values())
 
     def forward(self, ctx: Any, caches: List[Any]) -> Optional[torch.Tensor]:
         """Run the step described by ``ctx``; float32 logits [len(want), vocab] or None if nothing is wanted."""
         x = self.embedding.forward(ctx.token_ids, ctx.positions, self.position)
         stream = ResidualStream(x, self.dtype)
-        for st in self.layer_order:
+        nvtx = getattr(ctx, "nvtx", False)
+        for i, st in enumerate(self.layer_order):
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"layer {i} (block {st.block})")
             self.blocks[st.block].forward(stream, ctx, caches[st.cache].view(st.writes_cache))
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         if ctx.n_want == 0:
             return None
         if self.final_norm is not None:

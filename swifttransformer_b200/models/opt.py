@@ -59,4 +59,5 @@ def build_opt(cfg: OptConfig) -> ModelDef:
                       tied_to=ROOT + "embed_tokens.weight" if cfg.tie_word_embeddings else None,
                       project_out_name=ROOT + "project_out.weight" if proj else None)
     order = [LayerStep(block=i, cache=i) for i in range(cfg.num_hidden_layers)]
-    return ModelDef(cfg, embedding, position, blocks, order, final_norm, head, _canonical)
+    return ModelDef(cfg, embedding, position, blocks, order, final_norm, head, _canonical,
+                    max_seq_len=cfg.max_position_embeddings)

@@ -101,6 +101,18 @@ def _f(x: float):
     return ctypes.c_float(x)
 
 
+_SM_COUNT = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of a CUDA device (the current one by default); asked once per device."""
+    index = device.index if isinstance(device, torch.device) and device.index is not None \
+        else torch.cuda.current_device()
+    if index not in _SM_COUNT:
+        _SM_COUNT[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _SM_COUNT[index]
+
+
 # ------------------------------------------------------------------ embedding
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, positions: Optional[torch.Tensor] = None,
           pos_table: Optional[torch.Tensor] = None, pos_offset: int = 0) -> torch.Tensor:
@@ -410,10 +422,9 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
 
 def decode_warps(n_items: int, nkv: int, d: int, n_splits: int, max_kv: int) -> int:
     """Warps per block for the tensor-core decode attention.  Eight when the launch is at most two blocks per
-    SM and the key ranges are long: a warp's chain of groups is then half as long (measured on OPT-1.3B,
-    ms per step, eight against four: batch 8 at context 550: 1.256 / 1.299; batch 1 at context 1800 with
-    three parts: 1.131 / 1.230; with many blocks four are better, batch 64: 2.61 / 2.46)."""
-    return 8 if (d <= 64 and n_items * nkv * n_splits <= 2 * 148 and max_kv >= 256) else 4
+    SM and the key ranges are long: a warp's chain of groups is then half as long; with many blocks four are
+    better (measurements: profiles/decode_attention_splits.md)."""
+    return 8 if (d <= 64 and n_items * nkv * n_splits <= 2 * sm_count() and max_kv >= 256) else 4
 
 
 def attention_prefill_tile_rows() -> int:

@@ -13,17 +13,112 @@ bias is handed on with the result so the next norm kernel adds it.
 from __future__ import annotations
 
 import math
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..weights.spec import MATRIX, VECTOR, ParamSpec
-from .base import MIXERS, Delta, Mixer, PagedKVSpec
+from .base import MIXERS, Delta, Mixer, PagedKVSpec, StepPlan
 
 # requests that bring fewer new tokens than this are served token by token by
-# the bandwidth-bound kernel, the others in tiles of 64 queries on tensor cores
+# the bandwidth-bound kernel, the others in tiles of queries on tensor cores
 SHORT_PORTION = 16
+
+# Keys one block of the single-token attention walks alone before the key range is cut into parts (for head
+# sizes up to 64, where a block has eight warps; half of it beyond).  Recorded steps are keyed by the number
+# of such spans the longest single-token request needs, so the cut follows the real lengths, not the
+# longest possible one.
+KEYS_PER_BLOCK = 768
+
+
+def choose_splits(n_items: int, nh: int, max_kv: int, sms: int, head_dim: int = 64) -> int:
+    """Parts the key range of a single-token query is cut into: one while the launch fills the device or the
+    range is short (cutting costs a merge through global memory), else about KEYS_PER_BLOCK keys per part
+    for head sizes up to 64 and at least 128 keys per part beyond, within two blocks per SM.  The
+    measurements behind these rules are in profiles/decode_attention_splits.md."""
+    blocks = max(1, n_items * nh)
+    if blocks * 64 >= 250 * head_dim:
+        return 1
+    room = max(1, (2 * sms + blocks - 1) // blocks)
+    if head_dim <= 64:
+        want = (max_kv + KEYS_PER_BLOCK - 1) // KEYS_PER_BLOCK
+    else:
+        want = max(1, max_kv // 128)
+    return max(1, min(want, room, 32))
+
+
+class AttentionStepView:
+    """Which of the step's tokens go to which attention kernel (bfloat16 path): ``items`` lists the tokens
+    served one by one (-1: none), ``tiles`` pairs of (request, offset of a tile of query rows among its new
+    tokens); ``max_item_kv`` bounds the keys a single token reads."""
+
+    def __init__(self, items, n_items, tiles, n_tiles, max_item_kv):
+        self.items, self.n_items, self.tiles, self.n_tiles = items, n_items, tiles, n_tiles
+        self.max_item_kv = max_item_kv
+
+    def splits(self, nh: int, head_dim: int = 64) -> int:
+        dev = self.items.device if self.items is not None else None
+        return choose_splits(self.n_items, nh, self.max_item_kv, ops.sm_count(dev), head_dim)
+
+
+class PagedAttentionPlan(StepPlan):
+    """The step's tokens sorted for the paged attention kernels: short portions token by token, long ones in
+    tiles of ``tile_rows`` queries, the tile with the longest key range first."""
+
+    name = "paged_attention"
+    PAD_TILE_OFFSET = 1 << 24          # a tile offset past any request's tokens: its block leaves at once
+
+    def __init__(self):
+        self.tile_rows = ops.attention_prefill_tile_rows()
+        self.token_multiple = self.tile_rows
+
+    def _tile_cap(self, n_cap: int, b_cap: int) -> int:
+        return (n_cap + self.tile_rows - 1) // self.tile_rows + b_cap
+
+    def words(self, n_cap: int, b_cap: int) -> int:
+        return n_cap + 2 * self._tile_cap(n_cap, b_cap)
+
+    def shape_key(self, lens, start, n_cap: int, b_cap: int) -> Tuple:
+        short = lens < SHORT_PORTION
+        n_items = int(lens[short].sum())
+        item_kv = int((start + lens)[short].max()) if n_items else 0
+        i_pad = min(-(-n_items // 16) * 16, n_cap)
+        t_pad = 0 if bool(short.all()) else self._tile_cap(n_cap, b_cap)
+        return (i_pad, t_pad, max(-(-item_kv // KEYS_PER_BLOCK), 1) * KEYS_PER_BLOCK)
+
+    def fill(self, lens, q_start, start, out, n_cap: int, b_cap: int) -> Tuple:
+        short = lens < SHORT_PORTION
+        tiles: List[tuple] = []
+        if bool(short.all()):
+            n_items = int(q_start[-1])
+            out[:n_items] = np.arange(n_items, dtype=np.int32)
+        else:
+            items: List[int] = []
+            tr = self.tile_rows
+            for i in range(len(lens)):
+                n, s = int(lens[i]), int(start[i])
+                if short[i]:
+                    items.extend(range(int(q_start[i]), int(q_start[i + 1])))
+                else:
+                    tiles.extend((s + min(off + tr, n), i, off) for off in range(0, n, tr))
+            tiles.sort(reverse=True)
+            n_items = len(items)
+            out[:n_items] = items
+        out[n_items:n_cap] = -1
+        t = out[n_cap:]
+        k = 2 * len(tiles)
+        t[0:k:2] = [x[1] for x in tiles]
+        t[1:k:2] = [x[2] for x in tiles]
+        t[k::2] = 0
+        t[k + 1::2] = self.PAD_TILE_OFFSET
+        item_kv = int((start + lens)[short].max()) if n_items else 0
+        return (n_items, len(tiles), max(item_kv, 1))
+
+    def view(self, dev: torch.Tensor, key: Tuple, n_cap: int, b_cap: int) -> AttentionStepView:
+        n_items, n_tiles, max_kv = key
+        return AttentionStepView(dev[:n_items], n_items, dev[n_cap:], n_tiles, max_kv)
 
 
 def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float, window: int) -> torch.Tensor:
@@ -35,7 +130,7 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
         ops.attention_plain(q, cache.pool, cache.layer, out, ctx.positions, ctx.seq_of_token, ctx.slots,
                             cache.block_table, nh, scale, window)
         return out
-    plan = ctx.attention_plan()
+    plan = ctx.plan(PagedAttentionPlan.name)
     if plan.n_tiles:
         ops.attention_prefill(q, cache.pool, cache.layer, out, plan.tiles, plan.n_tiles, ctx.q_start,
                               ctx.start_pos, ctx.slots, cache.block_table, nh, scale, window, status=ctx.status)
@@ -94,6 +189,9 @@ class Attention(Mixer):
 
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.nkv, self.d, self.window)
+
+    def step_plan(self) -> StepPlan:
+        return PagedAttentionPlan()
 
     def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:
         q = torch.empty((h.shape[0], self.nh * self.d), dtype=h.dtype, device=h.device)

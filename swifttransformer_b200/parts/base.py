@@ -16,6 +16,7 @@ order is written out in src/csrc/model/gpt/gpt.cc:304-503.
 Interfaces
 ----------
 Mixer.cache_spec()        -> PagedKVSpec | StateSpec | None
+Mixer.step_plan()         -> StepPlan | None  (host work once per step, see StepPlan)
 Mixer.forward(h, ctx, cache) -> Delta         h: [N, width] activations
 FeedForward.forward(h, ctx)  -> Delta
 Norm.apply(x, delta, ...)    -> see parts.norm
@@ -75,12 +76,59 @@ class Part:
         return 0
 
 
+class StepPlan:
+    """Host work that a kind of mixer needs done once per step, before any layer runs.
+
+    The step function knows tokens, requests and wanted rows; how a mixer's kernels cut a step's work
+    (which tokens go to which kernel, in tiles of how many rows, over how many keys) is the mixer's
+    business.  A mixer that needs index arrays of its own returns a StepPlan from ``step_plan()``.
+    The step function gives every plan of the model room in the step's staging buffer (one pinned buffer,
+    one copy per step), lets it fill that room on the host, and hands what ``view`` returns to the mixers
+    through ``ctx.plan(name)``.  Plans are shared by name: all mixers that return a plan called
+    "paged_attention" read the same arrays.
+
+    A step is described to a plan by three int arrays (numpy, one element per request of the step):
+    ``lens`` (new tokens), ``q_start`` (offset of its first token among the step's tokens, one element more
+    than requests) and ``start`` (tokens it already has in the cache).
+
+    Steps are recorded as CUDA graphs of fixed shape and replayed; a recording made for ``n_cap`` tokens and
+    ``b_cap`` requests serves every step that fits and whose ``shape_key`` is equal.  ``fill`` must pad what
+    the step does not use with entries the mixer's kernels skip.
+    """
+
+    name = ""
+    # tokens of a recorded step are padded to a multiple of this (the row count of the mixer's tiles)
+    token_multiple = 1
+
+    def words(self, n_cap: int, b_cap: int) -> int:
+        """int32 words this plan wants for a step of at most n_cap tokens in b_cap requests."""
+        return 0
+
+    def shape_key(self, lens, start, n_cap: int, b_cap: int) -> Tuple:
+        """What a recorded step must agree in, beside n_cap and b_cap, to serve this step (padded counts,
+        never exact ones: every new key is a new recording)."""
+        return ()
+
+    def fill(self, lens, q_start, start, out, n_cap: int, b_cap: int) -> Tuple:
+        """Write the plan's arrays for this step into ``out`` (numpy int32, ``words(n_cap, b_cap)`` long);
+        returns the key that describes the step exactly, in the form ``shape_key`` returns."""
+        return ()
+
+    def view(self, dev: torch.Tensor, key: Tuple, n_cap: int, b_cap: int) -> Any:
+        """What the mixers get from ``ctx.plan(name)``: built over ``dev`` (the device copy of the words)
+        for a step described by ``key`` (an exact key, or a padded one when the step is recorded)."""
+        return None
+
+
 class Mixer(Part):
     # False for mixers whose forward does host-side work that cannot be
     # recorded into a CUDA graph (the engine then runs them eagerly).
     graph_safe = True
 
     def cache_spec(self):
+        return None
+
+    def step_plan(self) -> Optional[StepPlan]:
         return None
 
     def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:

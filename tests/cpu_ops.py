@@ -159,6 +159,10 @@ def attention_plain(q, pool, layer, out, positions, seq_of_token, slots, block_t
     return out
 
 
+def sm_count(device=None):
+    return 148
+
+
 def decode_warps(n_items, nkv, d, n_splits, max_kv):
     return 4
 
@@ -249,7 +253,7 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
     return res
 
 
-ALL = ["embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
+ALL = ["sm_count", "embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
        "qkv_linear_to_cache", "qkv_to_cache",
        "attention_plain", "attention_decode_scratch", "decode_warps", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]

@@ -206,23 +206,31 @@ def test_a_step_packed_into_a_padded_shape_is_padded_with_what_kernels_skip(mode
                StepEntry(slots[2], [8, 9, 10], 0, [])]
     exact, padded = r._layout(204, 3, 2), r._layout(256, 4, 4)
     he, hp = np.zeros(exact["total"], np.int32), np.full(padded["total"], -77, np.int32)
-    ie, ip = r._pack(entries, exact, he), r._pack(entries, padded, hp)
-    assert ie["N"] == ip["N"] == 204 and ip["n_items"] == 4 and ip["n_tiles"] == 2
+    ie, ip = r._pack(entries, exact, he, 204, 3), r._pack(entries, padded, hp, 256, 4)
+    # the attention's step plan describes the step as (single-token entries, tiles, longest key range of an entry)
+    assert ie["N"] == ip["N"] == 204 and ip["plan_keys"]["paged_attention"] == (4, 2, 3)
 
     def part(h, lay, name):
         o, n = lay[name]
         return h[o:o + n]
-    for name in exact:
-        if name != "total":
-            k = exact[name][1]
-            assert np.array_equal(part(hp, padded, name)[:k], part(he, exact, name)), name
+    for name in r.BASE_ARRAYS:
+        k = exact[name][1]
+        assert np.array_equal(part(hp, padded, name)[:k], part(he, exact, name)), name
     assert np.all(part(hp, padded, "positions")[204:] == -1)
     assert np.all(part(hp, padded, "q_start")[4:] == 204), "a padding request has no tokens"
-    assert np.all(part(hp, padded, "items")[4:] == -1) and list(part(hp, padded, "items")[:4]) == [200, 201, 202, 203]
-    tiles = part(hp, padded, "tiles").reshape(-1, 2)
-    assert [tuple(t) for t in tiles[:2]] == [(0, 0), (0, 128)] or [tuple(t) for t in tiles[:2]] == [(0, 128), (0, 0)]
+    # the plan's own arrays: the tokens served one by one, then (request, offset) of every tile of query rows
+    plan_e, plan_p = part(he, exact, "plan:paged_attention"), part(hp, padded, "plan:paged_attention")
+    assert list(plan_p[:4]) == [200, 201, 202, 203] == list(plan_e[:4]) and np.all(plan_p[4:256] == -1)
+    tiles = plan_p[256:].reshape(-1, 2)
+    assert [tuple(t) for t in tiles[:2]] == [(0, 128), (0, 0)], "the tile with the longest key range first"
+    assert [tuple(t) for t in plan_e[204:].reshape(-1, 2)[:2]] == [(0, 128), (0, 0)]
     assert np.all(tiles[2:, 1] >= 1 << 24) and np.all(part(hp, padded, "token_from") == -1)
     assert -77 not in hp, "every word of the padded layout is written"
+    # a recorded shape is keyed by padded counts: entries in sixteens, all tiles the shape has room for, spans of keys
+    lens, start = np.array([200, 1, 3], np.int32), np.zeros(3, np.int32)
+    from swifttransformer_b200.parts.attention import KEYS_PER_BLOCK
+    assert r.plans[0].shape_key(lens, start, 256, 4) == (16, 2 + 4, KEYS_PER_BLOCK)
+    assert r.plans[0].shape_key(np.ones(5, np.int32), np.full(5, 800, np.int32), 8, 8) == (8, 0, 2 * KEYS_PER_BLOCK)
 
 
 def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
@@ -239,3 +247,87 @@ def test_sampler_follows_the_plain_sampler(cpu_ops_installed):
         else:
             u = ops.uniform(p.seed, r)
             assert got[r] == plain_opt.softmax_sample(logits[r].numpy(), p.temperature, u, p.top_k)
+
+
+@pytest.mark.parametrize("pipeline", [False, True])
+def test_aborting_requests_changes_nothing_for_the_others(model_dirs, cpu_ops_installed, pipeline):
+    """Requests are taken out while waiting, while their prompt is half computed, while decoding (with steps
+    launched ahead: with a token still on its way) and after they finished: pages and slot are back in the same
+    call, no later step reports them, and the others generate what they generate alone."""
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    cfg, w = plain_opt.load_model(model_dirs["a"])
+    prompts = [helpers.random_tokens(512, n, 900 + i) for i, n in enumerate([30, 7, 44, 12, 21, 5])]
+    sp = SamplingParams(max_new_tokens=10)
+    eng = LLMEngine(model, page_size=8, num_pages=64, max_batch_tokens=24, chunk_size=16, max_num_seqs=3,
+                    pipeline=pipeline)
+    ids = [eng.add_request(p, dataclasses.replace(sp)) for p in prompts]
+    reported = []
+    # 5 is still waiting (three slots)
+    gone = {ids[5]: eng.abort_request(ids[5])}
+    assert gone[ids[5]].finish_reason == "aborted" and gone[ids[5]].output == []
+    reported += eng.step()
+    # 0 has had one portion of its prompt
+    r0 = eng.requests[ids[0]]
+    assert 0 < r0.n_computed < len(r0.prompt)
+    held = eng.cache.free_pages
+    gone[ids[0]] = eng.abort_request(ids[0])
+    assert eng.cache.free_pages > held and gone[ids[0]].slot is None
+    while not eng.requests[ids[1]].output:
+        reported += eng.step()
+    reported += eng.step()
+    # 1 is decoding; with steps launched ahead its next token is on its way
+    gone[ids[1]] = eng.abort_request(ids[1])
+    assert -1 not in gone[ids[1]].output and len(gone[ids[1]].output) >= 1
+    with pytest.raises(KeyError):
+        eng.abort_request(ids[1])
+    while eng.has_work():
+        reported += eng.step()
+    assert sorted(r.id for r in reported) == sorted([ids[2], ids[3], ids[4]])
+    assert eng.cache.free_pages == eng.cache.total_pages and eng.cache.num_free_slots == 3
+    eng.cache.check()
+    for i in (2, 3, 4):
+        assert eng.requests[ids[i]].output == plain_opt.greedy_generate(cfg, w, prompts[i], 10), i
+    # what 1 had got before it was taken out is the beginning of what it generates alone
+    alone = plain_opt.greedy_generate(cfg, w, prompts[1], 10)
+    assert gone[ids[1]].output == alone[:len(gone[ids[1]].output)]
+    # a finished request can be taken out as well: it keeps its reason
+    assert eng.abort_request(ids[2]).finish_reason == "length"
+    assert not eng.scheduler.finished, "the scheduler keeps no finished request once a step has reported it"
+
+
+def test_stats_show_the_pool_and_preemptions(model_dirs, cpu_ops_installed):
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    eng = LLMEngine(model, page_size=8, num_pages=9, max_batch_tokens=40, chunk_size=16, max_num_seqs=4)
+    assert eng.stats["pages_free"] == eng.stats["pages_total"] == 9 and eng.stats["preemptions"] == 0
+    for i in range(4):
+        eng.add_request(helpers.random_tokens(512, 14, 40 + i), SamplingParams(max_new_tokens=12, ignore_eos=True))
+    low = 9
+    while eng.has_work():
+        eng.step()
+        low = min(low, eng.stats["pages_free"])
+    st = eng.stats
+    assert low == 0 and st["preemptions"] > 0 and st["pages_free"] == 9 and st["running"] == st["waiting"] == 0
+    assert st["decode_tokens"] > 0 and st["prompt_tokens"] >= 4 * 14 and st["steps"] > 12
+
+
+def test_the_length_limit_comes_from_the_configuration(model_dirs, cpu_ops_installed):
+    """Block tables are sized by the per-request limit: the model's, or a smaller one the engine is given."""
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.models import load_model
+    from swifttransformer_b200.sampling import SamplingParams
+    model = load_model(model_dirs["a"], "float32", "cpu")
+    assert model.max_positions == 128
+    eng = LLMEngine(model, page_size=8, num_pages=32, max_num_seqs=2)
+    assert eng.max_seq_len == 128 and eng.cache.groups[0].block_table.shape == (2, 16)
+    eng = LLMEngine(model, page_size=8, num_pages=32, max_num_seqs=2, max_seq_len=40)
+    assert eng.max_seq_len == 40 and eng.cache.groups[0].block_table.shape == (2, 5)
+    with pytest.raises(ValueError, match="exceeds"):
+        eng.add_request([5] * 41)
+    out = eng.generate([[5] * 30], SamplingParams(max_new_tokens=50, ignore_eos=True))
+    assert len(out[0]) == 10, "a request ends when it holds as many tokens as the limit allows"

@@ -95,15 +95,16 @@ def test_decoding_with_the_key_range_cut_into_parts(model_dirs, name, monkeypatc
     """Long key ranges are cut into parts that separate blocks walk and the last one merges.  With the span a
     block walks alone set to 32 keys, decode steps of a few hundred positions run with up to nine parts, are
     recorded once per number of spans, and must still match the plain implementation."""
-    import swifttransformer_b200.engine.step as step
-    monkeypatch.setattr(step, "KEYS_PER_BLOCK", 32)
+    import swifttransformer_b200.parts.attention as attention
+    monkeypatch.setattr(attention, "KEYS_PER_BLOCK", 32)
     reqs = {k: v for k, v in requests_for(name).items() if len(v) >= 60}
     steps = helpers.trace_decode_tail(reqs, tail=48)
     s = session(model_dirs[name], name, "bfloat16", helpers.live_token_need(steps), max_requests=4)
     got = helpers.replay(s, steps)
     helpers.check_against_plain(model_dirs[name], reqs, got, "bfloat16", f"{name}/parts")
     assert s.runner.graph_steps > 0 and len(s.runner._graphs) >= 3, "one recorded step per number of spans"
-    assert max(g.ctx._plan.splits(TINY[name]["cfg"]["num_attention_heads"]) for g in s.runner._graphs.values()) > 2
+    assert max(g.ctx.plan("paged_attention").splits(TINY[name]["cfg"]["num_attention_heads"])
+               for g in s.runner._graphs.values()) > 2
     s.runner.check_status()
 
 

@@ -98,14 +98,15 @@ class OneStep:
         self.kv_len = torch.tensor([start + n], **i32)
         self.slots = torch.tensor([slot], **i32)
         self.status = torch.zeros(1, **i32)
-        from swifttransformer_b200.engine.step import AttentionPlan
+        from swifttransformer_b200.parts.attention import AttentionStepView
         tr = ops.attention_prefill_tile_rows()
         tiles = torch.tensor([v for off in range(0, n, tr) for v in (0, off)] or [0], **i32)
-        self._plan = AttentionPlan(torch.arange(n, **i32), n if n < 16 else 0, tiles,
-                                   0 if n < 16 else (n + tr - 1) // tr, start + n)
+        self._plan = AttentionStepView(torch.arange(n, **i32), n if n < 16 else 0, tiles,
+                                       0 if n < 16 else (n + tr - 1) // tr, start + n)
         self._buf = None
 
-    def attention_plan(self):
+    def plan(self, name):
+        assert name == "paged_attention"
         return self._plan
 
     def scratch_f32(self, k):
