@@ -36,11 +36,27 @@
 //     that run one after the other (same stream, or ordered by events) are
 //     independent; two calls that overlap on the GPU race on the array and
 //     give wrong results.
+//   * The first call on a device also fills that device's entry of a small
+//     table of addresses, without a lock: let one host thread make the first
+//     call on a device before other threads call for the same device.
 //   * It calls no cudaMalloc, cudaFree or allocating library routine.
 //
-// Returns 0, a positive cudaError_t, or a negative ST_ERR_* code.  `err` may be
-// null; otherwise up to err_len - 1 characters of explanation are written.
+// Returns 0, a positive cudaError_t, or a negative code: ST_ERR_TOO_LARGE (-3)
+// when the call does not fit the built-in scratch, ST_ERR_BAD_ARG (-4) for
+// sizes that make no sense, ST_ERR_BAD_SIZE (-2) for a head size the kernel
+// does not take.  `err` may be null; otherwise up to err_len - 1 characters of
+// explanation are written.
 #pragma once
+
+#ifndef ST_ERR_BAD_SIZE
+#define ST_ERR_BAD_SIZE (-2)
+#endif
+#ifndef ST_ERR_TOO_LARGE
+#define ST_ERR_TOO_LARGE (-3)
+#endif
+#ifndef ST_ERR_BAD_ARG
+#define ST_ERR_BAD_ARG (-4)
+#endif
 
 #define ST_NOALLOC_SCRATCH_FLOATS (1 << 20)
 #define ST_NOALLOC_MAX_PAIRS 16384

@@ -5,10 +5,14 @@ its own safetensors reader, its own config handling and computes with numpy
 (float64 by default).  It rests on the reference's formulas (the reference's
 model code needs a GPU, MPI and a missing submodule, so it cannot be run or
 compiled on a CPU); each function cites the lines it restates.  What of the
-reference does run on a CPU is its offline weight converter: its output for a
+reference does run on a CPU is (1) its offline weight converter: its output for a
 tiny random model is kept under tests/golden/, and tests/test_golden_converter.py
 checks that this file's logits equal those of the reference's order of
-operations on the converter's tensors (fused q|k|v, transposes, cut positions).  Where the
+operations on the converter's tensors (fused q|k|v, transposes, cut positions);
+and (2) the LibTorch attention oracle its kernel tests use
+(src/unittest/kernel/attention_ref.cc), compiled unchanged for the host: its
+inputs and outputs are kept under tests/golden/ too, and
+tests/test_golden_attention.py holds ``causal_attention`` to them.  Where the
 reference has no code for an option (post-LN, project_in/out, no bias, no
 affine), the definition used is stated in the function.
 """
@@ -175,13 +179,14 @@ def decoder_layer(x, w, i, cfg):
     return ln("final_layer_norm", r + feed_forward(r, w, p, cfg))
 
 
-def forward(cfg, w, ids, dtype=np.float64):
-    """Logits [T, vocab] for one whole sequence `ids`.
+def forward(cfg, w, ids, dtype=np.float64, rows=None):
+    """Logits [T, vocab] for one whole sequence `ids` (with `rows`: only at those positions, [len(rows), vocab];
+    the sequence is computed whole all the same).
 
     x = embed_tokens[id] (project_in when word_embed_proj_dim != hidden) + positions;
     layers; final LayerNorm only for pre-LN models; project_out; logits = h . embed_tokens^T
     (tied; src/csrc/model/gpt/gpt.cc:112-145 embedding, 614-624 final LN, 175-201 LM head)."""
-    w = {k: (v.astype(dtype) if v.dtype.kind == "f" else v) for k, v in w.items()}
+    w = {k: (v.astype(dtype, copy=False) if v.dtype.kind == "f" else v) for k, v in w.items()}
     ids = np.asarray(ids)
     H = cfg["hidden_size"]
     E = cfg.get("word_embed_proj_dim", H) or H
@@ -197,6 +202,8 @@ def forward(cfg, w, ids, dtype=np.float64):
         x = layer_norm(x, w["model.decoder.final_layer_norm.weight"] if affine else None,
                        w["model.decoder.final_layer_norm.bias"] if affine else None,
                        cfg.get("layer_norm_eps", 1e-5))
+    if rows is not None:
+        x = x[np.asarray(rows)]
     if E != H:
         x = linear(x, w["model.decoder.project_out.weight"])
     head = w["model.decoder.embed_tokens.weight"] if cfg.get("tie_word_embeddings", True) else w["lm_head.weight"]

@@ -223,6 +223,7 @@ class ToyConfig(ModelConfig):
     inner: int
     decay: float
     max_positions: int
+    on_device: bool = False      # the running average computed by device operations only (its steps can be recorded)
 
 
 @MIXERS.register("toy_running_average")
@@ -252,6 +253,34 @@ class RunningAverage(Mixer):
         return Delta(out)
 
 
+@MIXERS.register("toy_running_average_on_device")
+class RunningAverageOnDevice(RunningAverage):
+    """The same mixer without host work, so that its steps are recorded and replayed: the portion's tokens are
+    folded with a prefix sum (s_t = decay^(j+1) s_before + (1 - decay) sum_{u <= t} decay^(t-u) h_u, j the token's
+    place in its portion), padding tokens (position -1) contribute nothing, and a request's state moves by the
+    difference its last token makes (a fixed-shape scatter-add; padding adds zero)."""
+    graph_safe = True
+
+    def forward(self, h, ctx, cache):
+        n = h.shape[0]
+        seq = ctx.seq_of_token.long()
+        live = ctx.positions >= 0
+        first = ctx.q_start.long()[seq]
+        t = torch.arange(n, device=h.device)
+        j = (t - first).clamp(min=0).double()
+        hd = torch.where(live[:, None], h.double(), torch.zeros((), dtype=torch.float64, device=h.device))
+        scaled = hd * (self.decay ** -j)[:, None]
+        run = torch.cumsum(scaled, 0)
+        within = (run - (run[first] - scaled[first])) * (self.decay ** j)[:, None]
+        slot = ctx.slots.long()[seq]
+        before = cache.state[slot].double()
+        s = (self.decay ** (j + 1))[:, None] * before + (1 - self.decay) * within
+        out = (s.float() @ self.w.float().t()).to(h.dtype)
+        is_last = live & (t + 1 == ctx.q_start.long()[seq + 1])
+        cache.state.index_add_(0, slot, ((s - before) * is_last[:, None]).float())
+        return Delta(out)
+
+
 @register_model(ToyConfig.ARCHITECTURE)
 def build_toy(cfg):
     W = cfg.width
@@ -260,7 +289,8 @@ def build_toy(cfg):
     blocks = []
     for i in range(cfg.layers):
         if i % 2 == 0:
-            mixer = MIXERS.build("toy_running_average", width=W, decay=cfg.decay, name=f"l{i}.avg")
+            mixer = MIXERS.build("toy_running_average_on_device" if cfg.on_device else "toy_running_average",
+                                 width=W, decay=cfg.decay, name=f"l{i}.avg")
         else:
             mixer = MIXERS.build("attention", hidden=W, num_heads=cfg.heads, head_dim=W // cfg.heads, bias=False,
                                  names={k: f"l{i}.{k}" for k in "qkvo"})
@@ -316,6 +346,37 @@ def test_toy_mixer_with_state_runs_through_the_engine(tmp_path, dtype):
             scale = np.abs(refs[k]).max()
             bad = helpers.first_bad(got[k], refs[k], helpers.TOL[dtype] * scale)
             assert bad is None, (k, bad)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recorded_steps_move_per_request_state_once(tmp_path, dtype):
+    """A mixer with state of its own and no host work: its steps are recorded as graphs.  The first use of a
+    shape (the pass that sizes scratch memory, then the recording, then the replay) must move a request's
+    state exactly once: the logits of recorded steps equal the plain implementation's and those of the same
+    steps launched one by one."""
+    from swifttransformer_b200.engine.replay import TraceSession
+    cfg = ToyConfig(vocab_size=211, width=48, layers=3, heads=3, inner=100, decay=0.8, max_positions=96, on_device=True)
+    d = write_random_model(str(tmp_path / "toyd"), cfg, seed=3, std=0.15)
+    model = load_model(d, dtype, DEV)
+    assert model.graph_safe() and isinstance(model.definition.cache_specs()[0], StateSpec)
+    reqs = {"p": helpers.random_tokens(211, 70, 1), "q": helpers.random_tokens(211, 41, 2),
+            "r": helpers.random_tokens(211, 23, 3)}
+    refs = {k: toy_plain(d, cfg, np.array(v)) for k, v in reqs.items()}
+    for build in (helpers.trace_whole, lambda r: helpers.trace_decode_tail(r, tail=20), helpers.trace_portions,
+                  lambda r: helpers.trace_mixed(r, max_live=2, chunk=9)):
+        steps = build(reqs)
+        outs = []
+        for graphs in (True, False):
+            s = TraceSession(d, dtype, helpers.live_token_need(steps), page_size=8, max_requests=2)
+            s.runner.use_cuda_graphs = graphs
+            outs.append(helpers.replay(s, steps))
+            assert (s.runner.graph_steps + s.runner.padded_graph_steps > 0) == graphs
+        for k in reqs:
+            scale = np.abs(refs[k]).max()
+            bad = helpers.first_bad(outs[0][k], refs[k], helpers.TOL[dtype] * scale)
+            assert bad is None, ("recorded against plain", k, bad)
+            tol = (1e-5 if dtype == "float32" else 3e-2) * scale
+            assert helpers.first_bad(outs[0][k], outs[1][k], tol) is None, ("recorded against launched one by one", k)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -583,3 +644,45 @@ def test_routed_feed_forward_and_query_key_positions_run_through_the_engine(tmp_
         if build is helpers.trace_decode_tail:
             assert s.runner.graph_steps > 0, "decode steps of the toy model are recorded and replayed too"
     assert compared >= 4 * 100
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_without_a_position_table_generates_through_the_engine(tmp_path, dtype):
+    """The third toy architecture has no position table, so nothing in the model bounds a request's length: the
+    limit comes from the engine's configuration, block tables are sized by it, and requests generate through
+    LLMEngine - continuous batching, recorded decode steps, a pool so small that requests are preempted and
+    computed again - to the tokens the plain implementation gives."""
+    from swifttransformer_b200.engine.engine import DEFAULT_MAX_SEQ_LEN, LLMEngine
+    from swifttransformer_b200.sampling import SamplingParams
+    cfg = ToyRoutedConfig(vocab_size=257, width=64, layers=2, heads=2, experts=4, inner=96, turn=0.37)
+    d = write_random_model(str(tmp_path / "toyg"), cfg, seed=25, std=0.2)
+    model = load_model(d, dtype, DEV)
+    assert model.max_positions is None
+    assert LLMEngine(model, page_size=16, num_pages=8, max_num_seqs=2).max_seq_len == DEFAULT_MAX_SEQ_LEN
+    eng = LLMEngine(model, page_size=16, num_pages=7, max_batch_tokens=64, chunk_size=32, max_num_seqs=4,
+                    max_seq_len=96)
+    assert eng.cache.groups[0].block_table.shape == (4, 6)
+    prompts = [helpers.random_tokens(257, n, 30 + i) for i, n in enumerate([15, 31, 14, 30, 9])]
+    new = 12
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=new, ignore_eos=True))
+    eng.runner.check_status()
+    assert eng.stats["preemptions"] > 0, "the pool was made too small for the requests to finish side by side"
+    assert eng.runner.graph_steps > 0 and eng.cache.free_pages == eng.cache.total_pages
+    for p, o in zip(prompts, outs):
+        assert len(o) == new
+        ids = list(p)
+        for tok in o:
+            logits, sure = toy_routed_plain(d, cfg, np.array(ids))
+            if dtype == "bfloat16" and sure < len(ids):
+                break                      # a nearly tied routing decision: bfloat16 may take the other expert
+            best = int(np.argmax(logits[-1]))
+            if dtype == "float32":
+                assert tok == best
+            elif tok != best:
+                assert logits[-1][best] - logits[-1][tok] < 4e-2 * np.abs(logits[-1]).max()
+            ids.append(tok)
+    # a request may not outgrow the engine's limit
+    with pytest.raises(ValueError, match="exceeds"):
+        eng.add_request([5] * 97)
+    out = eng.generate([[5] * 90], SamplingParams(max_new_tokens=50, ignore_eos=True))[0]
+    assert len(out) == 6
