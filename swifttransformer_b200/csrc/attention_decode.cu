@@ -40,7 +40,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                         const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                         int n_layers, int layer, int nh, int nkv, int d_arg, int page_size, float scale_log2,
-                        int window, int n_splits, int* __restrict__ counters) {
+                        int window, int n_splits, int* __restrict__ counters, int* __restrict__ status) {
     const int d = FULL ? 64 * NCHUNK : d_arg;
     __shared__ float s_m[DEC_GROUPS], s_l[DEC_GROUPS];
     __shared__ int s_last;
@@ -68,7 +68,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
     const int p_lo = k_lo / page_size;
     if (k_lo < k_hi) {
         const int n_pages = (k_hi - 1) / page_size - p_lo + 1;
-        for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) s_pages[i] = __ldcg(bt + p_lo + i);
+        for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) {
+            const int page = __ldcg(bt + p_lo + i);
+            s_pages[i] = page;
+            if (page < 0 && status) *status = 1;     // a hole in the block table: its keys are dropped and the host hears of it
+        }
     }
     ST_PDL_WAIT();
     __syncthreads();
@@ -209,7 +213,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
 #pragma unroll
         for (int i = 0; i < DEC_GROUPS; ++i)
             a += (s_m[i] == -INFINITY) ? 0.f : s_acc[i * d + e] * exp2f(s_m[i] - mm);
-        if (n_splits == 1) out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / ll);
+        if (n_splits == 1) out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
         else part[2 + e] = a;
     }
     if (n_splits > 1 && threadIdx.x == 0) { part[0] = mm; part[1] = ll; }
@@ -240,7 +244,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ poo
             const float ms = __ldcg(all + (size_t)sp * (d + 2));
             a += (ms == -INFINITY) ? 0.f : __ldcg(all + (size_t)sp * (d + 2) + 2 + e) * exp2f(ms - gm);
         }
-        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / gl);
+        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(gl > 0.f ? a / gl : 0.f);
     }
 }
 
@@ -267,7 +271,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, bf16
             const float ms = part[(size_t)s * (d + 2)];
             a += (ms == -INFINITY) ? 0.f : part[(size_t)s * (d + 2) + 2 + e] * exp2f(ms - mm);
         }
-        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(a / ll);
+        out[((size_t)t * nh + h) * d + e] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
     }
 }
 
@@ -277,12 +281,13 @@ ST_EXPORT long long st_attention_decode_scratch_floats(int n_items, int nh, int 
 }
 
 // counters: n_items * nh ints, zero before the first launch (the kernel leaves them zero), or null: the
-// splits are then merged by a second kernel.
+// splits are then merged by a second kernel.  status: null, or a word that is set to 1 when a key range
+// crosses a hole in a block table.
 ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, float* partial, const int* items,
                                   int n_items, const int* positions, const int* seq_of_token, const int* slots,
                                   const int* block_table, int max_pages, int n_layers, int layer, int nh, int nkv,
                                   int d, int page_size, float scale, int window, int n_splits, int* counters,
-                                  void* stream) {
+                                  int* status, void* stream) {
     if (n_items <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
     if (d % 8 || d <= 0) return ST_ERR_BAD_SIZE;
@@ -291,7 +296,8 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_items, nh, n_splits);
     // merge buffers of the 16 key groups, then the page ids of the block's key range
-    const size_t smem = (size_t)DEC_GROUPS * d * sizeof(float) + (size_t)max_pages * sizeof(int);
+    const size_t smem = (size_t)DEC_GROUPS * d * sizeof(float)
+                        + (size_t)st_decode_block_pages(max_pages, page_size, window, n_splits) * sizeof(int);
     if (smem > 48 * 1024) return ST_ERR_TOO_LARGE;
     const float sl2 = scale * LOG2E;
 #define LAUNCH_DEC(NC)                                                                                         \
@@ -300,7 +306,7 @@ ST_EXPORT int st_attention_decode(const void* q, const void* pool, void* out, fl
     st_launch_pdl("decode", attention_decode_kernel<NC, FULL>, grid, dim3(DEC_THREADS), smem, s, (const bf16*)q,               \
         (const bf16*)pool, (bf16*)out, n_splits > 1 ? partial : (float*)nullptr, items, positions,              \
         seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, sl2, window,       \
-        n_splits, counters)
+        n_splits, counters, status)
     int rc;
     if (d <= 64) rc = LAUNCH_DEC(1);
     else if (d <= 128) rc = LAUNCH_DEC(2);
@@ -386,5 +392,5 @@ ST_EXPORT int st_attention_decode_noalloc(const void* q, const void* pool, void*
     }
     return st_attention_decode(q, pool, out, partial, items, n_items, positions, seq_of_token, slots, block_table,
                                max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window, n_splits,
-                               n_splits > 1 ? counters : nullptr, stream);
+                               n_splits > 1 ? counters : nullptr, nullptr, stream);
 }

@@ -37,7 +37,8 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                             int n_layers, int layer, int nh, int nkv, int d_arg, int page_size, int page_shift,
-                            float scale_log2, int window, int n_splits, int* __restrict__ counters) {
+                            float scale_log2, int window, int n_splits, int* __restrict__ counters,
+                            int* __restrict__ status) {
     const int d = FULL ? DMAX : d_arg;
     // page_shift: log2(page_size) if that is a power of two, else -1
     constexpr int STAGES = DmStages<DMAX>::value;
@@ -78,7 +79,11 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int p_lo = k_lo / page_size;
     if (k_lo < k_hi) {
         const int n_pages = (k_hi - 1) / page_size - p_lo + 1;
-        for (int i = threadIdx.x; i < n_pages; i += DM_THREADS) s_pages[i] = __ldcg(bt + p_lo + i);
+        for (int i = threadIdx.x; i < n_pages; i += DM_THREADS) {
+            const int page = __ldcg(bt + p_lo + i);
+            s_pages[i] = page;
+            if (page < 0 && status) *status = 1;     // a hole in the block table: zeros are read for it and the host hears of it
+        }
     }
     ST_PDL_WAIT();
     for (int i = threadIdx.x; i < 16 * chunks; i += DM_THREADS) {
@@ -337,11 +342,11 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 }
 
 template <int DMAX>
-static size_t dm_smem_bytes(int d, int max_pages, int warps) {
+static size_t dm_smem_bytes(int d, int block_pages, int warps) {
     const int DM_WARPS = warps;
     const size_t stages = (size_t)DM_WARPS * DmStages<DMAX>::value * 2 * DM_KEYS * DMAX * sizeof(bf16);
     const size_t merge = (size_t)DM_WARPS * 16 * d * sizeof(float);        // reuses the stages' space
-    return 16 * DMAX * sizeof(bf16) + (stages > merge ? stages : merge) + (size_t)max_pages * sizeof(int);
+    return 16 * DMAX * sizeof(bf16) + (stages > merge ? stages : merge) + (size_t)block_pages * sizeof(int);
 }
 
 ST_EXPORT int st_attention_decode_mma_applies(int d) { return d > 0 && d % 16 == 0 && d <= 128; }
@@ -351,7 +356,7 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
                                       int n_items, const int* positions, const int* seq_of_token, const int* slots,
                                       const int* block_table, int max_pages, int n_layers, int layer, int nh,
                                       int nkv, int d, int page_size, float scale, int window, int n_splits,
-                                      int* counters, int warps, void* stream) {
+                                      int* counters, int warps, int* status, void* stream) {
     if (n_items <= 0) return 0;
     if (warps != 4 && warps != 8) return ST_ERR_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
@@ -369,7 +374,7 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
     int rc;
 #define LAUNCH_DM(DMAX, FULL, WARPS)                                                                                 \
     do {                                                                                                             \
-        const size_t smem = dm_smem_bytes<DMAX>(d, max_pages, WARPS);                                                \
+        const size_t smem = dm_smem_bytes<DMAX>(d, st_decode_block_pages(max_pages, page_size, window, n_splits), WARPS);                                                \
         if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;                                                              \
         static bool configured = false;                                                                              \
         if (!configured) {                                                                                           \
@@ -382,7 +387,7 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
                            smem, s, (const bf16*)q, (const bf16*)pool, (bf16*)out,                                   \
                            n_splits > 1 ? partial : (float*)nullptr, items, positions, seq_of_token, slots,          \
                            block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift, sl2, window,  \
-                           n_splits, counters);                                                                      \
+                           n_splits, counters, status);                                                              \
     } while (0)
 #define LAUNCH_DM_W(DMAX, FULL)                                                                                      \
     do { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8); else LAUNCH_DM(DMAX, FULL, 4); } while (0)

@@ -23,7 +23,8 @@ __global__ void __launch_bounds__(KT)
 attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, T* __restrict__ out,
                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                        const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
-                       int n_layers, int layer, int nh, int nkv, int d, int page_size, float scale, int window) {
+                       int n_layers, int layer, int nh, int nkv, int d, int page_size, float scale, int window,
+                       int* __restrict__ status) {
     extern __shared__ float smem[];
     float* sq = smem;        // [d] query, pre-scaled
     float* sp = smem + d;    // [KT] probabilities of the tile
@@ -51,6 +52,8 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, T* _
                 float dot = 0.f;
                 for (int e = 0; e < d; ++e) dot += sq[e] * to_f32(krow[e]);
                 s = dot;
+            } else if (status) {
+                *status = 1;     // reported to the host: the step's bookkeeping is broken
             }
         }
         const float tile_max = block_max(s, scratch);
@@ -80,7 +83,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, T* _
         }
         __syncthreads();
     }
-    const float inv = 1.0f / l;
+    const float inv = l > 0.f ? 1.0f / l : 0.f;      // no key at all (every page missing): zeros, not NaN
     for (int c = 0; c < ndim; ++c) {
         const int e = threadIdx.x + c * KT;
         if (e < d) out[((size_t)t * nh + h) * d + e] = from_f32<T>(acc[c] * inv);
@@ -90,7 +93,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, T* _
 ST_EXPORT int st_attention_plain(const void* q, const void* pool, void* out, const int* positions,
                                  const int* seq_of_token, const int* slots, const int* block_table, int max_pages,
                                  int n_layers, int layer, int n_tokens, int nh, int nkv, int d, int page_size,
-                                 float scale, int window, int dtype, void* stream) {
+                                 float scale, int window, int dtype, int* status, void* stream) {
     if (n_tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || d <= 0 || page_size <= 0) return ST_ERR_BAD_ARG;
     if (d > 2 * KT) return ST_ERR_TOO_LARGE;
@@ -99,10 +102,10 @@ ST_EXPORT int st_attention_plain(const void* q, const void* pool, void* out, con
     const size_t smem = (size_t)(d + KT) * sizeof(float);
     if (dtype == 0)
         attention_plain_kernel<float><<<grid, KT, smem, s>>>((const float*)q, (const float*)pool, (float*)out,
-            positions, seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window);
+            positions, seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window, status);
     else if (dtype == 1)
         attention_plain_kernel<bf16><<<grid, KT, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,
-            positions, seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window);
+            positions, seq_of_token, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window, status);
     else return ST_ERR_BAD_DTYPE;
     return st_launch_status();
 }

@@ -30,7 +30,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
                          const int* __restrict__ tiles, const int* __restrict__ q_start,
                          const int* __restrict__ start_pos, const int* __restrict__ slots,
                          const int* __restrict__ block_table, int max_pages, int n_layers, int layer,
-                         int nh, int nkv, int d, int page_size, float scale_log2, int window) {
+                         int nh, int nkv, int d, int page_size, float scale_log2, int window,
+                         int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + PF_BM * DMAX;            // [2][PF_BN][DMAX]
@@ -67,6 +68,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
         if (ok) {
             const int page = bt[key / page_size];
             ok = page >= 0;                             // a hole in the block table: zeros, no access before the pool
+            if (!ok && status) *status = 1;             // and the host hears of it
             if (ok) src = pool + ((size_t)page * n_layers + layer) * 2 * kv_stride + kvh * head_stride
                           + (size_t)(key % page_size) * d;
         }
@@ -233,7 +235,7 @@ template <int DMAX>
 static int launch_prefill(const void* q, const void* pool, void* out, const int* tiles, int n_tiles,
                           const int* q_start, const int* start_pos, const int* slots, const int* block_table,
                           int max_pages, int n_layers, int layer, int nh, int nkv, int d, int page_size,
-                          float scale, int window, cudaStream_t s) {
+                          float scale, int window, int* status, cudaStream_t s) {
     const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * DMAX * sizeof(bf16);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
@@ -245,7 +247,7 @@ static int launch_prefill(const void* q, const void* pool, void* out, const int*
     dim3 grid(nh, n_tiles);
     attention_prefill_kernel<DMAX><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,
         tiles, q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size,
-        scale * LOG2E, window);
+        scale * LOG2E, window, status);
     return st_launch_status();
 }
 
@@ -254,7 +256,7 @@ ST_EXPORT int st_attention_prefill_tile_rows() { return PF_BM; }
 ST_EXPORT int st_attention_prefill(const void* q, const void* pool, void* out, const int* tiles, int n_tiles,
                                    const int* q_start, const int* start_pos, const int* slots,
                                    const int* block_table, int max_pages, int n_layers, int layer, int nh, int nkv,
-                                   int d, int page_size, float scale, int window, void* stream) {
+                                   int d, int page_size, float scale, int window, int* status, void* stream) {
     if (n_tiles <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_tiles > 65535) return ST_ERR_BAD_ARG;
     if (d <= 0 || d % 16) return ST_ERR_BAD_SIZE;
@@ -262,10 +264,10 @@ ST_EXPORT int st_attention_prefill(const void* q, const void* pool, void* out, c
     cudaStream_t s = (cudaStream_t)stream;
     if (d <= 64)
         return launch_prefill<64>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                  n_layers, layer, nh, nkv, d, page_size, scale, window, s);
+                                  n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
     if (d <= 128)
         return launch_prefill<128>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                   n_layers, layer, nh, nkv, d, page_size, scale, window, s);
+                                   n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
     return launch_prefill<256>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                               n_layers, layer, nh, nkv, d, page_size, scale, window, s);
+                               n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
 }

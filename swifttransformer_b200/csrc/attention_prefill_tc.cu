@@ -124,6 +124,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         if (ok) {
             const int page = bt[key / page_size];
             ok = page >= 0;                                     // a hole in the block table: zeros, no access before the pool
+            if (!ok) *status = 1;                               // and the host hears of it
             if (ok) src = pool + (((size_t)page * n_layers + layer) * 2 + which) * kv_stride + kvh * head_stride
                           + (size_t)(key % page_size) * d;
         }

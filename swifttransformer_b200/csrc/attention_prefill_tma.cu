@@ -253,6 +253,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
             __syncwarp();
             if (lane < n_pg) {
                 const int c2 = page < 0 ? -1 : ((page * n_layers + layer) * 2 + which) * nkv + kvh;
+                if (page < 0) *status = 1;       // the host hears of the hole
                 const uint32_t o = (uint32_t)(lane * page_size) * 128;
 #pragma unroll
                 for (int b = 0; b < DB; ++b) tc_tma_load_3d(dst + b * KV_BLK + o, &kv_map, b * 64, 0, c2, mb);

@@ -121,12 +121,37 @@ static inline int st_launch_status() { return (int)cudaGetLastError(); }
 #include <string.h>
 // ST_B200_NO_PDL=1 turns the attribute off for every kernel; ST_B200_PDL_ONLY=a,b limits it to the
 // kernels whose tag is listed (for finding a kernel that breaks the rules above).
+// The environment is read once, at the first launch.
 static inline bool st_pdl_enabled(const char* tag) {
-    const char* off = getenv("ST_B200_NO_PDL");
+    static const char* const off = getenv("ST_B200_NO_PDL");
+    static const char* const only = getenv("ST_B200_PDL_ONLY");
     if (off && off[0] && off[0] != '0') return false;
-    const char* only = getenv("ST_B200_PDL_ONLY");
     if (only && only[0]) return strstr(only, tag) != nullptr;
     return true;
+}
+
+// Streaming multiprocessors of the current device (asked once per device).
+static inline int st_sm_count() {
+    static int count[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!count[dev]) {
+        int n = 0;
+        count[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return count[dev];
+}
+
+// Page numbers one block of the single-token attention kernels keeps in shared memory: those of its own
+// part of the key range (the whole range, or a window of it, cut into n_splits parts rounded up to 16 keys),
+// not of the longest request the block table has room for.
+static inline int st_decode_block_pages(int max_pages, int page_size, int window, int n_splits) {
+    long long span = (long long)max_pages * page_size;
+    if (window > 0 && window < span) span = window;
+    long long per = (span + n_splits - 1) / n_splits;
+    per = (per + 15) / 16 * 16;
+    const long long pages = per / page_size + 2;
+    return (int)(pages < max_pages ? pages : max_pages);
 }
 
 template <typename... KArgs, typename... Args>

@@ -307,7 +307,7 @@ static int launch_add_norm(const float* x, const int* rows, const void* delta, c
         const int vpt = width <= 4096 ? 2 : 4;
         int block = (width / (4 * vpt) + 31) / 32 * 32;
         if (block < 64) block = 64;
-        int grid = 148 * (vpt == 2 ? 4 : 2);
+        int grid = st_sm_count() * (vpt == 2 ? 4 : 2);
         if (grid > n_rows) grid = n_rows;
         if (vpt == 2)
             return st_launch_pdl("norm", add_norm_vec_kernel<T, 2>, dim3(grid), dim3(block), 0, s, x, rows, (const T*)delta,
@@ -369,7 +369,7 @@ ST_EXPORT int st_bias_act(void* y, const float* bias, int act, int n_rows, int w
     const bool vec = width % 4 == 0 && aligned16(y) && aligned16(bias);
     const size_t work = vec ? total / 4 : total;
     int grid = (int)((work + 255) / 256);
-    if (grid > 148 * 8) grid = 148 * 8;
+    if (grid > st_sm_count() * 8) grid = st_sm_count() * 8;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == 0) {
         if (vec) bias_act_kernel<float, true><<<grid, 256, 0, s>>>((float*)y, bias, act, total, width);

@@ -240,7 +240,7 @@ ST_EXPORT int st_gemm_skinny_max_rows() { return 32; }
 // four per SM) and no more, at most 8; at least one round of loads per warp and slice
 static int skinny_slices(int N, int K) {
     const int tiles = (N + 15) / 16;
-    int s = (4 * 148) / tiles;
+    int s = (4 * st_sm_count()) / tiles;
     const int nkb = (K + 31) / 32;
     if (s > nkb / (SK_WARPS * SK_UNROLL)) s = nkb / (SK_WARPS * SK_UNROLL);
     if (s > 8) s = 8;

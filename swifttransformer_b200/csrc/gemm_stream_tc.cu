@@ -236,7 +236,7 @@ static int gs_map(const void* ptr, long long rows, long long cols, unsigned box_
 // stages of k per slice, at most 8
 static int gs_slices(int N, int K) {
     const int tiles = (N + GS_BM - 1) / GS_BM, nkb = (K + GS_BK - 1) / GS_BK;
-    int s = 148 / tiles;
+    int s = st_sm_count() / tiles;
     if (s > nkb / 4) s = nkb / 4;
     if (s > 8) s = 8;
     return s < 1 ? 1 : s;

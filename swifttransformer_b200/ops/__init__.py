@@ -203,6 +203,9 @@ def lossless_bf16(v: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return low if bool(torch.equal(low.float(), v)) else None
 
 
+_addmm_activation = getattr(torch, "_addmm_activation", None)    # the library product with bias and ReLU in its epilogue
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
            out_dtype: Optional[torch.dtype] = None, bias_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(a @ w.T + bias); w is [out, in].  float32: the plain fused-multiply-add kernel (true 32-bit).
@@ -224,9 +227,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return gemm_stream_tc(a, w, bias, act, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(a, w.t(), out_dtype=torch.float32)
-    elif bias_bf16 is not None and act in ("none", "relu"):
+    elif bias_bf16 is not None and (act == "none" or (act == "relu" and _addmm_activation is not None)):
         if act == "relu":
-            return torch._addmm_activation(bias_bf16, a, w.t(), use_gelu=False)
+            return _addmm_activation(bias_bf16, a, w.t(), use_gelu=False)
         return torch.addmm(bias_bf16, a, w.t())
     else:
         y = torch.mm(a, w.t())
@@ -234,18 +237,14 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 
 
 # Up to this many tokens the weight-streaming kernel serves bfloat16 products.  The kernel itself takes up
-# to 32 rows, but measured on OPT-1.3B sizes cuBLAS is ahead from 9 rows on (batch 12: 1.65 vs 1.78 ms per
-# step, batch 32: 2.17 vs 3.29 ms).
+# to 32 rows; from 9 rows on the library product is ahead (profiles/small_m_products.md).
 SKINNY_MAX_ROWS = 8
 SKINNY_KERNEL_MAX_ROWS = 32
 
 
 # Up to this many tokens (and above SKINNY_MAX_ROWS) the tcgen05 weight-streaming kernel serves bfloat16
-# products; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on.  Off by default: measured
-# on OPT-1.3B decode steps it is behind the library at every batch (16: 1.71 against 1.57 ms per step,
-# 64: 3.83 against 2.48).  Of the 18 us an 8192 x 2048 product with 64 tokens takes in a graph, the copy
-# pipeline alone accounts for 8 (4.1 TB/s) and the epilogue for 9, 6 of them the reduction over k slices
-# through distributed shared memory.
+# products; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on
+# (profiles/small_m_products.md has the comparison).
 STREAM_TC_MAX_ROWS = 0
 
 
@@ -343,13 +342,14 @@ def qkv_to_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.T
 
 def attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
                     seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
-                    scale: float, window: int = 0) -> torch.Tensor:
-    """Paged causal attention, one block per (token, head), float arithmetic, any sizes."""
+                    scale: float, window: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged causal attention, one block per (token, head), float arithmetic, any sizes.  ``status`` (as for
+    the other attention kernels) is set to 1 when a key a query needs has no page in the block table."""
     n = q.shape[0]
     _, n_layers, _, nkv, page_size, d = pool.shape
     _check(lib().st_attention_plain(_p(q), _p(pool), _p(out), _p(positions), _p(seq_of_token), _p(slots),
                                     _p(block_table), block_table.shape[1], n_layers, layer, n, nh, nkv, d,
-                                    page_size, _f(scale), window, _dt(q), _stream()), "attention_plain")
+                                    page_size, _f(scale), window, _dt(q), _p(status), _stream()), "attention_plain")
     return out
 
 
@@ -375,7 +375,7 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                      seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
                      scale: float, window: int = 0, n_splits: int = 1,
                      partial: Optional[torch.Tensor] = None, fused_merge: bool = True,
-                     kernel: str = "auto", warps: int = 4) -> torch.Tensor:
+                     kernel: str = "auto", warps: int = 4, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 paged attention for single query tokens; ``items`` lists the token indices it serves
     (None: tokens 0..n_items-1).  A token whose position is negative is skipped.
 
@@ -394,11 +394,9 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                                               and n_items * nh <= _DECODE_COUNTERS) else None
     mma_ok = bool(lib().st_attention_decode_mma_applies(d)) and (n_splits == 1 or counters is not None)
     if kernel == "auto":
-        # Measured on OPT sizes (ms per decode step, tensor-core kernel against lanes kernel): head size 64
-        # (OPT-1.3B): batch 1: 1.150 / 1.147, 8: 1.340 / 1.348, 64: 2.485 / 2.738; head size 128 (OPT-6.7B),
-        # where the tensor-core kernel holds three blocks per SM against four: batch 1: 3.60 / 3.35,
-        # 8: 4.49 / 3.87, 16: 4.12 / 3.92, 64: 6.19 / 6.34.  Grouped queries always gain from it: the group
-        # shares one read of the keys and values.
+        # Head sizes up to 64: the tensor-core kernel; beyond, it holds fewer blocks per SM than the lanes
+        # kernel and pays only for many blocks; grouped queries always gain from it (the group shares one
+        # read of the keys and values).  Measurements: profiles/decode_attention_splits.md.
         busy = n_items * nkv >= DECODE_MMA_MIN_BLOCKS
         kernel = "mma" if mma_ok and (d <= 64 or nh != nkv or busy) else "lanes"
     if kernel == "mma":
@@ -409,12 +407,12 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                                              _p(positions), _p(seq_of_token), _p(slots), _p(block_table),
                                              block_table.shape[1], n_layers, layer, nh, nkv, d, page_size,
                                              _f(scale), window, n_splits, _p(counters), warps if d <= 64 else 4,
-                                             _stream()), "attention_decode_mma")
+                                             _p(status), _stream()), "attention_decode_mma")
     elif kernel == "lanes":
         _check(lib().st_attention_decode(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items, _p(positions),
                                          _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
                                          n_layers, layer, nh, nkv, d, page_size, _f(scale), window, n_splits,
-                                         _p(counters), _stream()), "attention_decode")
+                                         _p(counters), _p(status), _stream()), "attention_decode")
     else:
         raise KernelError(f"attention_decode: no kernel named {kernel!r}")
     return out
@@ -442,7 +440,7 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
     "tma3" = the same with three softmax warpgroups per block instead of two, at head size 64 only),
     "tc" = the tcgen05 kernel fed by asynchronous copies (head sizes up to 128), "mma" = the mma.sync
     kernel (up to 256), "auto" = the first of these that applies.  ``status`` receives 3 if a tcgen05
-    kernel gave up waiting."""
+    kernel gave up waiting, and 1 from any of them when a key a query needs has no page in the block table."""
     n_pages, n_layers, _, nkv, page_size, d = pool.shape
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill is a bfloat16 kernel")
@@ -470,7 +468,7 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
         raise KernelError(f"attention_prefill: no kernel named {kernel!r}")
     _check(lib().st_attention_prefill(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start), _p(start_pos),
                                       _p(slots), _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv,
-                                      d, page_size, _f(scale), window, _stream()), "attention_prefill")
+                                      d, page_size, _f(scale), window, _p(status), _stream()), "attention_prefill")
     return out
 
 

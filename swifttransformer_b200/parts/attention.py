@@ -128,7 +128,7 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
     fast = q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256
     if not fast:
         ops.attention_plain(q, cache.pool, cache.layer, out, ctx.positions, ctx.seq_of_token, ctx.slots,
-                            cache.block_table, nh, scale, window)
+                            cache.block_table, nh, scale, window, status=ctx.status)
         return out
     plan = ctx.plan(PagedAttentionPlan.name)
     if plan.n_tiles:
@@ -141,7 +141,8 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
                              ctx.seq_of_token, ctx.slots, cache.block_table, nh, scale, window,
                              n_splits, ctx.scratch_f32(ops.attention_decode_scratch(plan.n_items, nh, d, n_splits))
                              if n_splits > 1 else None,
-                             warps=ops.decode_warps(plan.n_items, nkv, d, n_splits, plan.max_item_kv))
+                             warps=ops.decode_warps(plan.n_items, nkv, d, n_splits, plan.max_item_kv),
+                             status=ctx.status)
     return out
 
 

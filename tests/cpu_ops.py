@@ -137,7 +137,7 @@ def qkv_to_cache(qkv, bias, q_out, pool, layer, positions, seq_of_token, slots, 
         pool[page, layer, 1, :, pos % ps, :] = v[t, (nh + nkv) * d:].view(nkv, d).to(pool.dtype)
 
 
-def attention_plain(q, pool, layer, out, positions, seq_of_token, slots, block_table, nh, scale, window=0):
+def attention_plain(q, pool, layer, out, positions, seq_of_token, slots, block_table, nh, scale, window=0, status=None):
     n = q.shape[0]
     _, _, _, nkv, ps, d = pool.shape
     g = nh // nkv
@@ -172,7 +172,7 @@ def attention_decode_scratch(n_items, nh, d, n_splits):
 
 
 def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_token, slots, block_table, nh,
-                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto", warps=4):
+                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto", warps=4, status=None):
     idx = items[:n_items].long() if items is not None else torch.arange(n_items)
     tmp = torch.zeros_like(out)
     pos = torch.full_like(positions, -1)

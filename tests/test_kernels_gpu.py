@@ -266,8 +266,9 @@ def test_attention_prefill(shape, window, kernel):
 
 def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
     """A page missing from a request's block table (-1) must not be read through: every attention kernel
-    treats the keys of that page as absent (zeros or dropped), leaves the other requests' results exact and
-    returns finite numbers for the request with the hole."""
+    treats the keys of that page as absent (zeros or dropped), leaves the other requests' results exact,
+    returns finite numbers for the request with the hole, and sets the status word to 1 so that the host
+    hears of it (ModelRunner.check_status then raises: the step's bookkeeping is broken)."""
     nh, nkv, d, ps = 4, 2, 64, 16
     dtype = torch.bfloat16
     lens, new = [200, 150, 300], [200, 1, 300]
@@ -286,18 +287,45 @@ def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
         out = torch.zeros_like(ref, device=DEV)
         ops.attention_prefill(dev["q"], dev["pool"], 1, out, tiles, tiles.numel() // 2, dev["q_start"], dev["start"],
                               dev["slots"], dev["bt"], nh, scale, 0, status=status, kernel=kernel)
-        assert int(status.item()) == 0 and torch.isfinite(out.float()).all()
+        assert int(status.item()) == 1, f"prefill {kernel}: the hole must be reported"
+        status.zero_()
+        assert torch.isfinite(out.float()).all()
         close(out[keep], ref[keep], dtype, f"prefill {kernel} beside a hole", rel=1.5e-2)
-    item = torch.tensor([200], dtype=torch.int32, device=DEV)     # request 1's token
-    for kernel in ("mma", "lanes"):
+    # without a hole the word stays 0
+    clean = bt.to(DEV)
+    for kernel in ("tma", "tc", "mma"):
         out = torch.zeros_like(ref, device=DEV)
+        ops.attention_prefill(dev["q"], dev["pool"], 1, out, tiles, tiles.numel() // 2, dev["q_start"], dev["start"],
+                              dev["slots"], clean, nh, scale, 0, status=status, kernel=kernel)
+        assert int(status.item()) == 0, kernel
+    item = torch.tensor([200], dtype=torch.int32, device=DEV)     # request 1's token
+    for kernel, splits in (("mma", 1), ("lanes", 1), ("mma", 3), ("lanes", 3)):
+        out = torch.zeros_like(ref, device=DEV)
+        partial = torch.empty(max(ops.attention_decode_scratch(1, nh, d, splits), 1), device=DEV)
         ops.attention_decode(dev["q"], dev["pool"], 1, out, item, 1, dev["pos"], dev["seq"], dev["slots"], dev["bt"],
-                             nh, scale, kernel=kernel)
+                             nh, scale, n_splits=splits, partial=partial, kernel=kernel, status=status)
+        assert int(status.item()) == 1, f"decode {kernel}/{splits}: the hole must be reported"
+        status.zero_()
         assert torch.isfinite(out.float()).all() and float(out[200].float().abs().max()) > 0
+        ops.attention_decode(dev["q"], dev["pool"], 1, out, item, 1, dev["pos"], dev["seq"], dev["slots"], clean,
+                             nh, scale, n_splits=splits, partial=partial, kernel=kernel, status=status)
+        assert int(status.item()) == 0
     out = torch.zeros_like(ref, device=DEV)
-    ops.attention_plain(dev["q"], dev["pool"], 1, out, dev["pos"], dev["seq"], dev["slots"], dev["bt"], nh, scale)
-    assert torch.isfinite(out.float()).all()
+    ops.attention_plain(dev["q"], dev["pool"], 1, out, dev["pos"], dev["seq"], dev["slots"], dev["bt"], nh, scale,
+                        status=status)
+    assert int(status.item()) == 1 and torch.isfinite(out.float()).all()
+    status.zero_()
     close(out[keep], ref[keep], dtype, "plain beside a hole", rel=1e-2)
+    # a request none of whose pages is there: zeros or finite numbers, never NaN
+    none = torch.full_like(dev["bt"], -1)
+    for kernel in ("lanes", "mma"):
+        out = torch.zeros_like(ref, device=DEV)
+        ops.attention_decode(dev["q"], dev["pool"], 1, out, item, 1, dev["pos"], dev["seq"], dev["slots"], none,
+                             nh, scale, kernel=kernel, status=status)
+        assert torch.isfinite(out.float()).all() and int(status.item()) == 1, kernel
+    out = torch.full_like(ref, 7.0, device=DEV)
+    ops.attention_plain(dev["q"], dev["pool"], 1, out, dev["pos"], dev["seq"], dev["slots"], none, nh, scale)
+    assert bool((out == 0).all())
 
 
 def test_attention_finds_a_far_key_among_hundreds():
