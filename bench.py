@@ -115,6 +115,9 @@ def main():
                          "and output lengths uniform in [16,512], prompt portions of 512 tokens beside decoded "
                          "tokens, through LLMEngine.generate (host token ids in and out, wall clock)")
     ap.add_argument("--requests", type=int, default=64, help="requests of the mixed continuous batch")
+    ap.add_argument("--set", action="append", default=[], metavar="MODULE.NAME=VALUE",
+                    help="set a tuning constant of the package before the run, e.g. ops.SKINNY_MAX_ROWS=32 or "
+                         "parts.attention.KEYS_PER_BLOCK=512 (for A/B measurements; may be repeated)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -138,6 +141,14 @@ def main():
     from swifttransformer_b200.models import random_model
     from swifttransformer_b200.sampling import SamplingParams
 
+    for item in args.set:
+        import importlib
+        target, value = item.split("=", 1)
+        module, name = target.rsplit(".", 1)
+        mod = importlib.import_module("swifttransformer_b200." + module)
+        if not hasattr(mod, name):
+            raise SystemExit(f"bench.py: swifttransformer_b200.{module} has no constant {name}")
+        setattr(mod, name, json.loads(value))
     peaks = load_peaks()
     cfg = opt_preset(args.model_name)
     full_layers = cfg.num_hidden_layers

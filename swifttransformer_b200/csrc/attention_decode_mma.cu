@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(DM_WARPS * 32)
 attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
                             float* __restrict__ partial, const int* __restrict__ items,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                            const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
+                            const int* __restrict__ slots, const int* __restrict__ start_pos,
+                            const int* __restrict__ block_table, int max_pages,
                             int n_layers, int layer, int nh, int nkv, int d_arg, int page_size, int page_shift,
                             float scale_log2, int window, int n_splits, int* __restrict__ counters,
                             int* __restrict__ status) {
@@ -64,7 +65,11 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int split = blockIdx.z;
     const int pos = positions[t];
     if (pos < 0) return;   // padding entry of a fixed-shape launch
-    const int slot = slots[seq_of_token[t]];
+    const int seq = seq_of_token[t];
+    const int slot = slots[seq];
+    // keys below this position were written by earlier steps: they may be read before the wait for the
+    // kernel before this one (which writes this step's keys and values); null: none may
+    const int old_hi = start_pos ? start_pos[seq] : 0;
     const int* bt = block_table + (size_t)slot * max_pages;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int hi = pos + 1;
@@ -85,32 +90,12 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             if (page < 0 && status) *status = 1;     // a hole in the block table: zeros are read for it and the host hears of it
         }
     }
-    ST_PDL_WAIT();
-    for (int i = threadIdx.x; i < 16 * chunks; i += DM_THREADS) {
-        const int r = i / chunks, c = i - r * chunks;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < n_heads) v = __ldcg(reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h0 + r) * d + c * 8));
-        *reinterpret_cast<uint4*>(tile_ptr<DMAX>(sQ, r, c)) = v;
-    }
-    __syncthreads();
+    __syncthreads();          // the page numbers are in place for every warp
 
     const size_t head_stride = (size_t)page_size * d;
     const size_t kv_stride = (size_t)nkv * head_stride;
     const size_t page_stride = (size_t)n_layers * 2 * kv_stride;
     const bf16* kbase = pool + (size_t)layer * 2 * kv_stride + kvh * head_stride;   // this layer's and head's keys in page 0
-
-    // the query operand: fragments of the 16 x d tile, kept in registers
-    uint32_t qa[DMAX / 16][4];
-#pragma unroll
-    for (int kk = 0; kk < DMAX / 16; ++kk) {
-        if (kk * 16 < d)
-            ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3],
-                        tile_ptr<DMAX>(sQ, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
-    }
-    float o_acc[DMAX / 8][4];
-#pragma unroll
-    for (int i = 0; i < DMAX / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
 
     // this warp's groups of 16 keys: warp, warp + 4, ... of the block's range
     const int n_groups = k_lo < k_hi ? (k_hi - k_lo + DM_KEYS - 1) / DM_KEYS : 0;
@@ -176,11 +161,45 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             cp_async16_s(dk + V_BYTES + ld_off[j], ok ? src + kv_stride : pool, ok);
         }
     };
+    // The first stages: groups whose keys all lie below old_hi were written by earlier steps and are asked
+    // for now, under the tail of the kernel before this one; the rest, and the queries, after the wait.
+    int early = 0;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < my_n) load_group(s, s);
-        cp_async_commit();
+        if (early == s && s < my_n && k_lo + (warp + s * DM_WARPS + 1) * DM_KEYS <= old_hi) {
+            load_group(s, s);
+            cp_async_commit();
+            ++early;
+        }
     }
+    ST_PDL_WAIT();
+    for (int i = threadIdx.x; i < 16 * chunks; i += DM_THREADS) {
+        const int r = i / chunks, c = i - r * chunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_heads) v = __ldcg(reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h0 + r) * d + c * 8));
+        *reinterpret_cast<uint4*>(tile_ptr<DMAX>(sQ, r, c)) = v;
+    }
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s >= early) {
+            if (s < my_n) load_group(s, s);
+            cp_async_commit();
+        }
+    }
+    __syncthreads();          // the queries are in place
+    // the query operand: fragments of the 16 x d tile, kept in registers
+    uint32_t qa[DMAX / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+        if (kk * 16 < d)
+            ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3],
+                        tile_ptr<DMAX>(sQ, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
+    }
+    float o_acc[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
+
     for (int i = 0; i < my_n; ++i) {
         if (i + STAGES - 1 < my_n) load_group(i + STAGES - 1, (i + STAGES - 1) % STAGES);
         cp_async_commit();
@@ -351,12 +370,14 @@ static size_t dm_smem_bytes(int d, int block_pages, int warps) {
 
 ST_EXPORT int st_attention_decode_mma_applies(int d) { return d > 0 && d % 16 == 0 && d <= 128; }
 
-// Same arguments and scratch layout as st_attention_decode, and the number of warps per block (4 or 8).
+// Same arguments and scratch layout as st_attention_decode, and the number of warps per block (4 or 8);
+// start_pos (per request: the tokens it had in the cache before this step, or null) tells which keys earlier
+// steps wrote, so that their copies can start before the kernel before this one has finished.
 ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out, float* partial, const int* items,
                                       int n_items, const int* positions, const int* seq_of_token, const int* slots,
-                                      const int* block_table, int max_pages, int n_layers, int layer, int nh,
-                                      int nkv, int d, int page_size, float scale, int window, int n_splits,
-                                      int* counters, int warps, int* status, void* stream) {
+                                      const int* start_pos, const int* block_table, int max_pages, int n_layers,
+                                      int layer, int nh, int nkv, int d, int page_size, float scale, int window,
+                                      int n_splits, int* counters, int warps, int* status, void* stream) {
     if (n_items <= 0) return 0;
     if (warps != 4 && warps != 8) return ST_ERR_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
@@ -386,7 +407,7 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
         rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL, WARPS>, grid, dim3(WARPS * 32),    \
                            smem, s, (const bf16*)q, (const bf16*)pool, (bf16*)out,                                   \
                            n_splits > 1 ? partial : (float*)nullptr, items, positions, seq_of_token, slots,          \
-                           block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift, sl2, window,  \
+                           start_pos, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift, sl2, window,  \
                            n_splits, counters, status);                                                              \
     } while (0)
 #define LAUNCH_DM_W(DMAX, FULL)                                                                                      \

@@ -23,6 +23,19 @@
 // trip through L2 costs more than a microsecond here, and the old scheme
 // (scratch + counter + re-read) needed four of them.
 //
+// Two fusions take a neighbour of the product into its kernel.  The residual sum behind is what decode steps
+// use.  The norm in front is correct and tested but not used by the engine: in the recorded step a product
+// runs fastest when all its blocks start together on an idle GPU right behind a small norm kernel (whose few
+// microseconds hide the product's launch and first loads); with the norm inside, the product either starts
+// early, block by block as its predecessor drains, and streams at half the rate, or starts late and shows
+// its own prologue (profiles/decode_step_fusions.md):
+//   * a norm in front: the activations are norm(x) of the float residual rows x (LayerNorm or RMS norm,
+//     two-pass variance in float).  The blocks form clusters of as many blocks as there are rows (1, 2, 4
+//     or 8): block r of a cluster normalises row r with all its threads and stores the bfloat16 row into the
+//     shared memory of every block of the cluster (distributed shared memory), so a row is read from L2 once
+//     per cluster, and after one cluster barrier every block has all rows next to its tensor cores;
+//   * the residual sum behind: out[m, n] += product + bias in float, in place (each element has one owner).
+//
 // Epilogues: bias and activation; float or bfloat16 output; or the fused
 // q|k|v form: q (+bias) to a dense buffer, k and v (+bias) straight into the
 // paged cache at each token's position (what st_qkv_to_cache does after a
@@ -38,6 +51,7 @@ namespace cg = cooperative_groups;
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
+#define SK_XPAD 32        // bfloat16 elements between the rows of the normalised activations in shared memory
 #define SK_UNROLL 1      // k-blocks per round with up to 8 tokens; one with more (registers: four blocks per SM either way)
 
 struct QkvTarget {
@@ -58,6 +72,18 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The float rows a norm in front of the product reads, and the norm's constants.
+struct NormSource {
+    const float* x;            // [M, K] residual rows
+    const float* gamma;        // [K] or null
+    const float* beta;         // [K] or null
+    float eps;
+    int kind;                  // 0 LayerNorm, 1 RMS norm, 2 none (cast only)
+};
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+
 __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read once, do not keep in L1
     uint4 r;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -66,12 +92,17 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
 }
 
 // KFULL: K is a multiple of 32 (known when compiling: no test on k inside a block of 32)
-template <int NT, bool QKV, bool KFULL>
+// XV: 0; or the float4 pieces of a row each thread normalises (K <= 1024 * XV): the norm in front; or -1: the
+//     residual sum behind (out is float and the product is added to what is there)
+// out_f32: 0 bfloat16, 1 float
+template <int NT, bool QKV, bool KFULL, int XV>
 __global__ void __launch_bounds__(SK_THREADS, NT <= 2 ? 4 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
-                   void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt) {
+                   void* __restrict__ out, int M, int N, int K, int act, int out_f32, QkvTarget tgt, NormSource src) {
     __shared__ float red[SK_WARPS][16][8 * NT + 1];
     __shared__ float part[16 * 8 * NT];      // this block's sums over its slice of k
+    extern __shared__ __align__(16) unsigned char sk_dyn[];
+    bf16* xs = reinterpret_cast<bf16*>(sk_dyn);      // XV > 0: the normalised rows, [M][K + SK_XPAD]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * 16;
     const bf16* wa = w + (size_t)min(row0 + g, N - 1) * K + t * 8;
@@ -115,8 +146,12 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
             const int kb = kb0 + u * SK_WARPS;
             const bool ok = kb < nkb && (KFULL || kb * 32 + t * 8 < K);
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
-                r.xb[u][j] = (ok && xok[j]) ? __ldcg(reinterpret_cast<const uint4*>(xr[j] + kb * 32)) : zero;
+            for (int j = 0; j < NT; ++j) {
+                if (XV > 0)      // row g of the normalised rows in shared memory (rows 64 bytes askew: no bank conflicts)
+                    r.xb[u][j] = (ok && xok[j]) ? *reinterpret_cast<const uint4*>(xs + (size_t)g * (K + SK_XPAD) + kb * 32 + t * 8) : zero;
+                else
+                    r.xb[u][j] = (ok && xok[j]) ? __ldcg(reinterpret_cast<const uint4*>(xr[j] + kb * 32)) : zero;
+            }
         }
     };
     auto consume = [&](const Round& r) {
@@ -148,7 +183,94 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         if (pos_pre >= 0)
             page_pre = tgt.block_table[(size_t)tgt.slots[tgt.seq_of_token[m]] * tgt.max_pages + pos_pre / tgt.page_size];
     }
+    // the norm's gain and shift for this thread's pieces of a row are static too
+    constexpr bool NORM_PRE = XV > 0 && XV <= 2;      // wider rows: too many registers, fetched when used
+    float4 gam[NORM_PRE ? XV : 1], bet[NORM_PRE ? XV : 1];
+    (void)gam; (void)bet;
+    if (XV > 0) cluster_arrive();                     // matched below: every block of the cluster has started
+    if (NORM_PRE) {
+#pragma unroll
+        for (int i = 0; i < (NORM_PRE ? XV : 1); ++i) {
+            const int col = (i * SK_THREADS + threadIdx.x) * 4;
+            gam[i] = (src.gamma && col < K) ? *reinterpret_cast<const float4*>(src.gamma + col) : make_float4(1.f, 1.f, 1.f, 1.f);
+            bet[i] = (src.beta && col < K) ? *reinterpret_cast<const float4*>(src.beta + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float resid_pre = 0.f;
     ST_PDL_WAIT();
+    if constexpr (XV < 0) {
+        // the residual element this thread adds to in its first epilogue turn, asked for now
+        const int m = threadIdx.x >> 4, n = row0 + (threadIdx.x & 15);
+        if (threadIdx.x < 16 * 8 * NT && m < M && n < N && (gridDim.y == 1 || blockIdx.y == 0))
+            resid_pre = __ldcg(reinterpret_cast<const float*>(out) + (size_t)m * N + n);
+    }
+    if constexpr (XV > 0) {
+        // Block r of the cluster normalises row r with all its threads (the pieces of the row stay in
+        // registers between the two passes) and stores it, in bfloat16, into every block of the cluster.
+        cg::cluster_group cluster = cg::this_cluster();
+        const int cs = (int)cluster.num_blocks(), r = (int)cluster.block_rank();
+        __shared__ float nscratch[32];
+        bool first_row = true;
+        for (int row = r; row < M; row += cs) {
+            float4 v[XV > 0 ? XV : 1];
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                const int col = (i * SK_THREADS + threadIdx.x) * 4;
+                v[i] = col < K ? __ldcg(reinterpret_cast<const float4*>(src.x + (size_t)row * K + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            }
+            float mean = 0.f, rstd = 1.f;
+            if (src.kind == 0) {
+                mean = block_sum(sum, nscratch) / (float)K;
+                float sq = 0.f;
+#pragma unroll
+                for (int i = 0; i < XV; ++i) {
+                    const int col = (i * SK_THREADS + threadIdx.x) * 4;
+                    if (col < K) {
+                        const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+                        sq += (a * a + b * b) + (c * c + d * d);
+                    }
+                }
+                rstd = rsqrtf(block_sum(sq, nscratch) / (float)K + src.eps);
+            } else if (src.kind == 1) {
+                float sq = 0.f;
+#pragma unroll
+                for (int i = 0; i < XV; ++i) sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+                rstd = rsqrtf(block_sum(sq, nscratch) / (float)K + src.eps);
+            }
+            if (first_row) { cluster_wait(); first_row = false; }
+#pragma unroll
+            for (int i = 0; i < XV; ++i) {
+                const int col = (i * SK_THREADS + threadIdx.x) * 4;
+                if (col < K) {
+                    float4 y;
+                    if (src.kind == 2) {
+                        y = v[i];
+                    } else {
+                        float4 ga, be;
+                        if (NORM_PRE) { ga = gam[NORM_PRE ? i : 0]; be = bet[NORM_PRE ? i : 0]; }
+                        else {
+                            ga = src.gamma ? *reinterpret_cast<const float4*>(src.gamma + col) : make_float4(1.f, 1.f, 1.f, 1.f);
+                            be = src.beta ? *reinterpret_cast<const float4*>(src.beta + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        y.x = (v[i].x - mean) * rstd * ga.x + be.x;
+                        y.y = (v[i].y - mean) * rstd * ga.y + be.y;
+                        y.z = (v[i].z - mean) * rstd * ga.z + be.z;
+                        y.w = (v[i].w - mean) * rstd * ga.w + be.w;
+                    }
+                    uint2 packed;
+                    *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(y.x, y.y);
+                    *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(y.z, y.w);
+                    for (int dst = 0; dst < cs; ++dst)
+                        *reinterpret_cast<uint2*>(cluster.map_shared_rank(xs, dst) + (size_t)row * (K + SK_XPAD) + col) = packed;
+                }
+            }
+        }
+        if (first_row) cluster_wait();           // a block without a row of its own
+        cluster.sync();                          // every row is in place in every block
+        if (row0 >= N) return;                   // a block that only filled the cluster: nothing reads its memory from here on
+    }
     if (NT == 1) {
         // three rounds in flight (two of them asked for before the wait)
         issue_x(ra, kb_first);
@@ -210,7 +332,10 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         v += bias_pre;
         if (!QKV) {
             v = apply_act(v, act);
-            if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
+            if (XV < 0) {            // the residual sum, in place: this thread is the element's only owner
+                float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n;
+                *o = (i == (int)threadIdx.x ? resid_pre : __ldcg(o)) + v;
+            } else if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
             else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
         } else {
             if (n < tgt.qw) {
@@ -247,23 +372,28 @@ static int skinny_slices(int N, int K) {
     return s < 1 ? 1 : s;
 }
 
+// cluster_x: blocks along x that form a cluster (the norm in front), else 1; along y the slices of k do
 template <typename... KArgs, typename... Args>
-static int launch_skinny_kernel(void (*kernel)(KArgs...), dim3 grid, cudaStream_t s, Args... args) {
+static int launch_skinny_kernel(const char* tag, void (*kernel)(KArgs...), dim3 grid, size_t smem, int cluster_x,
+                                cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(SK_THREADS);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     int n = 0;
-    if (st_pdl_enabled("skinny")) {
+    // A product whose blocks form clusters over slices of k starts after its predecessor has finished, not as
+    // its blocks drain: started early, its clusters land wherever room appears and the step is 3 % slower
+    // (profiles/decode_step_fusions.md).
+    if (st_pdl_enabled(tag) && grid.y == 1) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (grid.y > 1) {
+    if (grid.y > 1 || cluster_x > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.x = cluster_x;
         attr[n].val.clusterDim.y = grid.y;
         attr[n].val.clusterDim.z = 1;
         ++n;
@@ -275,7 +405,7 @@ static int launch_skinny_kernel(void (*kernel)(KArgs...), dim3 grid, cudaStream_
     return st_launch_status();
 }
 
-template <bool QKV>
+template <bool QKV, int XV = 0>
 static int launch_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, int act,
                          int out_f32, const QkvTarget& tgt, cudaStream_t s) {
     if (M <= 0 || N <= 0) return 0;
@@ -283,19 +413,74 @@ static int launch_skinny(const void* x, const void* w, const float* bias, void* 
     if (K <= 0 || K % 8) return ST_ERR_BAD_SIZE;
     if (!aligned16(x) || !aligned16(w)) return ST_ERR_BAD_ARG;
     dim3 grid((N + 15) / 16, skinny_slices(N, K));
+    const NormSource no_norm = {};
 #define LAUNCH_SK(NT)                                                                                              \
-    (K % 32 == 0 ? launch_skinny_kernel(gemm_skinny_kernel<NT, QKV, true>, grid, s, (const bf16*)x, (const bf16*)w, \
-                                        bias, out, M, N, K, act, out_f32, tgt)                                      \
-                 : launch_skinny_kernel(gemm_skinny_kernel<NT, QKV, false>, grid, s, (const bf16*)x, (const bf16*)w, \
-                                        bias, out, M, N, K, act, out_f32, tgt))
+    (K % 32 == 0 ? launch_skinny_kernel(XV < 0 ? (K > 4096 ? "gemm_add_wide" : "gemm_add") : "skinny", gemm_skinny_kernel<NT, QKV, true, XV>, grid, 0, 1, s, (const bf16*)x,      \
+                                        (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, no_norm)            \
+                 : launch_skinny_kernel(XV < 0 ? "gemm_add" : "skinny", gemm_skinny_kernel<NT, QKV, false, XV>, grid, 0, 1, s, (const bf16*)x,     \
+                                        (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, no_norm))
     if (M <= 8) return LAUNCH_SK(1);
     if (M <= 16) return LAUNCH_SK(2);
     return LAUNCH_SK(4);
 #undef LAUNCH_SK
 }
 
+// The norm in front: at most 8 rows, K a multiple of 32 up to 8192.  One block per 16 features, no slices of
+// k (the blocks along x form clusters of as many blocks as rows instead).
+ST_EXPORT int st_gemm_skinny_norm_applies(int M, int K) { return M >= 1 && M <= 8 && K % 32 == 0 && K >= 32 && K <= 8192; }
+
+template <bool QKV>
+static int launch_skinny_norm(const NormSource& src, const void* w, const float* bias, void* out, int M, int N, int K,
+                              int act, int out_f32, const QkvTarget& tgt, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!st_gemm_skinny_norm_applies(M, K)) return ST_ERR_BAD_SIZE;
+    if (src.kind < 0 || src.kind > 2) return ST_ERR_BAD_ARG;
+    if (!aligned16(src.x) || !aligned16(w) || !aligned16(src.gamma) || !aligned16(src.beta)) return ST_ERR_BAD_ARG;
+    int cs = 1;
+    while (cs < M) cs *= 2;
+    const int tiles = (N + 15) / 16;
+    dim3 grid((tiles + cs - 1) / cs * cs, 1);
+    const size_t smem = (size_t)M * (K + SK_XPAD) * sizeof(bf16);
+#define LAUNCH_SKN(XV)                                                                                             \
+    do {                                                                                                           \
+        static size_t allowed = 48 * 1024 - 6 * 1024;      /* what a kernel may use without asking, less its static part */ \
+        if (smem > allowed) {                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<1, QKV, true, XV>,                             \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+            allowed = smem;                                                                                        \
+        }                                                                                                          \
+        return launch_skinny_kernel(QKV ? "qkv_norm" : "gemm_norm", gemm_skinny_kernel<1, QKV, true, XV>, grid, smem, cs, s, (const bf16*)nullptr, \
+                                    (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, src);                   \
+    } while (0)
+    if (K <= 1024) LAUNCH_SKN(1);
+    if (K <= 2048) LAUNCH_SKN(2);
+    if (K <= 4096) LAUNCH_SKN(4);
+    LAUNCH_SKN(8);
+#undef LAUNCH_SKN
+}
+
+// act( norm(x) . w^T + bias ) for at most 8 float rows x [M, K]: the norm of st_add_norm (kind 0 LayerNorm, 1 RMS
+// norm, 2 none; gamma and beta may be null) fused in front of the product.
+ST_EXPORT int st_gemm_skinny_norm(const float* x, const float* gamma, const float* beta, float eps, int kind,
+                                  const void* w, const float* bias, void* out, int M, int N, int K, int act,
+                                  int out_f32, void* stream) {
+    const NormSource src = {x, gamma, beta, eps, kind};
+    QkvTarget none = {};
+    if (out_f32 < 0 || out_f32 > 1) return ST_ERR_BAD_ARG;
+    return launch_skinny_norm<false>(src, w, bias, out, M, N, K, act, out_f32, none, (cudaStream_t)stream);
+}
+
+// out [M, N] (float) += x . w^T + bias: the residual sum fused behind the product.
+ST_EXPORT int st_gemm_skinny_add(const void* x, const void* w, const float* bias, float* out, int M, int N, int K,
+                                 void* stream) {
+    QkvTarget none = {};
+    return launch_skinny<false, -1>(x, w, bias, out, M, N, K, 0, 1, none, (cudaStream_t)stream);
+}
+
 ST_EXPORT int st_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
                              int act, int out_f32, void* stream) {
+    if (out_f32 < 0 || out_f32 > 1) return ST_ERR_BAD_ARG;
     QkvTarget none = {};
     return launch_skinny<false>(x, w, bias, out, M, N, K, act, out_f32, none, (cudaStream_t)stream);
 }
@@ -313,4 +498,21 @@ ST_EXPORT int st_gemm_skinny_qkv(const void* x, const void* w, const float* bias
     tgt.num_pages = num_pages; tgt.n_layers = n_layers; tgt.layer = layer; tgt.nkv = nkv; tgt.d = d;
     tgt.page_size = page_size; tgt.qw = nh * d; tgt.write_kv = write_kv;
     return launch_skinny<true>(x, w, bias, nullptr, M, (nh + 2 * nkv) * d, K, 0, 0, tgt, (cudaStream_t)stream);
+}
+
+// The same with the norm of the float residual rows x fused in front (see st_gemm_skinny_norm).
+ST_EXPORT int st_gemm_skinny_norm_qkv(const float* x, const float* gamma, const float* beta, float eps, int kind,
+                                      const void* w, const float* bias, void* q_out, void* pool,
+                                      const int* positions, const int* seq_of_token, const int* slots,
+                                      const int* block_table, int max_pages, int num_pages, int n_layers, int layer,
+                                      int M, int K, int nh, int nkv, int d, int page_size, int write_kv, int* status,
+                                      void* stream) {
+    if (nh <= 0 || nkv <= 0 || d <= 0 || page_size <= 0 || layer < 0 || layer >= n_layers) return ST_ERR_BAD_ARG;
+    QkvTarget tgt;
+    tgt.q_out = (bf16*)q_out; tgt.pool = (bf16*)pool; tgt.positions = positions; tgt.seq_of_token = seq_of_token;
+    tgt.slots = slots; tgt.block_table = block_table; tgt.status = status; tgt.max_pages = max_pages;
+    tgt.num_pages = num_pages; tgt.n_layers = n_layers; tgt.layer = layer; tgt.nkv = nkv; tgt.d = d;
+    tgt.page_size = page_size; tgt.qw = nh * d; tgt.write_kv = write_kv;
+    const NormSource src = {x, gamma, beta, eps, kind};
+    return launch_skinny_norm<true>(src, w, bias, nullptr, M, (nh + 2 * nkv) * d, K, 0, 0, tgt, (cudaStream_t)stream);
 }

@@ -292,6 +292,80 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+# ---- the same products with their neighbours fused (steps of a few tokens) ----
+# The residual sum behind a product (out[m, n] += ..., in float, in the product's epilogue) is used: a decode
+# step gains 4 %.  The norm in front of a product (five kernels per pre-norm layer instead of seven) is built
+# and tested but off: measured in the recorded step it loses, at batch 8 by 10 %, because the small norm
+# kernel between two products is what lets the second product start all at once on an idle GPU with its
+# first loads already under way (profiles/decode_step_fusions.md).  With a switch off, the operation runs as
+# the separate kernels it replaces.
+FUSED_MAX_ROWS = 8
+FUSE_NORM = False
+FUSE_RESIDUAL = True
+
+
+def fused_norm_applies(n_rows: int, k: int, w: torch.Tensor) -> bool:
+    """Whether ``norm_linear`` / ``norm_qkv_linear_to_cache`` / ``linear_add`` take a step of n_rows tokens
+    with inner dimension k and weights w."""
+    return (w.is_cuda and w.dtype == torch.bfloat16 and 1 <= n_rows <= min(FUSED_MAX_ROWS, SKINNY_MAX_ROWS)
+            and bool(lib().st_gemm_skinny_norm_applies(n_rows, k)))
+
+
+def norm_linear(x: torch.Tensor, kind: str, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor], eps: float,
+                w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(norm(x) @ w.T + bias) for at most FUSED_MAX_ROWS float32 rows x (the residual stream) and bfloat16
+    w [out, in]: the norm of ``add_norm`` (statistics in float, two passes; its result rounded to bfloat16 as
+    ``add_norm`` stores it) in front of the weight-streaming product, in one kernel."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and w.is_contiguous() and x.shape[1] == w.shape[1]
+    n, k = x.shape
+    m = w.shape[0]
+    out_dtype = out_dtype or w.dtype
+    if not FUSE_NORM:
+        h = torch.empty((n, k), dtype=w.dtype, device=x.device)
+        add_norm(x, gamma=gamma, beta=beta, eps=eps, kind=kind, out_act=h)
+        return gemm_skinny(h, w, bias, act, out_dtype)
+    out = torch.empty((n, m), dtype=out_dtype, device=x.device)
+    _check(lib().st_gemm_skinny_norm(_p(x), _p(gamma), _p(beta), _f(eps), NORM_CODES[kind], _p(w), _p(bias), _p(out),
+                                     n, m, k, ACT_CODES[act], int(out_dtype == torch.float32), _stream()),
+           "norm_linear")
+    return out
+
+
+def linear_add(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], x: torch.Tensor) -> None:
+    """x += a @ w.T + bias in place, for at most FUSED_MAX_ROWS bfloat16 rows a and float32 x (the residual
+    stream): the residual sum behind the weight-streaming product, in float, in one kernel."""
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dtype == torch.float32
+    assert a.is_contiguous() and w.is_contiguous() and x.is_contiguous()
+    assert a.shape[1] == w.shape[1] and x.shape == (a.shape[0], w.shape[0])
+    if not FUSE_RESIDUAL:
+        add_norm(x, delta=gemm_skinny(a, w), delta_bias=bias, resid_out=x, kind="none", act_dtype=a.dtype)
+        return
+    _check(lib().st_gemm_skinny_add(_p(a), _p(w), _p(bias), _p(x), a.shape[0], w.shape[0], a.shape[1], _stream()),
+           "linear_add")
+
+
+def norm_qkv_linear_to_cache(x: torch.Tensor, kind: str, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor],
+                             eps: float, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                             pool: torch.Tensor, layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                             slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, d: int,
+                             status: torch.Tensor, write_kv: bool = True) -> None:
+    """``qkv_linear_to_cache`` of norm(x) for float32 rows x: norm, product, bias and cache write in one kernel."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and w.is_contiguous() and pool.dtype == torch.bfloat16
+    num_pages, n_layers, _, pnkv, page_size, pd = pool.shape
+    assert pnkv == nkv and pd == d and w.shape[0] == (nh + 2 * nkv) * d
+    if not FUSE_NORM:
+        h = torch.empty(x.shape, dtype=w.dtype, device=x.device)
+        add_norm(x, gamma=gamma, beta=beta, eps=eps, kind=kind, out_act=h)
+        return qkv_linear_to_cache(h, w, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv,
+                                   d, status, write_kv)
+    _check(lib().st_gemm_skinny_norm_qkv(_p(x), _p(gamma), _p(beta), _f(eps), NORM_CODES[kind], _p(w), _p(bias),
+                                         _p(q_out), _p(pool), _p(positions), _p(seq_of_token), _p(slots),
+                                         _p(block_table), block_table.shape[1], num_pages, n_layers, layer,
+                                         x.shape[0], x.shape[1], nh, nkv, d, page_size, int(write_kv), _p(status),
+                                         _stream()), "norm_qkv_linear_to_cache")
+
+
 def qkv_linear_to_cache(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                         pool: torch.Tensor, layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
                         slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, d: int,
@@ -375,14 +449,17 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
                      seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
                      scale: float, window: int = 0, n_splits: int = 1,
                      partial: Optional[torch.Tensor] = None, fused_merge: bool = True,
-                     kernel: str = "auto", warps: int = 4, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     kernel: str = "auto", warps: int = 4, status: Optional[torch.Tensor] = None,
+                     start_pos: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 paged attention for single query tokens; ``items`` lists the token indices it serves
     (None: tokens 0..n_items-1).  A token whose position is negative is skipped.
 
     kernel: "mma" = the tensor-core kernel (head sizes that are multiples of 16 up to 128; with several
     splits it needs the fused merge), "lanes" = the kernel with eight lanes per key (multiples of 8 up to
     256), "auto" = the first that applies.  warps: warps per block of the tensor-core kernel, 4 or 8 (8 pays
-    for few and long blocks with head sizes up to 64, see decode_warps)."""
+    for few and long blocks with head sizes up to 64, see decode_warps).  start_pos: per request of the step, the
+    tokens it had in the cache before the step: the tensor-core kernel starts copying those keys before the
+    kernel that writes this step's keys has finished (None: it waits first)."""
     _, n_layers, _, nkv, page_size, d = pool.shape
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode is a bfloat16 kernel")
@@ -404,9 +481,10 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
             raise KernelError("attention_decode: the tensor-core kernel takes head sizes that are multiples of "
                               "16 up to 128 and merges its splits itself")
         _check(lib().st_attention_decode_mma(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items,
-                                             _p(positions), _p(seq_of_token), _p(slots), _p(block_table),
-                                             block_table.shape[1], n_layers, layer, nh, nkv, d, page_size,
-                                             _f(scale), window, n_splits, _p(counters), warps if d <= 64 else 4,
+                                             _p(positions), _p(seq_of_token), _p(slots), _p(start_pos),
+                                             _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv, d,
+                                             page_size, _f(scale), window, n_splits, _p(counters),
+                                             warps if d <= 64 else 4,
                                              _p(status), _stream()), "attention_decode_mma")
     elif kernel == "lanes":
         _check(lib().st_attention_decode(_p(q), _p(pool), _p(out), _p(partial), _p(items), n_items, _p(positions),

@@ -142,7 +142,7 @@ def paged_attention(q: torch.Tensor, cache: Any, ctx: Any, nh: int, scale: float
                              n_splits, ctx.scratch_f32(ops.attention_decode_scratch(plan.n_items, nh, d, n_splits))
                              if n_splits > 1 else None,
                              warps=ops.decode_warps(plan.n_items, nkv, d, n_splits, plan.max_item_kv),
-                             status=ctx.status)
+                             status=ctx.status, start_pos=ctx.start_pos)
     return out
 
 
@@ -218,6 +218,22 @@ class Attention(Mixer):
                              write_kv=cache.writable)
         o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
         return Delta(ops.linear(o, self.w_o), self.b_o)
+
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any) -> bool:
+        """x += attention(norm(x)) for a step of a few tokens in three kernels: norm + q|k|v product + bias +
+        cache write; attention; output product + bias + residual sum."""
+        if getattr(self.qk_position, "apply_qk", None) is not None or norm.kind not in ops.NORM_CODES:
+            return False
+        if not ops.fused_norm_applies(x.shape[0], self.hidden, self.w_qkv):
+            return False
+        q = torch.empty((x.shape[0], self.nh * self.d), dtype=self.w_qkv.dtype, device=x.device)
+        ops.norm_qkv_linear_to_cache(x, norm.kind, norm.gamma, norm.beta, norm.eps, self.w_qkv, self.b_qkv, q,
+                                     cache.pool, cache.layer, ctx.positions, ctx.seq_of_token, ctx.slots,
+                                     cache.block_table, self.nh, self.nkv, self.d, ctx.status,
+                                     write_kv=cache.writable)
+        o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
+        ops.linear_add(o, self.w_o, self.b_o, x)
+        return True
 
     def param_bytes(self) -> int:
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

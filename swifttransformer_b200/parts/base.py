@@ -19,6 +19,8 @@ Mixer.cache_spec()        -> PagedKVSpec | StateSpec | None
 Mixer.step_plan()         -> StepPlan | None  (host work once per step, see StepPlan)
 Mixer.forward(h, ctx, cache) -> Delta         h: [N, width] activations
 FeedForward.forward(h, ctx)  -> Delta
+Mixer.forward_into_residual(x, norm, ctx, cache), FeedForward.forward_into_residual(x, norm, ctx) -> bool
+                          optional: the whole sub-layer with its norm and residual sum fused in, in place
 Norm.apply(x, delta, ...)    -> see parts.norm
 PositionEncoding.table()     -> (table, offset) for encodings added to the hidden state
 Block.forward(stream, ctx, cache) -> None (updates the residual stream)
@@ -134,10 +136,21 @@ class Mixer(Part):
     def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:
         raise NotImplementedError
 
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any) -> bool:
+        """Optional fast path of a pre-norm block: x <- x + mixer(norm(x)) in place on the float32 residual
+        rows x, with the norm (a parts.norm.Norm: its kind, gain, shift and eps) fused into the mixer's first
+        kernel and the residual sum into its last.  Return False, having changed nothing, when it does not
+        apply to this step; the block then calls ``norm.apply`` and ``forward``."""
+        return False
+
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
         raise NotImplementedError
+
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any) -> bool:
+        """Optional fast path of a pre-norm block: x <- x + feed_forward(norm(x)) in place (see Mixer)."""
+        return False
 
 
 class Registry:

@@ -58,10 +58,18 @@ class Block(Part):
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
     def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
-        h = self.norm1.apply(stream.x, stream.pending, act_dtype=stream.act_dtype)
-        a = self.mixer.forward(h, ctx, cache)
-        h = self.norm2.apply(stream.x, a, act_dtype=stream.act_dtype)
-        stream.pending = self.feed_forward.forward(h, ctx)
+        # A sub-layer that can take its norm and its residual sum into its own kernels does so (steps of a
+        # few tokens, where every kernel less shortens the chain); otherwise norm kernel, sub-layer, and the
+        # result left pending for the next norm kernel to add.
+        x, pending = stream.x, stream.pending
+        low = stream.act_dtype != torch.float32
+        if not (low and pending is None and self.mixer.forward_into_residual(x, self.norm1, ctx, cache)):
+            h = self.norm1.apply(x, pending, act_dtype=stream.act_dtype)
+            pending = self.mixer.forward(h, ctx, cache)
+        if not (low and pending is None and self.feed_forward.forward_into_residual(x, self.norm2, ctx)):
+            h = self.norm2.apply(x, pending, act_dtype=stream.act_dtype)
+            pending = self.feed_forward.forward(h, ctx)
+        stream.pending = pending
         stream.act = None
 
 

@@ -44,5 +44,16 @@ class DenseFFN(FeedForward):
         u = ops.linear(h, self.w1, self.b1, self.activation, bias_bf16=self.b1_bf16)
         return Delta(ops.linear(u, self.w2), self.b2)
 
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any) -> bool:
+        """x += ffn(norm(x)) for a step of a few tokens in two kernels: norm + fc1 + bias + activation;
+        fc2 + bias + residual sum."""
+        if norm.kind not in ops.NORM_CODES or not ops.fused_norm_applies(x.shape[0], self.hidden, self.w1):
+            return False
+        if self.inner % 8:
+            return False
+        u = ops.norm_linear(x, norm.kind, norm.gamma, norm.beta, norm.eps, self.w1, self.b1, self.activation)
+        ops.linear_add(u, self.w2, self.b2, x)
+        return True
+
     def param_bytes(self) -> int:
         return (self.w1.numel() + self.w2.numel()) * self.w1.element_size()

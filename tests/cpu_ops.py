@@ -107,6 +107,33 @@ def kernel_status(device):
 SKINNY_MAX_ROWS = 8
 
 
+FUSED_MAX_ROWS = 8
+
+
+def fused_norm_applies(n_rows, k, w):
+    return False        # the CPU runs of the engine take the unfused path
+
+
+def _norm_rows(x, kind, gamma, beta, eps, dtype):
+    out = torch.empty(x.shape, dtype=dtype)
+    add_norm(x, gamma=gamma, beta=beta, eps=eps, kind=kind, out_act=out)
+    return out
+
+
+def norm_linear(x, kind, gamma, beta, eps, w, bias=None, act="none", out_dtype=None):
+    return linear(_norm_rows(x, kind, gamma, beta, eps, w.dtype), w, bias, act, out_dtype or w.dtype)
+
+
+def linear_add(a, w, bias, x):
+    x += linear(a, w, bias, "none", torch.float32)
+
+
+def norm_qkv_linear_to_cache(x, kind, gamma, beta, eps, w, bias, q_out, pool, layer, positions, seq_of_token, slots,
+                             block_table, nh, nkv, d, status, write_kv=True):
+    qkv_linear_to_cache(_norm_rows(x, kind, gamma, beta, eps, w.dtype), w, bias, q_out, pool, layer, positions,
+                        seq_of_token, slots, block_table, nh, nkv, d, status, write_kv)
+
+
 def qkv_linear_to_cache(h, w, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d,
                         status, write_kv=True):
     qkv = linear(h, w)
@@ -172,7 +199,7 @@ def attention_decode_scratch(n_items, nh, d, n_splits):
 
 
 def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_token, slots, block_table, nh,
-                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto", warps=4, status=None):
+                     scale, window=0, n_splits=1, partial=None, fused_merge=True, kernel="auto", warps=4, status=None, start_pos=None):
     idx = items[:n_items].long() if items is not None else torch.arange(n_items)
     tmp = torch.zeros_like(out)
     pos = torch.full_like(positions, -1)
@@ -253,7 +280,7 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
     return res
 
 
-ALL = ["sm_count", "embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
+ALL = ["sm_count", "fused_norm_applies", "norm_linear", "linear_add", "norm_qkv_linear_to_cache", "embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
        "qkv_linear_to_cache", "qkv_to_cache",
        "attention_plain", "attention_decode_scratch", "decode_warps", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]

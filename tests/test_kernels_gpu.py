@@ -231,6 +231,12 @@ def test_attention_decode(shape, window, n_splits, kernel):
                          kernel=kernel, warps=warps)
     close(out[items.long()], ref[items.long()], dtype, "attention_decode", rel=1e-2)
     assert torch.all(out[2] == 7.0), "a token that is not in the item list must not be written"
+    # told which keys earlier steps wrote, the kernel starts copying those before its wait: same result
+    early = torch.full_like(ref, 7.0, device=DEV)
+    ops.attention_decode(q.to(DEV), pool.to(DEV), 1, early, items.to(DEV), len(items), t["pos"].to(DEV),
+                         t["seq"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window, n_splits, partial,
+                         kernel=kernel, warps=warps, start_pos=t["start"].to(DEV))
+    assert torch.equal(early, out)
 
 
 @pytest.mark.parametrize("shape", ATT_SHAPES)
@@ -417,6 +423,94 @@ def test_gemm_skinny(shape):
     one = ops.gemm_skinny(a[n - 1:n].to(DEV).contiguous(), w.to(DEV), b.to(DEV), "none", torch.float32)
     full = ops.gemm_skinny(a.to(DEV), w.to(DEV), b.to(DEV), "none", torch.float32)
     assert torch.equal(one[0], full[n - 1])
+
+
+@pytest.mark.parametrize("shape", [(1, 130, 64), (2, 96, 96), (3, 1000, 544), (5, 2048, 2048), (8, 6144, 2048),
+                                   (8, 512, 4096), (7, 300, 7168), (4, 33, 8192), (8, 777, 1024)])
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm", "none"])
+def test_gemm_skinny_with_the_norm_in_front(shape, kind, monkeypatch):
+    """norm(x) . w^T for a few float rows x in one kernel: every count of rows (clusters of 1, 2, 4, 8 blocks that
+    share the normalised rows through distributed shared memory), widths that need 1, 2, 4 and 8 pieces of a row
+    per thread, feature counts that leave a cluster partly empty, with and without gain and shift.  The
+    reference rounds the normalised rows to bfloat16 where the kernel does."""
+    monkeypatch.setattr(ops, "FUSE_NORM", True)          # the kernel itself (the engine runs norm and product apart)
+    n, m, k = shape
+    x = rnd((n, k), torch.float32, 90) * 3 + 0.7
+    x[0, 1] = 40.0                                       # one large element, as residual streams have
+    w, b = rnd((m, k), torch.bfloat16, 91, 0.1), rnd((m,), torch.float32, 92)
+    gamma, beta = 1 + 0.2 * rnd((k,), torch.float32, 93), 0.3 * rnd((k,), torch.float32, 94)
+    assert ops.fused_norm_applies(n, k, w.to(DEV))
+    for g, be, act in ((gamma, beta, "relu"), (None, None, "none"), (gamma, None, "gelu")):
+        ref = cpu_ops.norm_linear(x, kind, g, be, 1e-5, w, b, act, torch.float32)
+        got = ops.norm_linear(x.to(DEV), kind, g.to(DEV) if g is not None else None,
+                              be.to(DEV) if be is not None else None, 1e-5, w.to(DEV), b.to(DEV), act, torch.float32)
+        # the normalised rows are rounded to bfloat16 in both; a value that lies near the middle between two
+        # bfloat16 numbers may round the other way after float rather than double arithmetic
+        close(got, ref, torch.float32, f"norm_linear {kind} {act}", rel=2e-3)
+    got = ops.norm_linear(x.to(DEV), kind, gamma.to(DEV), beta.to(DEV), 1e-5, w.to(DEV), None, "none")
+    close(got, cpu_ops.norm_linear(x, kind, gamma, beta, 1e-5, w), torch.bfloat16, "norm_linear bf16 out", rel=1e-2)
+    # a row's result does not depend on the other rows of the step, nor on their number
+    full = ops.norm_linear(x.to(DEV), kind, gamma.to(DEV), beta.to(DEV), 1e-5, w.to(DEV), b.to(DEV), "none", torch.float32)
+    one = ops.norm_linear(x[n - 1:n].to(DEV).contiguous(), kind, gamma.to(DEV), beta.to(DEV), 1e-5, w.to(DEV),
+                          b.to(DEV), "none", torch.float32)
+    assert torch.equal(one[0], full[n - 1])
+    # and equals the two kernels it replaces, bit for bit up to the order of the norm's sums
+    h = torch.empty((n, k), dtype=torch.bfloat16, device=DEV)
+    ops.add_norm(x.to(DEV), gamma=gamma.to(DEV), beta=beta.to(DEV), eps=1e-5, kind=kind, out_act=h)
+    two = ops.gemm_skinny(h, w.to(DEV), b.to(DEV), "none", torch.float32)
+    close(full, two, torch.float32, "fused against norm kernel + product", rel=2e-3)
+
+
+def test_fused_norm_is_refused_where_it_does_not_apply(monkeypatch):
+    monkeypatch.setattr(ops, "FUSE_NORM", True)
+    w = rnd((64, 80), torch.bfloat16, 95).to(DEV)
+    assert not ops.fused_norm_applies(9, 64, w) and not ops.fused_norm_applies(4, 80, w)
+    assert not ops.fused_norm_applies(4, 16384, w) and not ops.fused_norm_applies(4, 64, w.float())
+    with pytest.raises(ops.KernelError):
+        ops.norm_linear(rnd((4, 80), torch.float32, 96).to(DEV), "layernorm", None, None, 1e-5, w)
+
+
+@pytest.mark.parametrize("shape", [(1, 2048, 2048), (8, 2048, 8192), (3, 130, 64), (6, 1000, 520), (8, 96, 4096)])
+def test_gemm_skinny_with_the_residual_sum_behind(shape):
+    """x += a . w^T + bias in float, in place: with and without slices of k that meet in a cluster."""
+    n, m, k = shape
+    a, w, b = rnd((n, k), torch.bfloat16, 97), rnd((m, k), torch.bfloat16, 98, 0.1), rnd((m,), torch.float32, 99)
+    x = rnd((n, m), torch.float32, 100) * 5
+    for bias in (b, None):
+        got = x.to(DEV).clone()
+        ops.linear_add(a.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, got)
+        ref = x.double() + cpu_ops.linear(a, w, bias, "none", torch.float32).double()
+        close(got, ref, torch.float32, "linear_add", rel=2e-5)
+
+
+@pytest.mark.parametrize("n", [1, 5, 8])
+def test_norm_qkv_product_and_cache_write_in_one_kernel(n, monkeypatch):
+    """The fused first kernel of the attention layer against norm kernel + product + cache write."""
+    monkeypatch.setattr(ops, "FUSE_NORM", True)
+    nh, nkv, d, ps, L = 6, 2, 64, 16, 3
+    k = 384
+    lens = [40 + 17 * i for i in range(n)]
+    pool, bt, slots = make_cache(torch.bfloat16, n, lens, nkv, d, ps, L, 101)
+    x = rnd((n, k), torch.float32, 102) * 2
+    w, b = rnd(((nh + 2 * nkv) * d, k), torch.bfloat16, 103, 0.1), rnd(((nh + 2 * nkv) * d,), torch.float32, 104)
+    gamma, beta = 1 + 0.2 * rnd((k,), torch.float32, 105), 0.3 * rnd((k,), torch.float32, 106)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    pos[n // 2] = -1 if n > 1 else pos[0]                      # a padding token of a fixed-shape step writes nothing
+    seq = torch.arange(n, dtype=torch.int32)
+    status = torch.zeros(1, dtype=torch.int32)
+    ref_pool, ref_q = pool.clone(), torch.zeros(n, nh * d, dtype=torch.bfloat16)
+    cpu_ops.norm_qkv_linear_to_cache(x, "layernorm", gamma, beta, 1e-5, w, b, ref_q, ref_pool, 1, pos, seq, slots, bt,
+                                     nh, nkv, d, status)
+    got_pool, got_q = pool.to(DEV), torch.zeros(n, nh * d, dtype=torch.bfloat16, device=DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.norm_qkv_linear_to_cache(x.to(DEV), "layernorm", gamma.to(DEV), beta.to(DEV), 1e-5, w.to(DEV), b.to(DEV), got_q,
+                                 got_pool, 1, pos.to(DEV), seq.to(DEV), slots.to(DEV), bt.to(DEV), nh, nkv, d, st)
+    assert int(st.item()) == 0
+    live = pos >= 0
+    close(got_q[live.to(DEV)], ref_q[live], torch.bfloat16, "fused q", rel=1.2e-2)
+    close(got_pool, ref_pool, torch.bfloat16, "fused cache write", rel=1.2e-2)
+    changed = (got_pool.cpu() != pool).any(dim=-1).sum().item()
+    assert changed == int(live.sum()) * 2 * nkv, "one key row and one value row per live token and kv head, nothing else"
 
 
 @pytest.mark.parametrize("shape", [(9, 130, 64), (16, 2048, 2048), (33, 777, 520), (48, 300, 8192), (64, 6144, 2048),
