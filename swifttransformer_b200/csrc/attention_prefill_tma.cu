@@ -477,43 +477,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     }
 }
 
-// ---- host side: the pool's tensor map (encoded once per pool and geometry) ---------------------------
-struct TmMapKey {
-    const void* pool;
-    long long rows;
-    int page_size, d;
-};
-struct TmMapEntry {
-    TmMapKey key;
-    CUtensorMap map;
-};
-static std::mutex tm_mutex;
-static TmMapEntry tm_maps[16];
-static int tm_n_maps = 0, tm_next = 0;
-
-// rows: pages x layers x 2 x kv_heads, each [page_size][d] bfloat16
-static int tm_pool_map(const void* pool, long long rows, int page_size, int d, CUtensorMap* out) {
-    std::lock_guard<std::mutex> lock(tm_mutex);
-    for (int i = 0; i < tm_n_maps; ++i) {
-        const TmMapKey& k = tm_maps[i].key;
-        if (k.pool == pool && k.rows == rows && k.page_size == page_size && k.d == d) {
-            *out = tm_maps[i].map;
-            return 0;
-        }
-    }
-    const unsigned long long dims[3] = {(unsigned long long)d, (unsigned long long)page_size, (unsigned long long)rows};
-    const unsigned box[3] = {64, (unsigned)page_size, 1};
-    CUtensorMap m;
-    if (st_tma_encode_bf16(&m, pool, 3, dims, box)) return ST_ERR_BAD_ARG;
-    TmMapEntry& e = tm_maps[tm_next];
-    e.key = TmMapKey{pool, rows, page_size, d};
-    e.map = m;
-    tm_next = (tm_next + 1) % 16;
-    if (tm_n_maps < 16) ++tm_n_maps;
-    *out = m;
-    return 0;
-}
-
+// ---- host side ------------------------------------------------------------------------------------------
 static size_t tm_smem_bytes(int db, int nwg) {
     // Q, then per warpgroup two key and two value tiles and P; a kilobyte of slack to reach a 1024-byte boundary
     return (size_t)db * TC_BM * 128 + nwg * ((size_t)4 * db * TC_BN * 128 + TC_BM * 128) + 1024;
@@ -578,7 +542,7 @@ ST_EXPORT int st_attention_prefill_tma(const void* q, const void* pool, long lon
     if (rows >= (1ll << 31)) return ST_ERR_TOO_LARGE;          // TMA coordinates are 32-bit
     if ((reinterpret_cast<uintptr_t>(pool) & 15) != 0) return ST_ERR_BAD_ARG;
     CUtensorMap map;
-    int r = tm_pool_map(pool, rows, page_size, d, &map);
+    int r = st_tma_pool_map(pool, rows, page_size, d, &map);
     if (r) return r;
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 64 && tm_wg_d64 == 3 && tm_three_warpgroups_fit())

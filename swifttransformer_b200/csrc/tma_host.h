@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 typedef CUresult (*st_tma_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -44,4 +46,38 @@ static inline int st_tma_encode_bf16(CUtensorMap* out, const void* base, int ran
                            b, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+// The tensor map of a paged key/value pool for the attention kernels fed by TMA: a rank-3 tensor
+// [page x layer x (K|V) x kv_head][position in page][head_dim] with boxes of one page of one head and 64 of its
+// elements.  Encoded once per pool and geometry and kept in a small table (per translation unit).
+// rows: pages x layers x 2 x kv_heads.  Returns 0 or -4 (ST_ERR_BAD_ARG).
+static inline int st_tma_pool_map(const void* pool, long long rows, int page_size, int d, CUtensorMap* out) {
+    struct Entry {
+        const void* pool;
+        long long rows;
+        int page_size, d;
+        CUtensorMap map;
+    };
+    static std::mutex mutex;
+    static Entry table[16];
+    static int n = 0, next = 0;
+    std::lock_guard<std::mutex> lock(mutex);
+    for (int i = 0; i < n; ++i) {
+        const Entry& e = table[i];
+        if (e.pool == pool && e.rows == rows && e.page_size == page_size && e.d == d) {
+            *out = e.map;
+            return 0;
+        }
+    }
+    const unsigned long long dims[3] = {(unsigned long long)d, (unsigned long long)page_size, (unsigned long long)rows};
+    const unsigned box[3] = {64, (unsigned)page_size, 1};
+    CUtensorMap m;
+    if (st_tma_encode_bf16(&m, pool, 3, dims, box)) return -4;
+    Entry& e = table[next];
+    e.pool = pool; e.rows = rows; e.page_size = page_size; e.d = d; e.map = m;
+    next = (next + 1) % 16;
+    if (n < 16) ++n;
+    *out = m;
+    return 0;
 }

@@ -514,7 +514,8 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
     """bfloat16 tensor-core paged attention over tiles of 128 query tokens; tiles: int32 [n_tiles, 2] =
     (request index in the step, offset of the tile among the request's new tokens).
 
-    kernel: "tma" = the tcgen05 kernel fed by TMA (head sizes 64 and 128, pages of 8 to 64 positions;
+    kernel: "tmap" = the persistent tcgen05 kernel fed by TMA (head size 64, pages of 8 to 64 positions: one block
+    per SM walks through the (tile, head) pairs), "tma" = the same with one block per pair (head sizes 64 and 128;
     "tma3" = the same with three softmax warpgroups per block instead of two, at head size 64 only),
     "tc" = the tcgen05 kernel fed by asynchronous copies (head sizes up to 128), "mma" = the mma.sync
     kernel (up to 256), "auto" = the first of these that applies.  ``status`` receives 3 if a tcgen05
@@ -523,10 +524,19 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill is a bfloat16 kernel")
     if kernel == "auto":
-        if lib().st_attention_prefill_tma_applies(d, page_size):
+        if lib().st_attention_prefill_tmap_applies(d, page_size):
+            kernel = "tmap"
+        elif lib().st_attention_prefill_tma_applies(d, page_size):
             kernel = "tma"
         else:
             kernel = "tc" if d <= 128 else "mma"
+    if kernel == "tmap":
+        st = status if status is not None else _tc_status_word(q.device)
+        _check(lib().st_attention_prefill_tmap(_p(q), _p(pool), ctypes.c_longlong(n_pages), _p(out), _p(tiles),
+                                               n_tiles, _p(q_start), _p(start_pos), _p(slots), _p(block_table),
+                                               block_table.shape[1], n_layers, layer, nh, nkv, d, page_size,
+                                               _f(scale), window, _p(st), _stream()), "attention_prefill_tmap")
+        return out
     if kernel in ("tma", "tma3"):
         st = status if status is not None else _tc_status_word(q.device)
         lib().st_attention_prefill_tma_warpgroups(3 if kernel == "tma3" else 2)

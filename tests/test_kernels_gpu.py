@@ -241,11 +241,13 @@ def test_attention_decode(shape, window, n_splits, kernel):
 
 @pytest.mark.parametrize("shape", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
-@pytest.mark.parametrize("kernel", ["tma", "tma3", "tc", "mma"])
+@pytest.mark.parametrize("kernel", ["tmap", "tma", "tma3", "tc", "mma"])
 def test_attention_prefill(shape, window, kernel):
     nh, nkv, d, ps = shape
     if kernel == "tc" and d > 128:
         pytest.skip("the tcgen05 kernel takes head sizes up to 128")
+    if kernel == "tmap" and not (d == 64 and ps in (8, 16, 32, 64)):
+        pytest.skip("the persistent TMA-fed kernel takes head size 64 and pages of 8 to 64 positions")
     if kernel in ("tma", "tma3") and not (d in (64, 128) and ps in (8, 16, 32, 64)):
         pytest.skip("the TMA-fed kernel takes head sizes 64 and 128 and pages of 8 to 64 positions")
     if kernel == "tma3" and d != 64:
@@ -270,6 +272,43 @@ def test_attention_prefill(shape, window, kernel):
     assert torch.all(out[~keep] == 7.0)
 
 
+@pytest.mark.parametrize("window", [0, 200])
+@pytest.mark.parametrize("ps", [16, 64])
+def test_attention_prefill_persistent_kernel_walks_through_many_tiles(ps, window):
+    """More (tile, head) pairs than the GPU has SMs, so that every block of the persistent kernel goes through
+    several pairs: long and short tiles, a request whose keys lie mostly in the cache, tiles of a single key
+    tile (the second warpgroup has none), padding tiles between real ones."""
+    nh, nkv, d = 6, 3, 64
+    dtype = torch.bfloat16
+    lens, new = [2048, 700, 129, 1500, 40], [2048, 300, 129, 1000, 40]
+    pool, bt, slots, t, q, scale, ref = attention_case(dtype, nh, nkv, d, ps, lens, new, 55, window)
+    tr = ops.attention_prefill_tile_rows()
+    tiles = []
+    for i, m in enumerate(new):
+        tiles += [(lens[i] - m + min(off + tr, m), i, off) for off in range(0, m, tr)]
+    tiles.sort(reverse=True)                          # the longest key range first, as the engine lists them
+    flat = []
+    for j, (_, i, off) in enumerate(tiles):
+        flat += [i, off]
+        if j % 5 == 2:
+            flat += [0, 1 << 24]                      # a padding tile: an offset past any request's tokens
+    n_tiles = len(flat) // 2
+    assert n_tiles * nh > 148 * 1.2
+    out = torch.full_like(ref, 7.0, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attention_prefill(q.to(DEV), pool.to(DEV), 1, out, torch.tensor(flat, dtype=torch.int32, device=DEV), n_tiles,
+                          t["q_start"].to(DEV), t["start"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window,
+                          status=status, kernel="tmap")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    close(out, ref, dtype, "persistent attention_prefill", rel=1.5e-2)
+    same = torch.full_like(ref, 7.0, device=DEV)
+    ops.attention_prefill(q.to(DEV), pool.to(DEV), 1, same, torch.tensor(flat, dtype=torch.int32, device=DEV), n_tiles,
+                          t["q_start"].to(DEV), t["start"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window,
+                          status=status, kernel="tma")
+    assert torch.equal(out, same), "the persistent kernel does the arithmetic of the kernel with one block per pair"
+
+
 def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
     """A page missing from a request's block table (-1) must not be read through: every attention kernel
     treats the keys of that page as absent (zeros or dropped), leaves the other requests' results exact,
@@ -289,7 +328,7 @@ def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
     tr = ops.attention_prefill_tile_rows()
     tiles = torch.tensor([v for i in (0, 2) for off in range(0, new[i], tr) for v in (i, off)], dtype=torch.int32).to(DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for kernel in ("tma", "tma3", "tc", "mma"):
+    for kernel in ("tmap", "tma", "tma3", "tc", "mma"):
         out = torch.zeros_like(ref, device=DEV)
         ops.attention_prefill(dev["q"], dev["pool"], 1, out, tiles, tiles.numel() // 2, dev["q_start"], dev["start"],
                               dev["slots"], dev["bt"], nh, scale, 0, status=status, kernel=kernel)
@@ -299,7 +338,7 @@ def test_attention_kernels_drop_keys_behind_a_hole_in_the_block_table():
         close(out[keep], ref[keep], dtype, f"prefill {kernel} beside a hole", rel=1.5e-2)
     # without a hole the word stays 0
     clean = bt.to(DEV)
-    for kernel in ("tma", "tc", "mma"):
+    for kernel in ("tmap", "tma", "tc", "mma"):
         out = torch.zeros_like(ref, device=DEV)
         ops.attention_prefill(dev["q"], dev["pool"], 1, out, tiles, tiles.numel() // 2, dev["q_start"], dev["start"],
                               dev["slots"], clean, nh, scale, 0, status=status, kernel=kernel)
