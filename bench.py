@@ -106,6 +106,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--no-big", action="store_true", help="skip the OPT-6.7B points (13 GB of random weights)")
     ap.add_argument("--launch-floor", action="store_true",
                     help="with --only decode: same number of layers and kernels, but hidden size 64, so that the "
                          "step time is what the chain of dependent launches costs by itself")
@@ -320,6 +321,18 @@ def main():
             r = decode_device(b, min(K, 64), W)
             pts[f"decode_b{b}"] = round(r["tok_s"], 1)
             pts[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        if args.model_name == "opt_1.3b" and not args.layers and not args.launch_floor and not args.no_big:
+            # the same two measurements at the OPT-6.7B sizes (head size 128: another set of attention kernels)
+            del model
+            torch.cuda.empty_cache()
+            cfg = opt_preset("opt_6.7b")
+            model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            r = decode_device(8, min(K, 32), W)
+            pts["opt6.7b_decode_b8"] = round(r["tok_s"], 1)
+            pts["opt6.7b_decode_b8_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            pf = prefill(2048)
+            pts["opt6.7b_prefill_2048_ms"] = round(pf["ms"], 3)
+            pts["opt6.7b_prefill_frac"] = round(pf["frac"], 4)
         out["points"] = pts
     print(json.dumps(out))
     return 0
