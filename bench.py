@@ -110,11 +110,15 @@ def main():
     ap.add_argument("--launch-floor", action="store_true",
                     help="with --only decode: same number of layers and kernels, but hidden size 64, so that the "
                          "step time is what the chain of dependent launches costs by itself")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed"],
+    ap.add_argument("--rows", type=int, nargs="*", default=[16, 32, 64], help="with --only products: token counts")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "products"],
                     help="run just the device-timed decode loop or just the prefill (for profiling small cases), or "
                          "the mixed continuous batch: --requests requests with prompt lengths uniform in [16,1536] "
                          "and output lengths uniform in [16,512], prompt portions of 512 tokens beside decoded "
-                         "tokens, through LLMEngine.generate (host token ids in and out, wall clock)")
+                         "tokens, through LLMEngine.generate (host token ids in and out, wall clock); or products: "
+                         "the model's five matrix products alone at --rows tokens, each 16 times in a recorded graph "
+                         "with weights taken in turn from copies larger than L2, by the library, the tcgen05 "
+                         "weight-streaming kernel and (up to 32 rows) the mma.sync one")
     ap.add_argument("--requests", type=int, default=64, help="requests of the mixed continuous batch")
     ap.add_argument("--set", action="append", default=[], metavar="MODULE.NAME=VALUE",
                     help="set a tuning constant of the package before the run, e.g. ops.SKINNY_MAX_ROWS=32 or "
@@ -133,6 +137,7 @@ def main():
         args.warmup = 3
 
     import dataclasses
+    import gc
     import numpy as np
     import torch
     from swifttransformer_b200 import ops
@@ -166,6 +171,10 @@ def main():
     rng = np.random.default_rng(0)
 
     def new_engine(batch):
+        # an engine that went out of scope lies in a reference cycle with its recorded steps: collect it, and
+        # hand its pool back to the device, before the next one asks for its own
+        gc.collect()
+        torch.cuda.empty_cache()
         pages = batch * ((P + gen_room + 15) // 16 + 1) + (2048 // 16 + 2)
         return LLMEngine(model, page_size=16, num_pages=pages, max_batch_tokens=max(2048, batch * P if batch * P <= 8192 else 4096),
                          chunk_size=2048, max_num_seqs=max(batch, 1))
@@ -279,6 +288,44 @@ def main():
         eng.runner.check_status()
         return result
 
+    if args.only == "products":
+        H, F, V = cfg.hidden_size, cfg.ffn_dim, cfg.vocab_size
+
+        def graph_us(fn, calls=16, reps=20):
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for i in range(3):
+                    fn(i)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for i in range(calls):
+                        fn(i)
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps / calls * 1e3
+        for m in args.rows:
+            for n, k, name in ((3 * H, H, "qkv"), (H, H, "out"), (F, H, "fc1"), (H, F, "fc2"), (V, H, "head")):
+                copies = max(4, int(600e6 / (n * k * 2)))
+                ws = [torch.randn(n, k, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+                x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+                us = {"library": graph_us(lambda i: torch.mm(x, ws[i % copies].t()))}
+                if m <= 128:
+                    us["stream_tc"] = graph_us(lambda i: ops.gemm_stream_tc(x, ws[i % copies]))
+                if m <= 32:
+                    us["skinny"] = graph_us(lambda i: ops.gemm_skinny(x, ws[i % copies]))
+                print(json.dumps({"only": "products", "rows": m, "product": name, "n": n, "k": k,
+                                  "us": {a: round(b, 1) for a, b in us.items()},
+                                  "tb_s": {a: round(n * k * 2 / b / 1e6, 2) for a, b in us.items()}}))
+                del ws
+        return 0
     if args.only == "decode":
         r = decode_device(args.batch, K, W)
         print(json.dumps({"only": "decode", "ms_per_step": round(r["ms"], 4), "tok_s": round(r["tok_s"], 1)}))

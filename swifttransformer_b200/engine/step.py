@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import dataclasses
 import gc
+import weakref
 from math import gcd
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -123,7 +124,9 @@ class _RecordedStep:
 
     def __init__(self, runner: "ModelRunner", n_cap: int, b_cap: int, w_cap: int, plan_keys: Dict[str, Tuple],
                  decode: bool = False):
-        self.runner = runner
+        # weak references both ways (the runner holds its recordings, a context its scratch owner): a runner
+        # that goes out of scope is freed at once, pool and graphs with it, without waiting for the collector
+        self.runner = weakref.proxy(runner)
         self.n_cap, self.b_cap, self.w_cap, self.decode = n_cap, b_cap, w_cap, decode
         self._scratch_buf: Optional[torch.Tensor] = None
         self._frozen = False
@@ -133,7 +136,7 @@ class _RecordedStep:
         self.last_used = 0               # the runner's step count when this recording last ran
         self.lay = lay = runner._layout(n_cap, b_cap, w_cap)
         self.staging = _Staging(lay["total"], runner.device)
-        self.ctx = runner._context_over(self.staging.dev, lay, n_cap, b_cap, w_cap, plan_keys, self)
+        self.ctx = runner._context_over(self.staging.dev, lay, n_cap, b_cap, w_cap, plan_keys, weakref.proxy(self))
         self.token_from = self._view("token_from")
         if decode:
             assert n_cap == b_cap == w_cap

@@ -503,6 +503,10 @@ def decode_warps(n_items: int, nkv: int, d: int, n_splits: int, max_kv: int) -> 
     return 8 if (d <= 64 and n_items * nkv * n_splits <= 2 * sm_count() and max_kv >= 256) else 4
 
 
+# "auto", or the name of one prompt-attention kernel for every call that says "auto" (measurements)
+PREFILL_KERNEL = "auto"
+
+
 def attention_prefill_tile_rows() -> int:
     return int(lib().st_attention_prefill_tile_rows())
 
@@ -523,6 +527,8 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
     n_pages, n_layers, _, nkv, page_size, d = pool.shape
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill is a bfloat16 kernel")
+    if kernel == "auto":
+        kernel = PREFILL_KERNEL
     if kernel == "auto":
         if lib().st_attention_prefill_tmap_applies(d, page_size):
             kernel = "tmap"

@@ -31,6 +31,9 @@ SHORT_PORTION = 16
 # of such spans the longest single-token request needs, so the cut follows the real lengths, not the
 # longest possible one.
 KEYS_PER_BLOCK = 768
+# (token, head) pairs from which a launch of the single-token attention fills the device by itself: the key
+# ranges are then never cut (for head size 64; in proportion for others)
+FULL_LAUNCH_PAIRS = 250
 
 
 def choose_splits(n_items: int, nh: int, max_kv: int, sms: int, head_dim: int = 64) -> int:
@@ -39,7 +42,7 @@ def choose_splits(n_items: int, nh: int, max_kv: int, sms: int, head_dim: int = 
     for head sizes up to 64 and at least 128 keys per part beyond, within two blocks per SM.  The
     measurements behind these rules are in profiles/decode_attention_splits.md."""
     blocks = max(1, n_items * nh)
-    if blocks * 64 >= 250 * head_dim:
+    if blocks * 64 >= FULL_LAUNCH_PAIRS * head_dim:
         return 1
     room = max(1, (2 * sms + blocks - 1) // blocks)
     if head_dim <= 64:

@@ -155,3 +155,24 @@ def test_bfloat16_engine_against_reference_operations_with_bfloat16_storage(mode
         err = np.abs(got[rid] - ref[rid])
         assert err.max() < 1.5e-2 * scale, (rid, int(err.max(axis=1).argmax()), float(err.max() / scale))
         assert err.mean() < 1.5e-3 * scale, (rid, float(err.mean() / scale))
+
+
+def test_an_engine_that_goes_out_of_scope_gives_its_memory_back_at_once(model_dirs):
+    """Recorded steps and their runner refer to one another weakly: dropping the last reference to an engine frees
+    its pool and its graphs without a run of the garbage collector."""
+    import gc
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.sampling import SamplingParams
+    gc.collect()
+    gc.disable()
+    try:
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        eng = LLMEngine(model_dirs["c"], dtype="bfloat16", page_size=32, num_pages=4000, max_num_seqs=4)
+        eng.generate([helpers.random_tokens(777, 40, 1), helpers.random_tokens(777, 9, 2)], SamplingParams(max_new_tokens=5))
+        assert eng.runner.graph_steps > 0 and torch.cuda.memory_allocated() > before + 50e6
+        del eng
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() < before + 1e6
+    finally:
+        gc.enable()
