@@ -30,7 +30,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
                          const int* __restrict__ tiles, const int* __restrict__ q_start,
                          const int* __restrict__ start_pos, const int* __restrict__ slots,
                          const int* __restrict__ block_table, int max_pages, int n_layers, int layer,
-                         int nh, int nkv, int d, int page_size, float scale_log2, int window,
+                         int nh, int nkv, int d, int page_size, float scale_log2, int window, int q_stride,
                          int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
@@ -83,7 +83,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
         constexpr int Q_TPR = PF_THREADS / PF_BM;
         const int r = threadIdx.x / Q_TPR;
         const bool ok = r < n_rows;
-        const bf16* src = q + ((size_t)(tok0 + (ok ? r : 0)) * nh + h) * d;
+        const bf16* src = q + (size_t)(tok0 + (ok ? r : 0)) * q_stride + h * d;
         for (int c = threadIdx.x % Q_TPR; c < chunks; c += Q_TPR) cp_async16(tile_ptr<DMAX>(sQ, r, c), src + c * 8, ok);
     }
     load_kv(kt_begin, 0);
@@ -235,7 +235,7 @@ template <int DMAX>
 static int launch_prefill(const void* q, const void* pool, void* out, const int* tiles, int n_tiles,
                           const int* q_start, const int* start_pos, const int* slots, const int* block_table,
                           int max_pages, int n_layers, int layer, int nh, int nkv, int d, int page_size,
-                          float scale, int window, int* status, cudaStream_t s) {
+                          float scale, int window, int q_stride, int* status, cudaStream_t s) {
     const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * DMAX * sizeof(bf16);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
@@ -247,7 +247,7 @@ static int launch_prefill(const void* q, const void* pool, void* out, const int*
     dim3 grid(nh, n_tiles);
     attention_prefill_kernel<DMAX><<<grid, PF_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,
         tiles, q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size,
-        scale * LOG2E, window, status);
+        scale * LOG2E, window, q_stride, status);
     return st_launch_status();
 }
 
@@ -256,18 +256,19 @@ ST_EXPORT int st_attention_prefill_tile_rows() { return PF_BM; }
 ST_EXPORT int st_attention_prefill(const void* q, const void* pool, void* out, const int* tiles, int n_tiles,
                                    const int* q_start, const int* start_pos, const int* slots,
                                    const int* block_table, int max_pages, int n_layers, int layer, int nh, int nkv,
-                                   int d, int page_size, float scale, int window, int* status, void* stream) {
+                                   int d, int page_size, float scale, int window, int q_stride, int* status, void* stream) {
     if (n_tiles <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_tiles > 65535) return ST_ERR_BAD_ARG;
     if (d <= 0 || d % 16) return ST_ERR_BAD_SIZE;
     if (d > 256) return ST_ERR_TOO_LARGE;
+    if (q_stride <= 0) q_stride = nh * d;      // a dense [tokens, nh * d] query tensor
     cudaStream_t s = (cudaStream_t)stream;
     if (d <= 64)
         return launch_prefill<64>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                  n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
+                                  n_layers, layer, nh, nkv, d, page_size, scale, window, q_stride, status, s);
     if (d <= 128)
         return launch_prefill<128>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                   n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
+                                   n_layers, layer, nh, nkv, d, page_size, scale, window, q_stride, status, s);
     return launch_prefill<256>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                               n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
+                               n_layers, layer, nh, nkv, d, page_size, scale, window, q_stride, status, s);
 }

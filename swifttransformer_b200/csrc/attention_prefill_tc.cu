@@ -48,7 +48,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             const int* __restrict__ tiles, const int* __restrict__ q_start,
                             const int* __restrict__ start_pos, const int* __restrict__ slots,
                             const int* __restrict__ block_table, int max_pages, int n_layers, int layer,
-                            int nh, int nkv, int d, int page_size, float scale_log2, int window, int* status) {
+                            int nh, int nkv, int d, int page_size, float scale_log2, int window, int q_stride, int* status) {
     extern __shared__ unsigned char tc_raw[];
     constexpr int SETS = TC_SETS;
     __shared__ __align__(8) unsigned long long s_mbar[2 * SETS];
@@ -133,7 +133,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     };
     if (active) {   // the tile's queries: two threads per row (rows past the portion's end are zero)
         const bool ok = row < n_rows;
-        const bf16* src = q + ((size_t)(tok0 + (ok ? row : 0)) * nh + h) * d;
+        const bf16* src = q + (size_t)(tok0 + (ok ? row : 0)) * q_stride + h * d;
         for (int c = wg; c < chunks; c += 2) tc_cp16(tile_addr(sQ, Q_BLK, row, c), src + c * 8, ok);
     }
     // One key and one value buffer per warpgroup.  A buffer is refilled at the top of the round at whose
@@ -351,7 +351,7 @@ template <int DB>
 static int launch_prefill_tc(const void* q, const void* pool, void* out, const int* tiles, int n_tiles,
                              const int* q_start, const int* start_pos, const int* slots, const int* block_table,
                              int max_pages, int n_layers, int layer, int nh, int nkv, int d, int page_size,
-                             float scale, int window, int* status, cudaStream_t s) {
+                             float scale, int window, int q_stride, int* status, cudaStream_t s) {
     const size_t smem = tc_smem_bytes(DB);
     static bool configured = false;
     if (!configured) {
@@ -369,7 +369,7 @@ static int launch_prefill_tc(const void* q, const void* pool, void* out, const i
     dim3 grid((nh + SETS - 1) / SETS, n_tiles);
     attention_prefill_tc_kernel<DB><<<grid, SETS * TC_SET_THREADS, smem, s>>>((const bf16*)q, (const bf16*)pool, (bf16*)out,
         tiles, q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size,
-        scale * TC_LOG2E, window, status);
+        scale * TC_LOG2E, window, q_stride, status);
     return st_launch_status();
 }
 
@@ -396,16 +396,17 @@ ST_EXPORT int st_attention_prefill_tc_blocks_per_sm(int db) {
 ST_EXPORT int st_attention_prefill_tc(const void* q, const void* pool, void* out, const int* tiles, int n_tiles,
                                       const int* q_start, const int* start_pos, const int* slots,
                                       const int* block_table, int max_pages, int n_layers, int layer, int nh,
-                                      int nkv, int d, int page_size, float scale, int window, int* status,
+                                      int nkv, int d, int page_size, float scale, int window, int q_stride, int* status,
                                       void* stream) {
     if (n_tiles <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_tiles > 65535 || !status) return ST_ERR_BAD_ARG;
     if (d <= 0 || d % 16) return ST_ERR_BAD_SIZE;
     if (d > 128) return ST_ERR_TOO_LARGE;
+    if (q_stride <= 0) q_stride = nh * d;      // a dense [tokens, nh * d] query tensor
     cudaStream_t s = (cudaStream_t)stream;
     if (d <= 64)
         return launch_prefill_tc<1>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                    n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
+                                    n_layers, layer, nh, nkv, d, page_size, scale, window, q_stride, status, s);
     return launch_prefill_tc<2>(q, pool, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                n_layers, layer, nh, nkv, d, page_size, scale, window, status, s);
+                                n_layers, layer, nh, nkv, d, page_size, scale, window, q_stride, status, s);
 }

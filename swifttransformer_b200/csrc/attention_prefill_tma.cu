@@ -87,7 +87,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                              bf16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ q_start,
                              const int* __restrict__ start_pos, const int* __restrict__ slots,
                              const int* __restrict__ block_table, int max_pages, int n_layers, int layer,
-                             int nh, int nkv, int page_size, float scale_log2, int window, int* status) {
+                             int nh, int nkv, int page_size, float scale_log2, int window, int q_stride, int* status) {
     extern __shared__ unsigned char tm_raw[];
     // per warpgroup: S done, O done, then "landed" for the buffers K0, K1, V0, V1, then "free" for the same four
     __shared__ __align__(8) unsigned long long s_mbar[NWG][10];
@@ -158,7 +158,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     };
     if (!issuer) {   // the tile's queries: NWG threads per row (rows past the portion's end are zero)
         const bool ok = row < n_rows;
-        const bf16* src = q + ((size_t)(tok0 + (ok ? row : 0)) * nh + h) * d;
+        const bf16* src = q + (size_t)(tok0 + (ok ? row : 0)) * q_stride + h * d;
         for (int c = wg; c < d / 8; c += NWG) tc_cp16(tile_addr(sQ, Q_BLK, row, c), src + c * 8, ok);
         tc_cp_commit();
         tc_cp_wait<0>();
@@ -495,7 +495,7 @@ template <int DB, int NWG>
 static int launch_prefill_tma(const CUtensorMap& map, const void* q, void* out, const int* tiles, int n_tiles,
                               const int* q_start, const int* start_pos, const int* slots, const int* block_table,
                               int max_pages, int n_layers, int layer, int nh, int nkv, int page_size, float scale,
-                              int window, int* status, cudaStream_t s) {
+                              int window, int q_stride, int* status, cudaStream_t s) {
     const size_t smem = tm_smem_bytes(DB, NWG);
     static bool configured = false;
     if (!configured) {
@@ -506,7 +506,7 @@ static int launch_prefill_tma(const CUtensorMap& map, const void* q, void* out, 
     }
     dim3 grid(nh, n_tiles);
     attention_prefill_tma_kernel<DB, NWG><<<grid, TM_THREADS(NWG), smem, s>>>(map, (const bf16*)q, (bf16*)out, tiles,
-        q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, page_size, scale * TC_LOG2E, window,
+        q_start, start_pos, slots, block_table, max_pages, n_layers, layer, nh, nkv, page_size, scale * TC_LOG2E, window, q_stride,
         status);
     return st_launch_status();
 }
@@ -533,7 +533,7 @@ ST_EXPORT int st_attention_prefill_tma_applies(int d, int page_size) {
 ST_EXPORT int st_attention_prefill_tma(const void* q, const void* pool, long long n_pages, void* out, const int* tiles,
                                        int n_tiles, const int* q_start, const int* start_pos, const int* slots,
                                        const int* block_table, int max_pages, int n_layers, int layer, int nh,
-                                       int nkv, int d, int page_size, float scale, int window, int* status,
+                                       int nkv, int d, int page_size, float scale, int window, int q_stride, int* status,
                                        void* stream) {
     if (n_tiles <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || n_tiles > 65535 || n_pages <= 0 || !status) return ST_ERR_BAD_ARG;
@@ -544,13 +544,14 @@ ST_EXPORT int st_attention_prefill_tma(const void* q, const void* pool, long lon
     CUtensorMap map;
     int r = st_tma_pool_map(pool, rows, page_size, d, &map);
     if (r) return r;
+    if (q_stride <= 0) q_stride = nh * d;      // a dense [tokens, nh * d] query tensor
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 64 && tm_wg_d64 == 3 && tm_three_warpgroups_fit())
         return launch_prefill_tma<1, 3>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                        n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+                                        n_layers, layer, nh, nkv, page_size, scale, window, q_stride, status, s);
     if (d == 64)
         return launch_prefill_tma<1, 2>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                        n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+                                        n_layers, layer, nh, nkv, page_size, scale, window, q_stride, status, s);
     return launch_prefill_tma<2, 2>(map, q, out, tiles, n_tiles, q_start, start_pos, slots, block_table, max_pages,
-                                    n_layers, layer, nh, nkv, page_size, scale, window, status, s);
+                                    n_layers, layer, nh, nkv, page_size, scale, window, q_stride, status, s);
 }

@@ -87,7 +87,7 @@ struct TpWork {
     const int* start_pos;
     const int* slots;
     const int* block_table;
-    int max_pages, n_tiles, nh, nkv, window;
+    int max_pages, n_tiles, nh, nkv, window, q_stride;
 };
 // The next pair of this block at or after round `r` (advanced past it), or false.  Round r deals pairs
 // r G .. r G + G - 1 to the G blocks, forwards in even rounds, backwards in odd ones; a padding tile of a
@@ -294,7 +294,7 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
         // the portion's end are zero
         auto load_q = [&](const TpPair& p, int buf) {
             const bool ok = row < p.n_rows;
-            const bf16* src = q + ((size_t)(p.tok0 + (ok ? row : 0)) * work.nh + p.h) * d;
+            const bf16* src = q + (size_t)(p.tok0 + (ok ? row : 0)) * work.q_stride + p.h * d;
             for (int c = wg; c < d / 8; c += 2) tc_cp16(tile_addr(sQ + buf * TP_Q_BYTES, row, c), src + c * 8, ok);
         };
         TpPair nxt;
@@ -472,12 +472,13 @@ ST_EXPORT int st_attention_prefill_tmap_applies(int d, int page_size) {
     return d == TP_D && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
 
-// Same arguments as st_attention_prefill_tma.  `status` is set to 3 if a wait expired, to 1 if a key range
+// Same arguments as st_attention_prefill_tma (q_stride: elements between the query rows of consecutive tokens;
+// 0: nh * d, a dense [tokens, nh * d] tensor).  `status` is set to 3 if a wait expired, to 1 if a key range
 // crosses a hole in a block table.
 ST_EXPORT int st_attention_prefill_tmap(const void* q, const void* pool, long long n_pages, void* out, const int* tiles,
                                         int n_tiles, const int* q_start, const int* start_pos, const int* slots,
                                         const int* block_table, int max_pages, int n_layers, int layer, int nh,
-                                        int nkv, int d, int page_size, float scale, int window, int* status,
+                                        int nkv, int d, int page_size, float scale, int window, int q_stride, int* status,
                                         void* stream) {
     if (n_tiles <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || n_pages <= 0 || !status) return ST_ERR_BAD_ARG;
@@ -500,6 +501,7 @@ ST_EXPORT int st_attention_prefill_tmap(const void* q, const void* pool, long lo
     work.tiles = tiles; work.q_start = q_start; work.start_pos = start_pos; work.slots = slots;
     work.block_table = block_table; work.max_pages = max_pages; work.n_tiles = n_tiles; work.nh = nh; work.nkv = nkv;
     work.window = window;
+    work.q_stride = q_stride > 0 ? q_stride : nh * d;
     const long long total = (long long)n_tiles * nh;
     const int sms = st_sm_count();
     const int grid = (int)(total < sms ? total : sms);

@@ -70,7 +70,7 @@ __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __re
     if (VEC) {
 #pragma unroll
         for (int j = 0; j < TURN; ++j) {
-            const int v = threadIdx.x + j * blockDim.x;
+            const int v = (q_out ? 0 : qw / W) + threadIdx.x + j * blockDim.x;
             if (v < all) held[j] = *reinterpret_cast<const uint4*>(row + (size_t)v * W);
         }
     }
@@ -83,6 +83,9 @@ __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __re
             page = -1;
         }
     }
+    // q_out null: the queries stay where they are (the attention kernels read them with the row's stride) and
+    // only keys and values move
+    const int first = q_out ? 0 : qw / W;
     const int total = (page >= 0 ? qw + 2 * kw : qw) / W;
     auto target = [&](int e) -> T* {
         if (e < qw) return q_out + (size_t)t * qw + e;
@@ -92,13 +95,13 @@ __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __re
         return pool + (((((size_t)page * n_layers + layer) * 2 + kv) * nkv + head) * page_size + off) * d + dim;
     };
     if (VEC) {
-        for (int base = 0; base < total; base += TURN * blockDim.x) {
+        for (int base = first; base < total; base += TURN * blockDim.x) {
 #pragma unroll
             for (int j = 0; j < TURN; ++j) {
                 const int v = base + threadIdx.x + j * blockDim.x;
                 if (v >= total) continue;
                 const int e = v * W;
-                const uint4 u = base == 0 ? held[j] : *reinterpret_cast<const uint4*>(row + e);
+                const uint4 u = base == first ? held[j] : *reinterpret_cast<const uint4*>(row + e);
                 float f[W];
                 Vec16<T>::unpack(u, f);
                 if (bias) {
@@ -112,7 +115,7 @@ __global__ void qkv_to_cache_kernel(const T* __restrict__ qkv, const float* __re
             }
         }
     } else {
-        for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        for (int e = first + threadIdx.x; e < total; e += blockDim.x) {
             float a = to_f32(row[e]);
             if (bias) a += bias[e];
             *target(e) = from_f32<T>(a);

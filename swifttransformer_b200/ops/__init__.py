@@ -397,11 +397,12 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = 
 
 
 # ------------------------------------------------------------------ attention
-def qkv_to_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, pool: torch.Tensor,
+def qkv_to_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: Optional[torch.Tensor], pool: torch.Tensor,
                  layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor,
                  block_table: torch.Tensor, nh: int, nkv: int, d: int, status: torch.Tensor,
                  write_kv: bool = True) -> None:
-    """q_out = q + bias; pool[page, layer, 0/1, head, pos % page, :] = k/v + bias.
+    """q_out = q + bias; pool[page, layer, 0/1, head, pos % page, :] = k/v + bias.  ``q_out`` None: the queries
+    stay where they are (in ``qkv``), only keys and values move.
 
     pool: [pages, layers, 2, nkv, page_size, d]; block_table: [slots, max_pages] int32."""
     n = qkv.shape[0]
@@ -514,9 +515,11 @@ def attention_prefill_tile_rows() -> int:
 def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,
                       n_tiles: int, q_start: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor,
                       block_table: torch.Tensor, nh: int, scale: float, window: int = 0,
-                      status: Optional[torch.Tensor] = None, kernel: str = "auto") -> torch.Tensor:
+                      status: Optional[torch.Tensor] = None, kernel: str = "auto", q_stride: int = 0) -> torch.Tensor:
     """bfloat16 tensor-core paged attention over tiles of 128 query tokens; tiles: int32 [n_tiles, 2] =
-    (request index in the step, offset of the tile among the request's new tokens).
+    (request index in the step, offset of the tile among the request's new tokens).  ``q_stride``: elements
+    between the query rows of consecutive tokens when ``q`` is part of a wider tensor (the q|k|v product), 0 for
+    a dense [tokens, nh * d] tensor.
 
     kernel: "tmap" = the persistent tcgen05 kernel fed by TMA (head size 64, pages of 8 to 64 positions: one block
     per SM walks through the (tile, head) pairs), "tma" = the same with one block per pair (head sizes 64 and 128;
@@ -541,7 +544,7 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
         _check(lib().st_attention_prefill_tmap(_p(q), _p(pool), ctypes.c_longlong(n_pages), _p(out), _p(tiles),
                                                n_tiles, _p(q_start), _p(start_pos), _p(slots), _p(block_table),
                                                block_table.shape[1], n_layers, layer, nh, nkv, d, page_size,
-                                               _f(scale), window, _p(st), _stream()), "attention_prefill_tmap")
+                                               _f(scale), window, q_stride, _p(st), _stream()), "attention_prefill_tmap")
         return out
     if kernel in ("tma", "tma3"):
         st = status if status is not None else _tc_status_word(q.device)
@@ -549,20 +552,21 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
         _check(lib().st_attention_prefill_tma(_p(q), _p(pool), ctypes.c_longlong(n_pages), _p(out), _p(tiles),
                                               n_tiles, _p(q_start), _p(start_pos), _p(slots), _p(block_table),
                                               block_table.shape[1], n_layers, layer, nh, nkv, d, page_size,
-                                              _f(scale), window, _p(st), _stream()), "attention_prefill_tma")
+                                              _f(scale), window, q_stride, _p(st), _stream()), "attention_prefill_tma")
         return out
     if kernel == "tc":
         st = status if status is not None else _tc_status_word(q.device)
         _check(lib().st_attention_prefill_tc(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start),
                                              _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
-                                             n_layers, layer, nh, nkv, d, page_size, _f(scale), window, _p(st),
-                                             _stream()), "attention_prefill_tc")
+                                             n_layers, layer, nh, nkv, d, page_size, _f(scale), window, q_stride,
+                                             _p(st), _stream()), "attention_prefill_tc")
         return out
     if kernel != "mma":
         raise KernelError(f"attention_prefill: no kernel named {kernel!r}")
     _check(lib().st_attention_prefill(_p(q), _p(pool), _p(out), _p(tiles), n_tiles, _p(q_start), _p(start_pos),
                                       _p(slots), _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv,
-                                      d, page_size, _f(scale), window, _p(status), _stream()), "attention_prefill")
+                                      d, page_size, _f(scale), window, q_stride, _p(status), _stream()),
+           "attention_prefill")
     return out
 
 

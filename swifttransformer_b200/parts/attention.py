@@ -171,7 +171,7 @@ class Attention(Mixer):
         self.bias, self.window, self.names = bias, window, dict(names)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.qk_position = qk_position
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.b_qkv_bf16 = None
 
     def param_specs(self) -> List[ParamSpec]:
         qw, kw = self.nh * self.d, self.nkv * self.d
@@ -190,6 +190,9 @@ class Attention(Mixer):
         if self.bias:
             self.b_qkv = torch.cat([tensors.pop(n[k] + ".bias") for k in "qkv"], dim=0).contiguous()
             self.b_o = tensors.pop(n["o"] + ".bias")
+            if self.w_qkv.dtype == torch.bfloat16:
+                # lets the library product add the bias in its epilogue when that is exact
+                self.b_qkv_bf16 = ops.lossless_bf16(self.b_qkv)
 
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.nkv, self.d, self.window)
@@ -214,6 +217,20 @@ class Attention(Mixer):
             ops.qkv_linear_to_cache(h, self.w_qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions,
                                     ctx.seq_of_token, ctx.slots, cache.block_table, self.nh, self.nkv, self.d,
                                     ctx.status, write_kv=cache.writable)
+        elif self._queries_in_place(h, ctx):
+            # a step of tiles only (prompt portions): the library product adds the bias in its epilogue, keys
+            # and values are scattered into their pages, and the tile kernel reads the queries where the
+            # product left them, with the row's stride: no pass that copies the queries, none that adds the bias
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv, bias_bf16=self.b_qkv_bf16)
+            ops.qkv_to_cache(qkv, None, None, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token,
+                             ctx.slots, cache.block_table, self.nh, self.nkv, self.d, ctx.status,
+                             write_kv=cache.writable)
+            plan = ctx.plan(PagedAttentionPlan.name)
+            o = torch.empty((h.shape[0], self.nh * self.d), dtype=h.dtype, device=h.device)
+            ops.attention_prefill(qkv, cache.pool, cache.layer, o, plan.tiles, plan.n_tiles, ctx.q_start,
+                                  ctx.start_pos, ctx.slots, cache.block_table, self.nh, self.scale, self.window or 0,
+                                  status=ctx.status, q_stride=qkv.shape[1])
+            return Delta(ops.linear(o, self.w_o), self.b_o)
         else:
             qkv = ops.linear(h, self.w_qkv)
             ops.qkv_to_cache(qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token,
@@ -221,6 +238,16 @@ class Attention(Mixer):
                              write_kv=cache.writable)
         o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
         return Delta(ops.linear(o, self.w_o), self.b_o)
+
+    def _queries_in_place(self, h: torch.Tensor, ctx: Any) -> bool:
+        """Whether this step can leave the queries in the fused product: bfloat16, a head size the tile kernels
+        take, every token of the step in a tile, and a bias the product's epilogue adds exactly (or none)."""
+        if h.dtype != torch.bfloat16 or self.d % 16 or self.d > 256:
+            return False
+        if self.bias and self.b_qkv_bf16 is None:
+            return False
+        plan = ctx.plan(PagedAttentionPlan.name)
+        return plan.n_items == 0 and plan.n_tiles > 0
 
     def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any) -> bool:
         """x += attention(norm(x)) for a step of a few tokens in three kernels: norm + q|k|v product + bias +

@@ -147,7 +147,8 @@ def qkv_to_cache(qkv, bias, q_out, pool, layer, positions, seq_of_token, slots, 
     v = qkv.float()
     if bias is not None:
         v = v + bias
-    q_out.copy_(v[:, :nh * d].to(q_out.dtype))
+    if q_out is not None:
+        q_out.copy_(v[:, :nh * d].to(q_out.dtype))
     if not write_kv:
         return
     ps = pool.shape[4]
@@ -218,7 +219,9 @@ def attention_prefill_tile_rows():
 
 
 def attention_prefill(q, pool, layer, out, tiles, n_tiles, q_start, start_pos, slots, block_table, nh, scale,
-                      window=0, status=None, kernel="auto"):
+                      window=0, status=None, kernel="auto", q_stride=0):
+    if q_stride:
+        q = q[:, :out.shape[1]]
     n = q.shape[0]
     pos = torch.full((n,), -1, dtype=torch.int32)
     seq_of = torch.zeros(n, dtype=torch.int32)

@@ -166,6 +166,17 @@ def test_qkv_to_cache(dtype):
     close(gq, ref_q, dtype, "q", rel=1e-6 if dtype == torch.float32 else 8e-3)
     close(gp, ref_pool, dtype, "pool", rel=1e-6 if dtype == torch.float32 else 8e-3)
     assert torch.equal(gp[:, 0].cpu(), pool[:, 0]) and torch.equal(gp[:, 2].cpu(), pool[:, 2]), "other layers untouched"
+    # the queries may stay where they are: only keys and values move, without a bias, bit for bit
+    for head_dim in (24, 3):                                   # 16-byte pieces, and single elements
+        nh2, nkv2 = (nh, nkv) if head_dim == 24 else (5, 3)
+        pool2, bt_2, slots2 = make_cache(dtype, 3, lens, nkv2, head_dim, ps, L, 23)
+        wide = rnd((n, (nh2 + 2 * nkv2) * head_dim), dtype, 24)
+        want = pool2.clone()
+        cpu_ops.qkv_to_cache(wide, None, None, want, 1, pos, seq, slots2, bt_2, nh2, nkv2, head_dim, st)
+        got = pool2.to(DEV)
+        ops.qkv_to_cache(wide.to(DEV), None, None, got, 1, pos.to(DEV), seq.to(DEV), slots2.to(DEV), bt_2.to(DEV),
+                         nh2, nkv2, head_dim, gst)
+        assert torch.equal(got.cpu(), want) and not torch.equal(want, pool2)
     # a hole in the block table is reported, not written through
     bt2 = bt.clone(); bt2[int(slots[1]), 2] = -1
     ops.qkv_to_cache(qkv.to(DEV), bias.to(DEV), gq, gp, 1, pos.to(DEV), seq.to(DEV), slots.to(DEV), bt2.to(DEV),
@@ -270,6 +281,13 @@ def test_attention_prefill(shape, window, kernel):
     keep = t["seq"] != 2
     close(out[keep], ref[keep], dtype, "attention_prefill", rel=1.5e-2)
     assert torch.all(out[~keep] == 7.0)
+    # the queries as the first columns of a wider tensor (the fused q|k|v product), read with the row's stride
+    wide = torch.cat([q, rnd((q.shape[0], 2 * nkv * d), dtype, 51)], dim=1).to(DEV)
+    strided = torch.full_like(ref, 7.0, device=DEV)
+    ops.attention_prefill(wide, pool.to(DEV), 1, strided, tiles_t.to(DEV), len(tiles), t["q_start"].to(DEV),
+                          t["start"].to(DEV), slots.to(DEV), bt.to(DEV), nh, scale, window, status=status,
+                          kernel=kernel, q_stride=wide.shape[1])
+    assert torch.equal(strided, out)
 
 
 @pytest.mark.parametrize("window", [0, 200])
