@@ -28,7 +28,7 @@
 // runs fastest when all its blocks start together on an idle GPU right behind a small norm kernel (whose few
 // microseconds hide the product's launch and first loads); with the norm inside, the product either starts
 // early, block by block as its predecessor drains, and streams at half the rate, or starts late and shows
-// its own prologue (profiles/decode_step_fusions.md):
+// its own prologue (OPT-1.3B decode step at batch 8: 1.27 to 1.68 ms against 1.12):
 //   * a norm in front: the activations are norm(x) of the float residual rows x (LayerNorm or RMS norm,
 //     two-pass variance in float).  The blocks form clusters of as many blocks as there are rows (1, 2, 4
 //     or 8): block r of a cluster normalises row r with all its threads and stores the bfloat16 row into the
@@ -385,7 +385,7 @@ static int launch_skinny_kernel(const char* tag, void (*kernel)(KArgs...), dim3 
     int n = 0;
     // A product whose blocks form clusters over slices of k starts after its predecessor has finished, not as
     // its blocks drain: started early, its clusters land wherever room appears and the step is 3 % slower
-    // (profiles/decode_step_fusions.md).
+    // (OPT-1.3B, batch 8: 1.152 against 1.120 ms).
     if (st_pdl_enabled(tag) && grid.y == 1) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
