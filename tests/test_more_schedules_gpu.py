@@ -185,3 +185,65 @@ def test_an_engine_that_goes_out_of_scope_gives_its_memory_back_at_once(model_di
         assert torch.cuda.memory_allocated() < before + 0.05 * (during - before)
     finally:
         gc.enable()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_every_kernel_of_a_mixed_trace_against_its_reference(model_dirs, name, dtype):
+    """The checking mode (tests/paranoid.py): a mixed trace launched kernel by kernel, every operation's outputs
+    compared with the CPU reference of that operation on the same inputs."""
+    import paranoid
+    from swifttransformer_b200.engine.replay import TraceSession
+    cfg = TINY[name]["cfg"]
+    reqs = {f"r{i}": helpers.random_tokens(cfg["vocab_size"], n, 70 + i) for i, n in enumerate([40, 9, 64, 23])}
+    steps = helpers.trace_mixed(reqs, seed=11, max_live=3, chunk=20)
+    s = TraceSession(model_dirs[name], dtype, helpers.live_token_need(steps), page_size=TINY[name]["page_size"],
+                     max_requests=4)
+    s.runner.use_cuda_graphs = False
+    with paranoid.watch() as log:
+        got = helpers.replay(s, steps)
+    helpers.check_against_plain(model_dirs[name], reqs, got, dtype, f"paranoid/{name}")
+    assert log["calls"] > 10 * len(steps)
+    assert {"embed", "add_norm", "linear", "attention_plain" if dtype == "float32" else "attention_decode"} <= set(log["by_name"])
+
+
+def test_the_checking_mode_notices_a_wrong_kernel(model_dirs, monkeypatch):
+    import paranoid
+    from swifttransformer_b200 import ops
+    from swifttransformer_b200.engine.replay import TraceSession
+    real = ops.bias_act
+
+    def off_by_a_little(y, bias, act):
+        real(y, bias, act)
+        y[0, 0] += 0.5
+        return y
+    monkeypatch.setattr(ops, "bias_act", off_by_a_little)
+    s = TraceSession(model_dirs["c"], "bfloat16", 128, page_size=32, max_requests=2)     # gelu: bias_act runs
+    s.runner.use_cuda_graphs = False
+    with paranoid.watch():
+        # the outermost operation is the one compared: the library product whose bias and activation kernel is off
+        with pytest.raises(paranoid.ParanoidError, match="linear .* the result differs"):
+            s.run_step([dict(id="x", tokens=helpers.random_tokens(777, 30, 3), want=[29])])
+
+
+def test_operation_times_without_a_profiler(model_dirs):
+    from swifttransformer_b200.engine.replay import TraceSession
+    from swifttransformer_b200.ops import timing
+    s = TraceSession(model_dirs["a"], "bfloat16", 128, page_size=8, max_requests=2)
+    s.runner.use_cuda_graphs = False
+    toks = helpers.random_tokens(512, 40, 5)
+    s.run_step([dict(id="x", tokens=toks[:39], want=[])])
+    timing.start()
+    with pytest.raises(RuntimeError):
+        timing.start()
+    s.run_step([dict(id="x", tokens=toks[39:], want=[0])])
+    report = timing.stop()
+    layers = TINY["a"]["cfg"]["num_hidden_layers"]
+    # a single-token step: per layer the norm + q|k|v + cache write (one operation for the engine), the attention,
+    # two products with the residual sum behind and the norm + fc1; then the final norm and the output head
+    assert report["norm_qkv_linear_to_cache"]["calls"] == layers and report["attention_decode"]["calls"] == layers
+    assert report["linear_add"]["calls"] == 2 * layers and report["norm_linear"]["calls"] == layers
+    assert report["add_norm"]["calls"] == 1
+    assert all(r["ms"] > 0 for r in report.values()) and list(report) == sorted(report, key=lambda k: -report[k]["ms"])
+    from swifttransformer_b200 import ops
+    assert ops.add_norm.__name__ == "add_norm" and not hasattr(ops.add_norm, "__wrapped__")
