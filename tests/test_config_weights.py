@@ -188,3 +188,20 @@ def test_damaged_files(tmp_path):
         load_model(str(empty), "float32", "cpu")
     with pytest.raises(ValueError, match="dtype"):
         load_model(src, "float16", "cpu")
+
+
+def test_run_gpt_reads_its_input_and_decodes_with_a_vocabulary(tmp_path):
+    """The command line's host-side helpers: one line of ids per request (blank lines skipped), and the id ->
+    token table of a vocab.json with the byte-level markers for space and newline turned back."""
+    import json
+    from swifttransformer_b200.cli.run_gpt import PRECISIONS, VocabDecoder, build_parser, read_input
+    inp = tmp_path / "in.txt"
+    inp.write_text("5 17 3\n\n  9 \n100 2 2 2\n")
+    assert read_input(str(inp)) == [[5, 17, 3], [9], [100, 2, 2, 2]]
+    vocab = tmp_path / "vocab.json"
+    vocab.write_text(json.dumps({"One": 5, ",": 17, "Ġtwo": 3, "Ċ": 9}))
+    dec = VocabDecoder(str(vocab))
+    assert "".join(dec.decode(t) for t in [5, 17, 3, 9, 44]) == "One, two\n<44>"
+    args = build_parser().parse_args(["dummy", "opt_125m", "fp16", str(inp), "-v", str(vocab), "-d"])
+    assert args.vocab_json_path == str(vocab) and args.debug and args.end_token == 50118 and args.max_decoding_step == 128
+    assert PRECISIONS["fp16"] == "bfloat16" and PRECISIONS["fp32"] == "float32"

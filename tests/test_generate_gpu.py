@@ -194,6 +194,16 @@ def test_run_gpt_command_line(model_dirs, tmp_path):
         assert line.split(")")[1].split("(")[0].split() == [str(t) for t in want]
         assert "(6 tokens generated)" in line
     assert "Context stage" in r.stdout and "Regression stage" in r.stdout and r.stdout.rstrip().endswith("Done!")
+    # with a vocabulary the same tokens are printed as text
+    vocab = tmp_path / "vocab.json"
+    vocab.write_text(json.dumps({f"Ġt{i}": i for i in range(512)}))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "run_gpt"), model_dirs["a"], "tiny", "fp32",
+                        str(inp), "--max_decoding_step", "3", "--block_size", "8", "--num_total_blocks", "32",
+                        "-v", str(vocab), "-d"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    first = [l for l in r.stdout.splitlines() if l.startswith("[")][0]
+    want = plain_opt.greedy_generate(cfg, w, prompts[0], 3)
+    assert first.split(")")[1].split("(")[0].strip() == " ".join(f"t{t}" for t in want) and "step 1:" in r.stdout
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "run_gpt"), model_dirs["a"], "tiny", "int8",
                           str(inp)], capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "Invalid precision" in bad.stdout
