@@ -204,10 +204,10 @@ class _RecordedStep:
         self._frozen = True
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
-        # Nothing may destroy a CUDA object while the stream records (an engine that went out of scope, or
-        # a recording that was replaced, owns graphs of its own and lies in a reference cycle): the
-        # collector is kept off until the recording has ended.  A full collection beforehand is not needed
-        # for that and costs more than the recording itself (25 ms of the 35 a new shape took).
+        # Nothing may destroy a CUDA object while the stream records (what torch keeps of an older graph may
+        # lie in a reference cycle and wait for the collector): the collector is kept off until the recording
+        # has ended.  A full collection beforehand is not needed for that and costs more than the recording
+        # itself (25 ms of the 35 a new shape took).
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
