@@ -120,3 +120,46 @@ def test_many_requests_decoding_together(big_models, name, dtype, n_requests):
         compare(got[rid], refs[i % len(seqs)], dtype, f"{name}/{n_requests} together/{rid}")
     assert s.cache.free_pages == s.cache.total_pages
     assert s.runner.graph_steps >= tail - 1
+
+
+# The widths of OPT-30B: 56 heads of 128 (a head count that is no multiple of 8), 7168 wide, feed-forward 28672.
+# One layer and a small vocabulary that is no power of two keep the oracle on the CPU short; the widths are real.
+WIDE = dict(vocab_size=5003, hidden_size=7168, num_hidden_layers=1, ffn_dim=28672, num_attention_heads=56,
+            max_position_embeddings=2048, do_layer_norm_before=True, word_embed_proj_dim=7168, enable_bias=True,
+            layer_norm_elementwise_affine=True, activation_function="relu")
+
+
+@pytest.fixture(scope="module")
+def wide_model(tmp_path_factory):
+    from swifttransformer_b200.config import OptConfig
+    from swifttransformer_b200.models import write_random_model
+    d = str(tmp_path_factory.mktemp("opt_30b_widths"))
+    write_random_model(d, OptConfig.from_dict(dict(WIDE)), seed=47, std=0.02)
+    return (d,) + tuple(plain_opt.load_model(d))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_widest_layers_prompts_and_decoding(wide_model, dtype):
+    """Three requests of 97 to 203 tokens at OPT-30B widths: the prompts in portions of 64 beside one another,
+    then the last 6 tokens of all three together, one by one."""
+    model_dir, cfg, w = wide_model
+    tail = 6
+    reqs = {f"w{i}": helpers.random_tokens(cfg["vocab_size"], n, 700 + i) for i, n in enumerate([97, 150, 203])}
+    rows = {rid: sorted(set(range(31, len(t) - tail, 32)) | set(range(len(t) - tail, len(t)))) for rid, t in reqs.items()}
+    refs = {rid: plain_rows(("wide", rid), cfg, w, t, rows[rid]) for rid, t in reqs.items()}
+    steps, longest = [], max(len(t) for t in reqs.values()) - tail
+    for a in range(0, longest, 64):
+        entries = []
+        for rid, t in reqs.items():
+            b = min(a + 64, len(t) - tail)
+            if a < b:
+                entries.append(dict(id=rid, tokens=t[a:b], want=[r - a for r in rows[rid] if a <= r < b]))
+        steps.append(dict(entries=entries, end=[]))
+    for j in range(tail):
+        steps.append(dict(entries=[dict(id=rid, tokens=[t[len(t) - tail + j]], want=[0]) for rid, t in reqs.items()],
+                          end=list(reqs) if j == tail - 1 else []))
+    s = session(model_dir, dtype, helpers.live_token_need(steps), max_requests=3, max_batch_tokens=512)
+    got = helpers.replay(s, steps)
+    for rid in reqs:
+        compare(got[rid], refs[rid], dtype, f"30b widths/{rid}")
+    assert s.cache.free_pages == s.cache.total_pages
