@@ -10,7 +10,7 @@ import torch
 MATRIX = "matrix"        # [out, in] weight of a matrix product: compute dtype
 TABLE = "table"          # rows looked up by an integer id: compute dtype
 VECTOR = "vector"        # bias / shift: always 32-bit
-GAIN = "gain"            # multiplicative norm weight: always 32-bit, initialised around 1
+GAIN = "gain"            # multiplicative norm weight: always 32-bit, initialised near one
 INT_TABLE = "int_table"  # integer lookup table: int32
 
 
