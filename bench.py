@@ -106,7 +106,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
-    ap.add_argument("--no-big", action="store_true", help="skip the OPT-6.7B points (13 GB of random weights)")
+    ap.add_argument("--no-big", action="store_true", help="skip the OPT-6.7B and OPT-30B points (13 and 60 GB of random weights)")
     ap.add_argument("--launch-floor", action="store_true",
                     help="with --only decode: same number of layers and kernels, but hidden size 64, so that the "
                          "step time is what the chain of dependent launches costs by itself")
@@ -380,6 +380,20 @@ def main():
             pf = prefill(2048)
             pts["opt6.7b_prefill_2048_ms"] = round(pf["ms"], 3)
             pts["opt6.7b_prefill_frac"] = round(pf["frac"], 4)
+            # and at the OPT-30B sizes (60 GB of weights, 56 heads of 128), with prompts of 1024 tokens
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+            cfg = opt_preset("opt_30b")
+            model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            P = 1024
+            gen_room = min(ctx_max - P, 2 * (K + W) + 16)
+            r = decode_device(8, min(K, 16), W)
+            pts["opt30b_decode_b8"] = round(r["tok_s"], 1)
+            pts["opt30b_decode_b8_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            pf = prefill(2048)
+            pts["opt30b_prefill_2048_ms"] = round(pf["ms"], 3)
+            pts["opt30b_prefill_frac"] = round(pf["frac"], 4)
         out["points"] = pts
     print(json.dumps(out))
     return 0
