@@ -27,10 +27,15 @@
 #define DM_KEYS 16               // keys per group: the k extent of P V and two n-tiles of S
 #define DM_LOG2E 1.4426950408889634f
 
-template <int DMAX> struct DmStages { static constexpr int value = DMAX == 64 ? 3 : 2; };   // 50 / 68 KB per block
+// stages of a warp's ring.  Few: 50 / 68 KB per block of four warps, so that several blocks share an SM.  DEEP: when the
+// launch has no more blocks than the GPU has SMs a block may take the SM's shared memory for itself, and a warp asks
+// for up to five groups of keys before the wait for the kernel before this one: a decode step of one to four
+// requests then finds nearly all of its keys in shared memory when its queries arrive, instead of fetching three
+// of a warp's five groups one after the other behind them (3.5 us per layer at batch 1).
+template <int DMAX, bool DEEP> struct DmStages { static constexpr int value = DEEP ? 6 : (DMAX == 64 ? 3 : 2); };
 
 // head_dim <= DMAX, a multiple of 16; FULL: head_dim == DMAX, known when compiling (no tests on it in the loops)
-template <int DMAX, bool FULL, int DM_WARPS>
+template <int DMAX, bool FULL, int DM_WARPS, bool DEEP>
 __global__ void __launch_bounds__(DM_WARPS * 32)
 attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
                             float* __restrict__ partial, const int* __restrict__ items,
@@ -42,7 +47,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             int* __restrict__ status) {
     const int d = FULL ? DMAX : d_arg;
     // page_shift: log2(page_size) if that is a power of two, else -1
-    constexpr int STAGES = DmStages<DMAX>::value;
+    constexpr int STAGES = DmStages<DMAX, DEEP>::value;
     constexpr int DM_THREADS = DM_WARPS * 32;
     constexpr int STAGE_ELEMS = 2 * DM_KEYS * DMAX;              // keys, then values, of one group
     extern __shared__ __align__(128) unsigned char dm_raw[];
@@ -360,10 +365,10 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     }
 }
 
-template <int DMAX>
+template <int DMAX, bool DEEP>
 static size_t dm_smem_bytes(int d, int block_pages, int warps) {
     const int DM_WARPS = warps;
-    const size_t stages = (size_t)DM_WARPS * DmStages<DMAX>::value * 2 * DM_KEYS * DMAX * sizeof(bf16);
+    const size_t stages = (size_t)DM_WARPS * DmStages<DMAX, DEEP>::value * 2 * DM_KEYS * DMAX * sizeof(bf16);
     const size_t merge = (size_t)DM_WARPS * 16 * d * sizeof(float);        // reuses the stages' space
     return 16 * DMAX * sizeof(bf16) + (stages > merge ? stages : merge) + (size_t)block_pages * sizeof(int);
 }
@@ -393,25 +398,31 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
     for (int b = 0; b < 30; ++b)
         if (page_size == (1 << b)) page_shift = b;
     int rc;
-#define LAUNCH_DM(DMAX, FULL, WARPS)                                                                                 \
+    // one block per SM at most: the deep ring
+    const bool deep = (long long)n_items * gy * n_splits <= st_sm_count();
+#define LAUNCH_DM(DMAX, FULL, WARPS, DEEP)                                                                           \
     do {                                                                                                             \
-        const size_t smem = dm_smem_bytes<DMAX>(d, st_decode_block_pages(max_pages, page_size, window, n_splits), WARPS);                                                \
+        const size_t smem = dm_smem_bytes<DMAX, DEEP>(d, st_decode_block_pages(max_pages, page_size, window, n_splits), WARPS); \
         if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;                                                              \
         static bool configured = false;                                                                              \
         if (!configured) {                                                                                           \
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL, WARPS>,                     \
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL, WARPS, DEEP>,               \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
             if (e != cudaSuccess) return (int)e;                                                                     \
             configured = true;                                                                                       \
         }                                                                                                            \
-        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL, WARPS>, grid, dim3(WARPS * 32),    \
+        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL, WARPS, DEEP>, grid, dim3(WARPS * 32), \
                            smem, s, (const bf16*)q, (const bf16*)pool, (bf16*)out,                                   \
                            n_splits > 1 ? partial : (float*)nullptr, items, positions, seq_of_token, slots,          \
                            start_pos, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift, sl2, window,  \
                            n_splits, counters, status);                                                              \
     } while (0)
 #define LAUNCH_DM_W(DMAX, FULL)                                                                                      \
-    do { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8); else LAUNCH_DM(DMAX, FULL, 4); } while (0)
+    do {                                                                                                             \
+        if (deep && dm_smem_bytes<DMAX, true>(d, st_decode_block_pages(max_pages, page_size, window, n_splits), warps) <= 200 * 1024) { \
+            if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, true); else LAUNCH_DM(DMAX, FULL, 4, true); }                   \
+        else { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, false); else LAUNCH_DM(DMAX, FULL, 4, false); }              \
+    } while (0)
     if (d == 64) LAUNCH_DM_W(64, true);
     else if (d < 64) LAUNCH_DM_W(64, false);
     else if (d == 128) LAUNCH_DM_W(128, true);
