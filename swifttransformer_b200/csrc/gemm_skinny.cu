@@ -36,6 +36,12 @@
 //     per cluster, and after one cluster barrier every block has all rows next to its tensor cores;
 //   * the residual sum behind: out[m, n] += product + bias in float, in place (each element has one owner).
 //
+// A third variant (up to 8 tokens, K from 544 to 2048, one wave of blocks, no slices of k) brings ALL of a block's
+// weights onto the SM before the wait for the kernel before it: the first two rounds in registers as ever, the
+// rest (up to 48 KB per block, four blocks per SM) with 16-byte asynchronous copies into shared memory.  Behind
+// a norm kernel, whose few microseconds the copies have to themselves, the product then finds its weights next
+// to the tensor cores when its activations arrive, instead of streaming three quarters of them behind the wait.
+//
 // Epilogues: bias and activation; float or bfloat16 output; or the fused
 // q|k|v form: q (+bias) to a dense buffer, k and v (+bias) straight into the
 // paged cache at each token's position (what st_qkv_to_cache does after a
@@ -93,7 +99,8 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
 
 // KFULL: K is a multiple of 32 (known when compiling: no test on k inside a block of 32)
 // XV: 0; or the float4 pieces of a row each thread normalises (K <= 1024 * XV): the norm in front; or -1: the
-//     residual sum behind (out is float and the product is added to what is there)
+//     residual sum behind (out is float and the product is added to what is there); or -2: all weights brought
+//     on chip before the wait (NT == 1, KFULL, no slices of k, 16 < K / 32 <= 64)
 // out_f32: 0 bfloat16, 1 float
 template <int NT, bool QKV, bool KFULL, int XV>
 __global__ void __launch_bounds__(SK_THREADS, NT <= 2 ? 4 : 2)
@@ -103,6 +110,10 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     __shared__ float part[16 * 8 * NT];      // this block's sums over its slice of k
     extern __shared__ __align__(16) unsigned char sk_dyn[];
     bf16* xs = reinterpret_cast<bf16*>(sk_dyn);      // XV > 0: the normalised rows, [M][K + SK_XPAD]
+    constexpr bool PRE = XV == -2;                   // the k-blocks behind the first 2 x SK_WARPS in shared memory
+    constexpr int REG_KB = 2 * SK_WARPS;
+    bf16* ws = reinterpret_cast<bf16*>(sk_dyn);      // PRE: [16][K - 32 REG_KB + 32] (rows 64 bytes askew: no bank conflicts)
+    const int ws_stride = K - 32 * REG_KB + 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * 16;
     const bf16* wa = w + (size_t)min(row0 + g, N - 1) * K + t * 8;
@@ -170,6 +181,17 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     Round ra, rb, rc;
     issue_w(ra, kb_first);          // out-of-range blocks load nothing
     if (NT == 1) issue_w(rb, kb_first + STEP);
+    if constexpr (PRE) {
+        // the rest of this block's weights, asked for now: rows row0 .. row0 + 15, k from 32 REG_KB on
+        const int cpr = (K - 32 * REG_KB) >> 3;        // 16-byte pieces per row
+        for (int r = warp; r < 16; r += SK_WARPS) {
+            const bf16* src = w + (size_t)min(row0 + r, N - 1) * K + 32 * REG_KB;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ws + (size_t)r * ws_stride);
+            for (int c = lane; c < cpr; c += 32)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + c * 16), "l"(src + c * 8));
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
     // What the epilogue needs and no kernel of the step writes is fetched now, under the weight stream,
     // instead of at the end, where every dependent load is a round trip on the critical path: the bias
     // of this thread's output feature (the same in all of its epilogue turns, 256 being a multiple of
@@ -198,7 +220,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     }
     float resid_pre = 0.f;
     ST_PDL_WAIT();
-    if constexpr (XV < 0) {
+    if constexpr (XV == -1) {
         // the residual element this thread adds to in its first epilogue turn, asked for now
         const int m = threadIdx.x >> 4, n = row0 + (threadIdx.x & 15);
         if (threadIdx.x < 16 * 8 * NT && m < M && n < N && (gridDim.y == 1 || blockIdx.y == 0))
@@ -271,7 +293,32 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         cluster.sync();                          // every row is in place in every block
         if (row0 >= N) return;                   // a block that only filled the cluster: nothing reads its memory from here on
     }
-    if (NT == 1) {
+    if constexpr (PRE) {
+        // the activations of all of this warp's k-blocks are asked for at once; the weights are on the SM
+        issue_x(ra, kb_first);
+        issue_x(rb, kb_first + STEP);
+        constexpr int MAXS = (64 - REG_KB) / SK_WARPS;          // k-blocks per warp in shared memory at most
+        uint4 xq[MAXS];
+#pragma unroll
+        for (int j = 0; j < MAXS; ++j) {
+            const int kb = REG_KB + warp + j * SK_WARPS;
+            xq[j] = (kb < nkb && xok[0]) ? __ldcg(reinterpret_cast<const uint4*>(xr[0] + kb * 32)) : zero;
+        }
+        consume(ra);
+        consume(rb);
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();                                        // every thread's copies have landed
+#pragma unroll
+        for (int j = 0; j < MAXS; ++j) {
+            const int kb = REG_KB + warp + j * SK_WARPS;
+            if (kb < nkb) {
+                const uint4 ua = *reinterpret_cast<const uint4*>(ws + (size_t)g * ws_stride + (kb - REG_KB) * 32 + t * 8);
+                const uint4 ub = *reinterpret_cast<const uint4*>(ws + (size_t)(g + 8) * ws_stride + (kb - REG_KB) * 32 + t * 8);
+                mma16816(acc[0], ua.x, ub.x, ua.y, ub.y, xq[j].x, xq[j].y);
+                mma16816(acc[0], ua.z, ub.z, ua.w, ub.w, xq[j].z, xq[j].w);
+            }
+        }
+    } else if (NT == 1) {
         // three rounds in flight (two of them asked for before the wait)
         issue_x(ra, kb_first);
         issue_x(rb, kb_first + STEP);
@@ -332,7 +379,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         v += bias_pre;
         if (!QKV) {
             v = apply_act(v, act);
-            if (XV < 0) {            // the residual sum, in place: this thread is the element's only owner
+            if (XV == -1) {          // the residual sum, in place: this thread is the element's only owner
                 float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n;
                 *o = (i == (int)threadIdx.x ? resid_pre : __ldcg(o)) + v;
             } else if (out_f32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
@@ -360,6 +407,12 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 }
 
 ST_EXPORT int st_gemm_skinny_max_rows() { return 32; }
+
+// ST_B200_SKINNY_NO_PRE=1 in the environment: no product brings its weights on chip before its wait (for measurements)
+static inline bool st_skinny_pre_enabled() {
+    static const char* const off = getenv("ST_B200_SKINNY_NO_PRE");
+    return !(off && off[0] && off[0] != '0');
+}
 
 // how many slices k is cut into (the cluster size): as many blocks as fit on the GPU at once (about
 // four per SM) and no more, at most 8; at least one round of loads per warp and slice
@@ -414,10 +467,32 @@ static int launch_skinny(const void* x, const void* w, const float* bias, void* 
     if (!aligned16(x) || !aligned16(w)) return ST_ERR_BAD_ARG;
     dim3 grid((N + 15) / 16, skinny_slices(N, K));
     const NormSource no_norm = {};
+    if constexpr (XV == 0) {
+        // all weights on chip before the wait: a few tokens, one wave of blocks of four per SM, no slices of k
+        const size_t pre_smem = (size_t)16 * (K - 32 * 2 * SK_WARPS + 32) * sizeof(bf16);
+        if (M <= 8 && K % 32 == 0 && K > 32 * 2 * SK_WARPS && K <= 2048 && grid.y == 1 && st_skinny_pre_enabled()) {
+            static int blocks_per_sm = -1;
+            static size_t allowed = 0;
+            if (pre_smem > allowed) {
+                if (cudaFuncSetAttribute(gemm_skinny_kernel<1, QKV, true, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(16 * (2048 - 32 * 2 * SK_WARPS + 32) * sizeof(bf16))) == cudaSuccess)
+                    allowed = 16 * (2048 - 32 * 2 * SK_WARPS + 32) * sizeof(bf16);
+                else
+                    (void)cudaGetLastError();
+            }
+            if (blocks_per_sm < 0 && allowed) {
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, gemm_skinny_kernel<1, QKV, true, -2>, SK_THREADS,
+                                                                  allowed) != cudaSuccess) { (void)cudaGetLastError(); blocks_per_sm = 0; }
+            }
+            if (pre_smem <= allowed && (long long)grid.x <= (long long)blocks_per_sm * st_sm_count())
+                return launch_skinny_kernel("skinny", gemm_skinny_kernel<1, QKV, true, -2>, grid, pre_smem, 1, s, (const bf16*)x,
+                                            (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, no_norm);
+        }
+    }
 #define LAUNCH_SK(NT)                                                                                              \
-    (K % 32 == 0 ? launch_skinny_kernel(XV < 0 ? (K > 4096 ? "gemm_add_wide" : "gemm_add") : "skinny", gemm_skinny_kernel<NT, QKV, true, XV>, grid, 0, 1, s, (const bf16*)x,      \
+    (K % 32 == 0 ? launch_skinny_kernel(XV == -1 ? (K > 4096 ? "gemm_add_wide" : "gemm_add") : "skinny", gemm_skinny_kernel<NT, QKV, true, XV>, grid, 0, 1, s, (const bf16*)x,      \
                                         (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, no_norm)            \
-                 : launch_skinny_kernel(XV < 0 ? "gemm_add" : "skinny", gemm_skinny_kernel<NT, QKV, false, XV>, grid, 0, 1, s, (const bf16*)x,     \
+                 : launch_skinny_kernel(XV == -1 ? "gemm_add" : "skinny", gemm_skinny_kernel<NT, QKV, false, XV>, grid, 0, 1, s, (const bf16*)x,     \
                                         (const bf16*)w, bias, out, M, N, K, act, out_f32, tgt, no_norm))
     if (M <= 8) return LAUNCH_SK(1);
     if (M <= 16) return LAUNCH_SK(2);
