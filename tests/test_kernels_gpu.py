@@ -592,6 +592,62 @@ def test_gemm_stream_tc(shape):
     assert torch.equal(one[0], full[n - 1])
 
 
+@pytest.mark.parametrize("shape", [(5, 6144, 2048), (8, 5000, 576), (2, 8192, 1056), (1, 4768, 1024)])
+def test_gemm_skinny_with_all_weights_on_chip_before_its_wait(shape, monkeypatch):
+    """Few tokens, an inner dimension of 544 to 2048 and more than 296 tiles of 16 features (no slices of k): the
+    product copies what its two register rounds do not hold into shared memory ahead of its dependency wait.  Sizes:
+    the engine's own, a feature count that is no multiple of 16, an inner dimension of an odd number of blocks of
+    32, the fewest features that still run uncut.  The same launch with the variant switched off gives the same bits
+    (the arithmetic per output is the same: a warp's k-blocks in the same order)."""
+    n, m, k = shape
+    a, w, b = rnd((n, k), torch.bfloat16, 180), rnd((m, k), torch.bfloat16, 181, 0.1), rnd((m,), torch.float32, 182)
+    for act in ("none", "relu"):
+        got = ops.gemm_skinny(a.to(DEV), w.to(DEV), b.to(DEV), act, torch.float32)
+        close(got, cpu_ops.linear(a, w, b, act, torch.float32), torch.float32, f"gemm_skinny on chip {act}", rel=2e-5)
+    one = ops.gemm_skinny(a[n - 1:n].to(DEV).contiguous(), w.to(DEV), b.to(DEV), "none", torch.float32)
+    full = ops.gemm_skinny(a.to(DEV), w.to(DEV), b.to(DEV), "none", torch.float32)
+    assert torch.equal(one[0], full[n - 1])
+
+
+@pytest.mark.parametrize("shape", [(3, 1000, 1024), (8, 130, 2048), (7, 2040, 800), (8, 6144, 1536)])
+def test_linear_add_uncut_with_all_weights_on_chip(shape):
+    """The residual sum behind a product of 544 to 2048 inner elements: one block per 16 features over the whole of k
+    (never cut into cluster slices), weights on chip before the wait."""
+    n, m, k = shape
+    a, w, b = rnd((n, k), torch.bfloat16, 185), rnd((m, k), torch.bfloat16, 186, 0.1), rnd((m,), torch.float32, 187)
+    x = rnd((n, m), torch.float32, 188) * 5
+    got = x.to(DEV).clone()
+    ops.linear_add(a.to(DEV), w.to(DEV), b.to(DEV), got)
+    ref = x.double() + cpu_ops.linear(a, w, b, "none", torch.float32).double()
+    close(got, ref, torch.float32, "linear_add on chip", rel=2e-5)
+
+
+def test_qkv_linear_to_cache_with_all_weights_on_chip():
+    """The fused q|k|v product at a size that takes the on-chip variant (6144 features, 1024 inner elements, 7 tokens
+    of which one is padding): queries and pages as the plain reference leaves them."""
+    dtype = torch.bfloat16
+    n, nh, nkv, d, ps, L, K = 7, 32, 32, 64, 16, 2, 1024
+    lens = [33 + 5 * i for i in range(n)]
+    pool, bt, slots = make_cache(dtype, n, lens, nkv, d, ps, L, 190)
+    pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32)
+    pos[3] = -1
+    seq = torch.arange(n, dtype=torch.int32)
+    h, w = rnd((n, K), dtype, 191), rnd(((nh + 2 * nkv) * d, K), dtype, 192, 0.1)
+    bias = rnd(((nh + 2 * nkv) * d,), torch.float32, 193)
+    ref_pool, ref_q, st = pool.clone(), torch.zeros(n, nh * d, dtype=dtype), torch.zeros(1, dtype=torch.int32)
+    cpu_ops.qkv_linear_to_cache(h, w, bias, ref_q, ref_pool, 1, pos, seq, slots, bt, nh, nkv, d, st)
+    gp, gq = pool.to(DEV), torch.zeros(n, nh * d, dtype=dtype, device=DEV)
+    gst = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.qkv_linear_to_cache(h.to(DEV), w.to(DEV), bias.to(DEV), gq, gp, 1, pos.to(DEV), seq.to(DEV), slots.to(DEV),
+                            bt.to(DEV), nh, nkv, d, gst)
+    assert int(gst.item()) == 0
+    live = pos >= 0
+    close(gq[live.to(DEV)], ref_q[live], dtype, "q on chip", rel=1e-2)
+    close(gp, ref_pool, dtype, "pool on chip", rel=1e-2)
+    changed = (gp.cpu() != pool).any(dim=-1).sum().item()
+    assert changed <= 2 * nkv * (n - 1)
+
+
 @pytest.mark.parametrize("n", [1, 8, 13, 32])
 def test_qkv_linear_to_cache(n):
     dtype = torch.bfloat16
