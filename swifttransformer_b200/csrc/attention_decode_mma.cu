@@ -6,9 +6,13 @@
 // the arithmetic is a handful of m16n8k16 products per 16 keys and the kernel is back to being a
 // copy loop:
 //
-//   * One thread block per (query token, kv head, split of the key range); the rows of the 16-row
-//     query operand are the query heads that share the kv head (one for multi-head attention, the
-//     whole group for grouped-query attention), zero beyond.
+//   * One thread block per (query token, kv head, split of the key range) and up to 8 query heads that
+//     share the kv head (one for multi-head attention, the group for grouped-query attention).  The
+//     products are taken transposed: S^T = K Q^T with the 16 KEYS of a group as the 16-row operand and
+//     the heads as the 8 columns, O^T += V^T P^T with 16 head dimensions as the rows: four products per
+//     16 keys for each of the two instead of eight, two exponentials per lane and head pair instead of
+//     eight per lane, half the accumulator registers.  (With the heads as the 16 rows, fifteen of which
+//     are empty in multi-head attention, the kernel spent as many issue slots as memory cycles.)
 //   * Each of the block's warps (four, or eight when the launch has few and long blocks: the chain of
 //     groups a warp works through is then half as long) runs its own pipeline, without block-wide barriers: it takes
 //     every fourth (eighth) group of 16 keys, gathers their key and value rows page by page with 16-byte
@@ -51,10 +55,9 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     constexpr int DM_THREADS = DM_WARPS * 32;
     constexpr int STAGE_ELEMS = 2 * DM_KEYS * DMAX;              // keys, then values, of one group
     extern __shared__ __align__(128) unsigned char dm_raw[];
-    bf16* sQ = reinterpret_cast<bf16*>(dm_raw);                  // [16][DMAX]
-    bf16* sKV = sQ + 16 * DMAX;                                  // [DM_WARPS][STAGES][2][DM_KEYS][DMAX]
+    bf16* sKV = reinterpret_cast<bf16*>(dm_raw);                 // [DM_WARPS][STAGES][2][DM_KEYS][DMAX]
     int* s_pages = reinterpret_cast<int*>(sKV + DM_WARPS * STAGES * STAGE_ELEMS);
-    __shared__ float s_m[DM_WARPS][16], s_l[DM_WARPS][16];
+    __shared__ float s_m[DM_WARPS][8], s_l[DM_WARPS][8];
     __shared__ int s_last;
     ST_PDL_TRIGGER();
     // Which token, where it stands, its slot and the page numbers of its key range are inputs of the step
@@ -63,10 +66,10 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int t = items ? items[blockIdx.x] : blockIdx.x;
     if (t < 0) return;            // a padding entry of a fixed-shape step
     const int group = nh / nkv;                                   // query heads per kv head
-    const int chunks_per_kv = (group + 15) / 16;
+    const int chunks_per_kv = (group + 7) / 8;
     const int kvh = blockIdx.y / chunks_per_kv;
-    const int h0 = kvh * group + (blockIdx.y % chunks_per_kv) * 16;   // first query head of this block
-    const int n_heads = min(16, kvh * group + group - h0);
+    const int h0 = kvh * group + (blockIdx.y % chunks_per_kv) * 8;    // first query head of this block
+    const int n_heads = min(8, kvh * group + group - h0);
     const int split = blockIdx.z;
     const int pos = positions[t];
     if (pos < 0) return;   // padding entry of a fixed-shape launch
@@ -109,11 +112,14 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     // instructions use inside a stage: nothing of this is recomputed per group
     const uint32_t my_stages = smem_u32(sKV + warp * STAGES * STAGE_ELEMS);
     constexpr uint32_t STAGE_BYTES = STAGE_ELEMS * sizeof(bf16), V_BYTES = DM_KEYS * DMAX * sizeof(bf16);
+    // keys as the row operand of S^T (plain ldmatrix: matrices = keys 0-7 | 8-15 x dims 16 kk + 0-7 | 8-15) and
+    // values as the row operand of O^T (transposing ldmatrix: matrices = keys 0-7 | 8-15 x dims 16 mt + 0-7 | 8-15,
+    // in the order the fragment wants its rows = dims)
     uint32_t k_off[DMAX / 16], v_off[DMAX / 16];
 #pragma unroll
     for (int kk = 0; kk < DMAX / 16; ++kk) {
-        k_off[kk] = (uint32_t)(tile_ptr<DMAX>(sQ, (lane & 7) + (lane >> 4) * 8, 2 * kk + ((lane >> 3) & 1)) - sQ) * 2;
-        v_off[kk] = V_BYTES + (uint32_t)(tile_ptr<DMAX>(sQ, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)) - sQ) * 2;
+        k_off[kk] = (uint32_t)(tile_ptr<DMAX>(sKV, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)) - sKV) * 2;
+        v_off[kk] = V_BYTES + (uint32_t)(tile_ptr<DMAX>(sKV, (lane & 7) + (lane >> 4) * 8, 2 * kk + ((lane >> 3) & 1)) - sKV) * 2;
     }
     // Consecutive lanes copy consecutive 16-byte chunks of a row (whole 128-byte lines per instruction).
     // Which (row of the group, chunk) a lane copies in its j-th turn does not depend on the group: worked
@@ -127,7 +133,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         const int r = idx / chunks, c = idx - r * chunks;
         ld_row[j] = r < DM_KEYS ? r : -1;
         ld_col[j] = c * 8;
-        ld_off[j] = r < DM_KEYS ? (uint32_t)(tile_ptr<DMAX>(sQ, r, c) - sQ) * 2 : 0;
+        ld_off[j] = r < DM_KEYS ? (uint32_t)(tile_ptr<DMAX>(sKV, r, c) - sKV) * 2 : 0;
     }
     // When pages hold a multiple of 16 positions and the range starts on such a multiple, the 16 keys of a
     // group lie in one page: one page lookup per group instead of one per copied row.
@@ -178,11 +184,20 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         }
     }
     ST_PDL_WAIT();
-    for (int i = threadIdx.x; i < 16 * chunks; i += DM_THREADS) {
-        const int r = i / chunks, c = i - r * chunks;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < n_heads) v = __ldcg(reinterpret_cast<const uint4*>(q + ((size_t)t * nh + h0 + r) * d + c * 8));
-        *reinterpret_cast<uint4*>(tile_ptr<DMAX>(sQ, r, c)) = v;
+    // the queries as the column operand of S^T: lane (g, t) holds dims 2t, 2t+1 (and +8) of head g for every
+    // block of 16 dims, straight from global memory (one trip, no staging)
+    const int g = lane >> 2, t4 = lane & 3;
+    uint32_t qb[DMAX / 16][2];
+    {
+        const bf16* qrow = q + ((size_t)t * nh + h0 + min(g, n_heads - 1)) * d + 2 * t4;
+#pragma unroll
+        for (int kk = 0; kk < DMAX / 16; ++kk) {
+            qb[kk][0] = qb[kk][1] = 0u;
+            if (kk * 16 < d && g < n_heads) {
+                qb[kk][0] = __ldcg(reinterpret_cast<const unsigned*>(qrow + kk * 16));
+                qb[kk][1] = __ldcg(reinterpret_cast<const unsigned*>(qrow + kk * 16 + 8));
+            }
+        }
     }
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -191,19 +206,14 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             cp_async_commit();
         }
     }
-    __syncthreads();          // the queries are in place
-    // the query operand: fragments of the 16 x d tile, kept in registers
-    uint32_t qa[DMAX / 16][4];
+    // O^T: rows = dims (16 per tile), columns = heads: lane (g, t) holds dims 16 mt + g (and + 8) of heads 2t, 2t+1
+    float o_acc[DMAX / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < DMAX / 16; ++kk) {
-        if (kk * 16 < d)
-            ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3],
-                        tile_ptr<DMAX>(sQ, (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
-    }
-    float o_acc[DMAX / 8][4];
-#pragma unroll
-    for (int i = 0; i < DMAX / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
+    for (int i = 0; i < DMAX / 16; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // heads 2t and 2t+1 (the same in every g)
+    // where this lane's P operand comes from: keys 2t, 2t+1 (and + 8) of head g lie in lanes (2t, g/2) and (2t+1, g/2)
+    const int src_a = (2 * t4) * 4 + (g >> 1), src_b = (2 * t4 + 1) * 4 + (g >> 1);
+    const bool odd_head = g & 1;
 
     for (int i = 0; i < my_n; ++i) {
         if (i + STAGES - 1 < my_n) load_group(i + STAGES - 1, (i + STAGES - 1) % STAGES);
@@ -211,37 +221,32 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         cp_async_wait<STAGES - 1>();       // group i has landed (for this lane; the barrier covers the others)
         __syncwarp();
         const uint32_t st = my_stages + (i % STAGES) * STAGE_BYTES;
-        // S = Q K^T: 16 rows x 16 keys
-        float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // S^T = K Q^T: 16 keys x 8 heads; lane (g, t): keys g and g + 8 of heads 2t, 2t+1
+        float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int kk = 0; kk < DMAX / 16; ++kk) {
             if (kk * 16 < d) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_s(b0, b1, b2, b3, st + k_off[kk]);
-                mma_bf16(s_acc[0], qa[kk], b0, b1);
-                mma_bf16(s_acc[1], qa[kk], b2, b3);
+                uint32_t a[4];
+                ldmatrix_x4_s(a[0], a[1], a[2], a[3], st + k_off[kk]);
+                mma_bf16(s_acc, a, qb[kk][0], qb[kk][1]);
             }
         }
         const int key0 = k_lo + (warp + i * DM_WARPS) * DM_KEYS;
         if (key0 + DM_KEYS > k_hi) {       // the range's last group: keys past its end do not count
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 2; ++e)
-                    if (key0 + nt * 8 + (lane & 3) * 2 + e >= k_hi) s_acc[nt][e] = s_acc[nt][2 + e] = -INFINITY;
+            if (key0 + g >= k_hi) s_acc[0] = s_acc[1] = -INFINITY;
+            if (key0 + g + 8 >= k_hi) s_acc[2] = s_acc[3] = -INFINITY;
         }
-        float mx[2];
-        mx[0] = fmaxf(fmaxf(s_acc[0][0], s_acc[0][1]), fmaxf(s_acc[1][0], s_acc[1][1]));
-        mx[1] = fmaxf(fmaxf(s_acc[0][2], s_acc[0][3]), fmaxf(s_acc[1][2], s_acc[1][3]));
-        // The reference maximum of a row only moves when the true maximum has grown by more than 2^8 (or
+        // The reference maximum of a head only moves when the true maximum has grown by more than 2^8 (or
         // from "no key yet"): until then P is taken relative to the older reference, which is exact after
         // the final division by the sum, and O and the sum need no rescaling.
+        float mx[2] = {fmaxf(s_acc[0], s_acc[2]), fmaxf(s_acc[1], s_acc[3])};
         float corr[2] = {1.f, 1.f}, m_use[2];
         bool moved = false;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
             const float m_new = fmaxf(m_run[r], mx[r] * scale_log2);   // scale > 0: max commutes with it
             if (m_new > m_run[r] + 8.f) {
                 corr[r] = fast_exp2(m_run[r] - m_new);                // m_run = -inf: 0
@@ -251,42 +256,34 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             m_use[r] = (m_run[r] == -INFINITY) ? 0.f : m_run[r];
         }
         moved = __any_sync(0xffffffffu, moved);
-        float rs[2] = {0.f, 0.f};
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float pa = fast_exp2(fmaf(s_acc[nt][e], scale_log2, -m_use[0]));
-                const float pb = fast_exp2(fmaf(s_acc[nt][2 + e], scale_log2, -m_use[1]));
-                s_acc[nt][e] = pa; s_acc[nt][2 + e] = pb;
-                rs[0] += pa; rs[1] += pb;
-            }
-        }
+        const float p0 = fast_exp2(fmaf(s_acc[0], scale_log2, -m_use[0])), p1 = fast_exp2(fmaf(s_acc[1], scale_log2, -m_use[1]));
+        const float p2 = fast_exp2(fmaf(s_acc[2], scale_log2, -m_use[0])), p3 = fast_exp2(fmaf(s_acc[3], scale_log2, -m_use[1]));
+        float rs[2] = {p0 + p2, p1 + p3};
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
-            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 4);
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 8);
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 16);
             l_run[r] = l_run[r] * corr[r] + rs[r];
         }
-        uint32_t a[4];
-        a[0] = pack_bf16(s_acc[0][0], s_acc[0][1]);
-        a[1] = pack_bf16(s_acc[0][2], s_acc[0][3]);
-        a[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
-        a[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
-        // O = O corr + P V
+        // P^T as the column operand of O^T: (key g | key g + 8) of each of this lane's heads packed, fetched by the
+        // lane that needs keys 2t, 2t+1 of head g, and re-paired by key
+        const uint32_t x_even = pack_bf16(p0, p2), x_odd = pack_bf16(p1, p3);
+        const uint32_t ae = __shfl_sync(0xffffffffu, x_even, src_a), ao = __shfl_sync(0xffffffffu, x_odd, src_a);
+        const uint32_t be = __shfl_sync(0xffffffffu, x_even, src_b), bo = __shfl_sync(0xffffffffu, x_odd, src_b);
+        const uint32_t xa = odd_head ? ao : ae, xb = odd_head ? bo : be;
+        const uint32_t pb0 = __byte_perm(xa, xb, 0x5410), pb1 = __byte_perm(xa, xb, 0x7632);
+        // O^T = O^T corr + V^T P^T
 #pragma unroll
-        for (int np = 0; np < DMAX / 16; ++np) {
-            if (np * 16 < d) {
+        for (int mt = 0; mt < DMAX / 16; ++mt) {
+            if (mt * 16 < d) {
                 if (moved) {
-                    o_acc[2 * np][0] *= corr[0]; o_acc[2 * np][1] *= corr[0];
-                    o_acc[2 * np][2] *= corr[1]; o_acc[2 * np][3] *= corr[1];
-                    o_acc[2 * np + 1][0] *= corr[0]; o_acc[2 * np + 1][1] *= corr[0];
-                    o_acc[2 * np + 1][2] *= corr[1]; o_acc[2 * np + 1][3] *= corr[1];
+                    o_acc[mt][0] *= corr[0]; o_acc[mt][1] *= corr[1];
+                    o_acc[mt][2] *= corr[0]; o_acc[mt][3] *= corr[1];
                 }
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans_s(b0, b1, b2, b3, st + v_off[np]);
-                mma_bf16(o_acc[2 * np], a, b0, b1);
-                mma_bf16(o_acc[2 * np + 1], a, b2, b3);
+                uint32_t a[4];
+                ldmatrix_x4_trans_s(a[0], a[1], a[2], a[3], st + v_off[mt]);
+                mma_bf16(o_acc[mt], a, pb0, pb1);
             }
         }
         __syncwarp();                      // every lane is done with the stage before it is refilled
@@ -294,22 +291,20 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     cp_async_wait<0>();
     __syncthreads();                       // all warps are done with their stages: the space is reused
 
-    // ---- merge the four warps: each leaves (max, sum, O) of its 16 rows in shared memory
-    float* s_o = reinterpret_cast<float*>(sKV);                  // [DM_WARPS][16][d]
+    // ---- merge the warps: each leaves (max, sum, O) of its 8 heads in shared memory
+    float* s_o = reinterpret_cast<float*>(sKV);                  // [DM_WARPS][8][d]
     {
-        const int ra = lane >> 2, rb = ra + 8;
-        if ((lane & 3) == 0) {
-            s_m[warp][ra] = m_run[0]; s_l[warp][ra] = l_run[0];
-            s_m[warp][rb] = m_run[1]; s_l[warp][rb] = l_run[1];
+        if (g == 0) {
+            s_m[warp][2 * t4] = m_run[0]; s_l[warp][2 * t4] = l_run[0];
+            s_m[warp][2 * t4 + 1] = m_run[1]; s_l[warp][2 * t4 + 1] = l_run[1];
         }
 #pragma unroll
-        for (int nt = 0; nt < DMAX / 8; ++nt) {
-            const int dim = nt * 8 + (lane & 3) * 2;
-            if (dim < d) {
-                float* pa = s_o + ((size_t)warp * 16 + ra) * d + dim;
-                float* pb = s_o + ((size_t)warp * 16 + rb) * d + dim;
-                pa[0] = o_acc[nt][0]; pa[1] = o_acc[nt][1];
-                pb[0] = o_acc[nt][2]; pb[1] = o_acc[nt][3];
+        for (int mt = 0; mt < DMAX / 16; ++mt) {
+            const int dim = mt * 16 + g;
+            if (dim < d) {                 // d is a multiple of 16: dim + 8 < d as well
+                float* pa = s_o + ((size_t)warp * 8 + 2 * t4) * d + dim;
+                pa[0] = o_acc[mt][0]; pa[d] = o_acc[mt][1];
+                pa[8] = o_acc[mt][2]; pa[d + 8] = o_acc[mt][3];
             }
         }
     }
@@ -324,7 +319,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         for (int w = 0; w < DM_WARPS; ++w) {
             const float f = s_m[w][r] == -INFINITY ? 0.f : exp2f(s_m[w][r] - mm);
             ll += s_l[w][r] * f;
-            a += s_o[((size_t)w * 16 + r) * d + e] * f;
+            a += s_o[((size_t)w * 8 + r) * d + e] * f;
         }
         const int h = h0 + r;
         if (n_splits == 1) {
@@ -369,8 +364,8 @@ template <int DMAX, bool DEEP>
 static size_t dm_smem_bytes(int d, int block_pages, int warps) {
     const int DM_WARPS = warps;
     const size_t stages = (size_t)DM_WARPS * DmStages<DMAX, DEEP>::value * 2 * DM_KEYS * DMAX * sizeof(bf16);
-    const size_t merge = (size_t)DM_WARPS * 16 * d * sizeof(float);        // reuses the stages' space
-    return 16 * DMAX * sizeof(bf16) + (stages > merge ? stages : merge) + (size_t)block_pages * sizeof(int);
+    const size_t merge = (size_t)DM_WARPS * 8 * d * sizeof(float);         // reuses the stages' space
+    return (stages > merge ? stages : merge) + (size_t)block_pages * sizeof(int);
 }
 
 ST_EXPORT int st_attention_decode_mma_applies(int d) { return d > 0 && d % 16 == 0 && d <= 128; }
@@ -389,7 +384,7 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
     if (!st_attention_decode_mma_applies(d)) return ST_ERR_BAD_SIZE;
     if (n_splits > 1 && !partial) return ST_ERR_BAD_ARG;
     const int group = nh / nkv;
-    const long long gy = (long long)nkv * ((group + 15) / 16);
+    const long long gy = (long long)nkv * ((group + 7) / 8);
     if (gy > 65535) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_items, (unsigned)gy, n_splits);
