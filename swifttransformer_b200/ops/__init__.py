@@ -475,8 +475,11 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
         # Head sizes up to 64: the tensor-core kernel; beyond, it holds fewer blocks per SM than the lanes
         # kernel and pays only for many blocks; grouped queries always gain from it (the group shares one
         # read of the keys and values).
+        # (OPT-6.7B decode step, tensor-core / lanes kernel, ms: batch 1 2.98 / 3.08, batch 8 3.68 / 3.70, batch 16
+        # 3.88 / 3.76, batch 64 the tensor-core kernel either way: it also serves launches of up to two blocks per SM)
         busy = n_items * nkv >= DECODE_MMA_MIN_BLOCKS
-        kernel = "mma" if mma_ok and (d <= 64 or nh != nkv or busy) else "lanes"
+        few = n_items * nkv * n_splits <= 2 * sm_count(q.device)
+        kernel = "mma" if mma_ok and (d <= 64 or nh != nkv or busy or few) else "lanes"
     if kernel == "mma":
         if not mma_ok:
             raise KernelError("attention_decode: the tensor-core kernel takes head sizes that are multiples of "
