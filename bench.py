@@ -369,31 +369,31 @@ def main():
             pts[f"decode_b{b}"] = round(r["tok_s"], 1)
             pts[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
         if args.model_name == "opt_1.3b" and not args.layers and not args.launch_floor and not args.no_big:
-            # the same two measurements at the OPT-6.7B sizes (head size 128: another set of attention kernels)
-            del model
-            torch.cuda.empty_cache()
-            cfg = opt_preset("opt_6.7b")
-            model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
-            r = decode_device(8, min(K, 32), W)
-            pts["opt6.7b_decode_b8"] = round(r["tok_s"], 1)
-            pts["opt6.7b_decode_b8_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
-            pf = prefill(2048)
-            pts["opt6.7b_prefill_2048_ms"] = round(pf["ms"], 3)
-            pts["opt6.7b_prefill_frac"] = round(pf["frac"], 4)
-            # and at the OPT-30B sizes (60 GB of weights, 56 heads of 128), with prompts of 1024 tokens
-            del model
-            gc.collect()
-            torch.cuda.empty_cache()
-            cfg = opt_preset("opt_30b")
-            model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
-            P = 1024
-            gen_room = min(ctx_max - P, 2 * (K + W) + 16)
-            r = decode_device(8, min(K, 16), W)
-            pts["opt30b_decode_b8"] = round(r["tok_s"], 1)
-            pts["opt30b_decode_b8_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
-            pf = prefill(2048)
-            pts["opt30b_prefill_2048_ms"] = round(pf["ms"], 3)
-            pts["opt30b_prefill_frac"] = round(pf["frac"], 4)
+            # The same two measurements at the OPT-6.7B sizes (head size 128: another set of attention kernels) and at
+            # the OPT-30B sizes (60 GB of weights, 56 heads of 128; prompts of 1024 tokens).  A GPU that has no room
+            # for them (someone else's memory on it) costs these points, not the line.
+            for name, key, prompt, steps in (("opt_6.7b", "opt6.7b", P, 32), ("opt_30b", "opt30b", 1024, 16)):
+                model = None
+                gc.collect()
+                torch.cuda.empty_cache()
+                free = torch.cuda.mem_get_info()[0]
+                cfg = opt_preset(name)
+                need = 2 * 12 * cfg.num_hidden_layers * cfg.hidden_size ** 2 * 1.25
+                if free < need:
+                    pts[f"{key}_skipped"] = f"{free >> 30} GiB free on the device"
+                    continue
+                try:
+                    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+                    P = prompt
+                    gen_room = min(ctx_max - P, 2 * (K + W) + 16)
+                    r = decode_device(8, min(K, steps), W)
+                    pts[f"{key}_decode_b8"] = round(r["tok_s"], 1)
+                    pts[f"{key}_decode_b8_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+                    pf = prefill(2048)
+                    pts[f"{key}_prefill_2048_ms"] = round(pf["ms"], 3)
+                    pts[f"{key}_prefill_frac"] = round(pf["frac"], 4)
+                except torch.cuda.OutOfMemoryError:
+                    pts[f"{key}_skipped"] = "out of device memory"
         out["points"] = pts
     print(json.dumps(out))
     return 0
