@@ -87,9 +87,18 @@ ST_EXPORT int st_add_positions(const void* in, int n_tokens, int width, const in
 //       kind 2: s                                                    (no norm)
 //   out_act[r] = T(y)  (optional), out_f32[r] = y  (optional; may alias x when rows is null)
 // The row is staged in shared memory as float; all statistics are float.
+// Further float addends of the residual sum: `n` tensors of the shape of x, `stride` elements apart (the slices of
+// k a product was cut into leave their parts for the norm kernel to add, in slice order, instead of meeting in
+// the product's own kernel).
+struct AddParts {
+    const float* p;
+    int n;
+    long long stride;
+};
+
 template <typename T, bool VEC>
 __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
-                                const T* __restrict__ delta, const float* __restrict__ delta_bias,
+                                const T* __restrict__ delta, const float* __restrict__ delta_bias, AddParts parts,
                                 float* resid_out, const float* __restrict__ gamma,
                                 const float* __restrict__ beta, float eps, int kind, int width,
                                 T* __restrict__ out_act, float* out_f32) {
@@ -118,9 +127,15 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
             const int v1 = v0 + blockDim.x;
             const bool two = v1 < nvec;
             float4 a = load4_cg(xr + v0 * 4), b = two ? load4_cg(xr + v1 * 4) : make_float4(0, 0, 0, 0);
-            if (delta) {
-                a = add4(a, load4_cg(delta + i * width + v0 * 4));
-                if (two) b = add4(b, load4_cg(delta + i * width + v1 * 4));
+            if (delta || parts.n) {
+                float4 da = delta ? load4_cg(delta + i * width + v0 * 4) : make_float4(0, 0, 0, 0);
+                float4 db = (delta && two) ? load4_cg(delta + i * width + v1 * 4) : make_float4(0, 0, 0, 0);
+                for (int sl = 0; sl < parts.n; ++sl) {
+                    da = add4(da, load4_cg(parts.p + sl * parts.stride + i * width + v0 * 4));
+                    if (two) db = add4(db, load4_cg(parts.p + sl * parts.stride + i * width + v1 * 4));
+                }
+                a = add4(a, da);
+                if (two) b = add4(b, db);
             }
             if (delta_bias) {
                 a = add4(a, load4(delta_bias + v0 * 4));
@@ -140,7 +155,11 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
     } else {
         for (int e = threadIdx.x; e < width; e += blockDim.x) {
             float v = load1_cg(xr + e);
-            if (delta) v += load1_cg(delta + i * width + e);
+            if (delta || parts.n) {
+                float dv = delta ? load1_cg(delta + i * width + e) : 0.f;
+                for (int sl = 0; sl < parts.n; ++sl) dv += load1_cg(parts.p + sl * parts.stride + i * width + e);
+                v += dv;
+            }
             if (delta_bias) v += delta_bias[e];
             srow[e] = v;
             sum += v;
@@ -203,9 +222,9 @@ __global__ void add_norm_kernel(const float* x, const int* __restrict__ rows,
 // and the bias of delta are fetched once per block, before the wait for the kernel before this one (no
 // kernel writes them).  Every row is computed by the same code in the same order whatever the number of
 // rows: the result of a token does not depend on the batch.
-template <typename T, int VPT>
-__global__ void __launch_bounds__(512, VPT == 2 ? 2 : 1) add_norm_vec_kernel(const float* x, const int* __restrict__ rows,
-                                    const T* __restrict__ delta, const float* __restrict__ delta_bias,
+template <typename T, int VPT, bool PARTS>
+__global__ void __launch_bounds__(512, (VPT == 2 && !PARTS) ? 2 : 1) add_norm_vec_kernel(const float* x, const int* __restrict__ rows,
+                                    const T* __restrict__ delta, const float* __restrict__ delta_bias, AddParts parts,
                                     float* resid_out, const float* __restrict__ gamma,
                                     const float* __restrict__ beta, float eps, int kind, int width, int n_rows,
                                     T* __restrict__ out_act, float* out_f32) {
@@ -236,6 +255,17 @@ __global__ void __launch_bounds__(512, VPT == 2 ? 2 : 1) add_norm_vec_kernel(con
             const int v = threadIdx.x + j * blockDim.x;
             xa[j] = ok[j] ? load4_cg(x + i * width + 4 * v) : zero4;
             da[j] = (delta && ok[j]) ? load4_cg(delta + i * width + 4 * v) : zero4;
+            if constexpr (PARTS) {
+                // all of a batch of four parts asked for before the first is added (one trip to L2 per batch, not per part)
+                for (int s0 = 0; s0 < parts.n; s0 += 4) {
+                    float4 pv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        pv[u] = (ok[j] && s0 + u < parts.n) ? load4_cg(parts.p + (s0 + u) * parts.stride + i * width + 4 * v) : zero4;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) da[j] = add4(da[j], pv[u]);
+                }
+            }
         }
         return i;
     };
@@ -299,11 +329,12 @@ __global__ void __launch_bounds__(512, VPT == 2 ? 2 : 1) add_norm_vec_kernel(con
 }
 
 template <typename T>
-static int launch_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias,
+static int launch_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias, AddParts parts,
                            float* resid_out, const float* gamma, const float* beta, float eps, int kind, int n_rows,
                            int width, void* out_act, float* out_f32, cudaStream_t s) {
     const size_t smem = (size_t)width * sizeof(float);
-    const bool vec = width % 4 == 0 && aligned16(x) && aligned16(delta) && aligned16(delta_bias) &&
+    const bool vec = width % 4 == 0 && aligned16(x) && aligned16(delta) && aligned16(delta_bias) && aligned16(parts.p) &&
+                     parts.stride % 4 == 0 &&
                      aligned16(resid_out) && aligned16(gamma) && aligned16(beta) && aligned16(out_act) &&
                      aligned16(out_f32);
     if (vec && width <= 8192) {
@@ -313,11 +344,13 @@ static int launch_add_norm(const float* x, const int* rows, const void* delta, c
         if (block < 64) block = 64;
         int grid = st_sm_count() * (vpt == 2 ? 4 : 2);
         if (grid > n_rows) grid = n_rows;
-        if (vpt == 2)
-            return st_launch_pdl("norm", add_norm_vec_kernel<T, 2>, dim3(grid), dim3(block), 0, s, x, rows, (const T*)delta,
-                                 delta_bias, resid_out, gamma, beta, eps, kind, width, n_rows, (T*)out_act, out_f32);
-        return st_launch_pdl("norm", add_norm_vec_kernel<T, 4>, dim3(grid), dim3(block), 0, s, x, rows, (const T*)delta,
-                             delta_bias, resid_out, gamma, beta, eps, kind, width, n_rows, (T*)out_act, out_f32);
+#define LAUNCH_VEC_NORM(VPT, PARTS)                                                                                          \
+        return st_launch_pdl("norm", add_norm_vec_kernel<T, VPT, PARTS>, dim3(grid), dim3(block), 0, s, x, rows, (const T*)delta, \
+                             delta_bias, parts, resid_out, gamma, beta, eps, kind, width, n_rows, (T*)out_act, out_f32)
+        if (vpt == 2) { if (parts.n) LAUNCH_VEC_NORM(2, true); LAUNCH_VEC_NORM(2, false); }
+        if (parts.n) LAUNCH_VEC_NORM(4, true);
+        LAUNCH_VEC_NORM(4, false);
+#undef LAUNCH_VEC_NORM
     }
     int block = vec ? (width / 8 + 31) / 32 * 32 : 256;   // vector path: two vectors per thread and round
     if (block > 512) block = 512;
@@ -327,22 +360,25 @@ static int launch_add_norm(const float* x, const int* rows, const void* delta, c
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return st_launch_pdl("norm", kern, dim3(n_rows), dim3(block), smem, s, x, rows, (const T*)delta, delta_bias, resid_out,
+    return st_launch_pdl("norm", kern, dim3(n_rows), dim3(block), smem, s, x, rows, (const T*)delta, delta_bias, parts, resid_out,
                          gamma, beta, eps, kind, width, (T*)out_act, out_f32);
 }
 
+// parts: n_parts further float addends [n_parts][rows of x][width], part_stride elements apart, or null / 0
 ST_EXPORT int st_add_norm(const float* x, const int* rows, const void* delta, const float* delta_bias,
-                          float* resid_out, const float* gamma, const float* beta, float eps, int kind,
+                          const float* parts, int n_parts, long long part_stride, float* resid_out, const float* gamma, const float* beta, float eps, int kind,
                           int n_rows, int width, void* out_act, float* out_f32, int dtype, void* stream) {
     if (n_rows <= 0) return 0;
     if (kind < 0 || kind > 2 || width <= 0) return ST_ERR_BAD_ARG;
     if ((size_t)width * sizeof(float) > 200 * 1024) return ST_ERR_TOO_LARGE;
+    if (n_parts < 0 || n_parts > 16 || (n_parts > 0 && !parts)) return ST_ERR_BAD_ARG;
+    const AddParts ap = {n_parts > 0 ? parts : nullptr, n_parts > 0 ? n_parts : 0, part_stride};
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == 0)
-        return launch_add_norm<float>(x, rows, delta, delta_bias, resid_out, gamma, beta, eps, kind, n_rows, width,
+        return launch_add_norm<float>(x, rows, delta, delta_bias, ap, resid_out, gamma, beta, eps, kind, n_rows, width,
                                       out_act, out_f32, s);
     if (dtype == 1)
-        return launch_add_norm<bf16>(x, rows, delta, delta_bias, resid_out, gamma, beta, eps, kind, n_rows, width,
+        return launch_add_norm<bf16>(x, rows, delta, delta_bias, ap, resid_out, gamma, beta, eps, kind, n_rows, width,
                                      out_act, out_f32, s);
     return ST_ERR_BAD_DTYPE;
 }

@@ -100,7 +100,9 @@ __device__ __forceinline__ uint4 ldg_stream(const bf16* p) {   // weights: read 
 // KFULL: K is a multiple of 32 (known when compiling: no test on k inside a block of 32)
 // XV: 0; or the float4 pieces of a row each thread normalises (K <= 1024 * XV): the norm in front; or -1: the
 //     residual sum behind (out is float and the product is added to what is there); or -2: all weights brought
-//     on chip before the wait (NT == 1, KFULL, no slices of k, 16 < K / 32 <= 64); -3: both of the last two
+//     on chip before the wait (NT == 1, KFULL, no slices of k, 16 < K / 32 <= 64); -3: both of the last two;
+//     -4: slices of k that do not meet: slice y leaves its sums, in float and without the bias, in out[y][M][N]
+//     (blocks of their own, no cluster; the norm kernel behind adds the parts in slice order)
 // out_f32: 0 bfloat16, 1 float
 template <int NT, bool QKV, bool KFULL, int XV>
 __global__ void __launch_bounds__(SK_THREADS, NT <= 2 ? 4 : 2)
@@ -112,6 +114,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     bf16* xs = reinterpret_cast<bf16*>(sk_dyn);      // XV > 0: the normalised rows, [M][K + SK_XPAD]
     constexpr bool PRE = XV == -2 || XV == -3;       // the k-blocks behind the first 2 x SK_WARPS in shared memory
     constexpr bool RESID = XV == -1 || XV == -3;     // the residual sum behind
+    constexpr bool PARTS = XV == -4;                 // slices of k leave their parts
     constexpr int REG_KB = 2 * SK_WARPS;
     bf16* ws = reinterpret_cast<bf16*>(sk_dyn);      // PRE: [16][K - 32 REG_KB + 32] (rows 64 bytes askew: no bank conflicts)
     const int ws_stride = K - 32 * REG_KB + 32;
@@ -349,7 +352,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
     }
     __syncthreads();
-    const int n_slices = gridDim.y;            // == cluster size when > 1
+    const int n_slices = PARTS ? 1 : gridDim.y;            // == cluster size when > 1
     if (n_slices > 1) {
         for (int i = threadIdx.x; i < 16 * 8 * NT; i += SK_THREADS) {
             const int r = i & 15, m = i >> 4;
@@ -377,6 +380,10 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
             for (int wi = 0; wi < SK_WARPS; ++wi) v += red[wi][r][m];
         }
         if (m >= M || n >= N) continue;
+        if (PARTS) {
+            reinterpret_cast<float*>(out)[((size_t)blockIdx.y * M + m) * N + n] = v;
+            continue;
+        }
         v += bias_pre;
         if (!QKV) {
             v = apply_act(v, act);
@@ -551,6 +558,25 @@ ST_EXPORT int st_gemm_skinny_norm(const float* x, const float* gamma, const floa
     QkvTarget none = {};
     if (out_f32 < 0 || out_f32 > 1) return ST_ERR_BAD_ARG;
     return launch_skinny_norm<false>(src, w, bias, out, M, N, K, act, out_f32, none, (cudaStream_t)stream);
+}
+
+// The slices of k a product of up to 8 tokens is cut into (st_gemm_skinny_parts_slices(N, K); 1: it is not cut) as
+// blocks of their own: parts [slices][M][N] float = the slices' sums of x . w^T, no bias.  No cluster and no early
+// start: the launch of a cluster and the meeting of its blocks through distributed shared memory cost 1.3 us per
+// product in a decode step, and the norm kernel that follows reads the parts in the trip to memory it makes anyway.
+ST_EXPORT int st_gemm_skinny_parts_slices(int N, int K) { return (K > 0 && K % 32 == 0 && N > 0) ? skinny_slices(N, K) : 1; }
+
+ST_EXPORT int st_gemm_skinny_parts(const void* x, const void* w, float* parts, int M, int N, int K, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 8) return ST_ERR_TOO_LARGE;
+    if (K <= 0 || K % 32) return ST_ERR_BAD_SIZE;
+    if (!aligned16(x) || !aligned16(w) || !parts) return ST_ERR_BAD_ARG;
+    const dim3 grid((N + 15) / 16, skinny_slices(N, K));
+    const QkvTarget none = {};
+    const NormSource no_norm = {};
+    gemm_skinny_kernel<1, false, true, -4><<<grid, SK_THREADS, 0, (cudaStream_t)stream>>>(
+        (const bf16*)x, (const bf16*)w, nullptr, parts, M, N, K, 0, 1, none, no_norm);
+    return st_launch_status();
 }
 
 // out [M, N] (float) += x . w^T + bias: the residual sum fused behind the product.

@@ -142,12 +142,18 @@ def add_norm(x: torch.Tensor, *, delta: Optional[torch.Tensor] = None, delta_bia
              resid_out: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None,
              beta: Optional[torch.Tensor] = None, eps: float = 1e-5, kind: str = "layernorm",
              rows: Optional[torch.Tensor] = None, out_act: Optional[torch.Tensor] = None,
-             out_f32: Optional[torch.Tensor] = None, act_dtype: Optional[torch.dtype] = None) -> None:
-    """s = x[i] + delta[i] + delta_bias; resid_out[i] = s; y = norm(s); out_act[r] = y; out_f32[r] = y.
+             out_f32: Optional[torch.Tensor] = None, act_dtype: Optional[torch.dtype] = None,
+             parts: Optional[torch.Tensor] = None) -> None:
+    """s = x[i] + (delta[i] + parts[0][i] + parts[1][i] + ...) + delta_bias; resid_out[i] = s; y = norm(s);
+    out_act[r] = y; out_f32[r] = y.
 
-    ``x`` is the float32 residual stream; ``i = rows[r]`` when ``rows`` is given, else ``r``.
+    ``x`` is the float32 residual stream; ``i = rows[r]`` when ``rows`` is given, else ``r``.  ``parts``: float32
+    [n, rows of x, width], further addends (the slices of k of a product, see ``linear_parts``).
     """
     assert x.dtype == torch.float32 and x.is_contiguous()
+    if parts is not None:
+        assert parts.dtype == torch.float32 and parts.dim() == 3 and parts.shape[1:] == x.shape
+        assert parts.stride(2) == 1 and parts.stride(1) == x.shape[1]
     width = x.shape[1]
     n = rows.numel() if rows is not None else x.shape[0]
     if out_act is not None:
@@ -158,7 +164,9 @@ def add_norm(x: torch.Tensor, *, delta: Optional[torch.Tensor] = None, delta_bia
         code = 0 if act_dtype in (None, torch.float32) else 1
     if delta is not None and out_act is not None:
         assert delta.dtype == out_act.dtype
-    _check(lib().st_add_norm(_p(x), _p(rows), _p(delta), _p(delta_bias), _p(resid_out), _p(gamma), _p(beta),
+    _check(lib().st_add_norm(_p(x), _p(rows), _p(delta), _p(delta_bias), _p(parts),
+                             parts.shape[0] if parts is not None else 0,
+                             ctypes.c_longlong(parts.stride(0) if parts is not None else 0), _p(resid_out), _p(gamma), _p(beta),
                              _f(eps), NORM_CODES[kind], n, width, _p(out_act), _p(out_f32), code, _stream()),
            "add_norm")
 
@@ -302,6 +310,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
 FUSED_MAX_ROWS = 8
 FUSE_NORM = False
 FUSE_RESIDUAL = True
+LINEAR_PARTS = True       # a product cut over k leaves its slices' sums for the next norm kernel (decode steps)
+UNCUT_MAX_INNER = 2048    # up to this inner dimension ``linear_add`` runs uncut with its weights on chip: no parts
 
 
 def fused_norm_applies(n_rows: int, k: int, w: torch.Tensor) -> bool:
@@ -313,17 +323,22 @@ def fused_norm_applies(n_rows: int, k: int, w: torch.Tensor) -> bool:
 
 def norm_linear(x: torch.Tensor, kind: str, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor], eps: float,
                 w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
-                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                out_dtype: Optional[torch.dtype] = None, delta: Optional[torch.Tensor] = None,
+                delta_bias: Optional[torch.Tensor] = None, parts: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(norm(x) @ w.T + bias) for at most FUSED_MAX_ROWS float32 rows x (the residual stream) and bfloat16
     w [out, in]: the norm of ``add_norm`` (statistics in float, two passes; its result rounded to bfloat16 as
-    ``add_norm`` stores it) in front of the weight-streaming product, in one kernel."""
+    ``add_norm`` stores it) in front of the weight-streaming product, in one kernel.  ``delta`` / ``delta_bias`` /
+    ``parts``: what is still to be added to x (``add_norm`` adds it, x is updated); only with FUSE_NORM off."""
     assert x.dtype == torch.float32 and x.is_contiguous() and w.is_contiguous() and x.shape[1] == w.shape[1]
     n, k = x.shape
     m = w.shape[0]
     out_dtype = out_dtype or w.dtype
+    pending = delta is not None or delta_bias is not None or parts is not None
+    assert not (FUSE_NORM and pending)
     if not FUSE_NORM:
         h = torch.empty((n, k), dtype=w.dtype, device=x.device)
-        add_norm(x, gamma=gamma, beta=beta, eps=eps, kind=kind, out_act=h)
+        add_norm(x, delta=delta, delta_bias=delta_bias, parts=parts, resid_out=x if pending else None, gamma=gamma,
+                 beta=beta, eps=eps, kind=kind, out_act=h)
         return gemm_skinny(h, w, bias, act, out_dtype)
     out = torch.empty((n, m), dtype=out_dtype, device=x.device)
     _check(lib().st_gemm_skinny_norm(_p(x), _p(gamma), _p(beta), _f(eps), NORM_CODES[kind], _p(w), _p(bias), _p(out),
@@ -345,18 +360,51 @@ def linear_add(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], x
            "linear_add")
 
 
+_parts_scratch = {}
+
+
+def linear_parts_slices(n_rows: int, w: torch.Tensor) -> int:
+    """Into how many slices of k ``linear_parts`` cuts a product with w [out, in] for n_rows tokens (1: it does not
+    apply: more than FUSED_MAX_ROWS tokens, weights that are not bfloat16 on the device, an inner dimension that is
+    no multiple of 32, or a product that is not cut)."""
+    if not (LINEAR_PARTS and w.is_cuda and w.dtype == torch.bfloat16 and 1 <= n_rows <= FUSED_MAX_ROWS):
+        return 1
+    return int(lib().st_gemm_skinny_parts_slices(w.shape[0], w.shape[1]))
+
+
+def linear_parts(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """The slices' sums of a @ w.T for at most FUSED_MAX_ROWS bfloat16 rows: float32 [slices, rows, out], to be
+    added in slice order (``add_norm(parts=...)`` does, in the kernel that reads the residual rows anyway).  The
+    result lives in a buffer that the next call for the same sizes overwrites."""
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
+    assert a.shape[1] == w.shape[1]
+    n, m = a.shape[0], w.shape[0]
+    slices = linear_parts_slices(n, w)
+    key = (a.device.index, slices, m)
+    if key not in _parts_scratch:
+        _parts_scratch[key] = torch.zeros(slices * FUSED_MAX_ROWS * m, dtype=torch.float32, device=a.device)
+    parts = _parts_scratch[key][:slices * n * m].view(slices, n, m)
+    _check(lib().st_gemm_skinny_parts(_p(a), _p(w), _p(parts), n, m, a.shape[1], _stream()), "linear_parts")
+    return parts
+
+
 def norm_qkv_linear_to_cache(x: torch.Tensor, kind: str, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor],
                              eps: float, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                              pool: torch.Tensor, layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
                              slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, d: int,
-                             status: torch.Tensor, write_kv: bool = True) -> None:
-    """``qkv_linear_to_cache`` of norm(x) for float32 rows x: norm, product, bias and cache write in one kernel."""
+                             status: torch.Tensor, write_kv: bool = True, delta: Optional[torch.Tensor] = None,
+                             delta_bias: Optional[torch.Tensor] = None, parts: Optional[torch.Tensor] = None) -> None:
+    """``qkv_linear_to_cache`` of norm(x) for float32 rows x: norm, product, bias and cache write in one kernel.
+    ``delta`` / ``delta_bias`` / ``parts``: as in ``norm_linear``."""
     assert x.dtype == torch.float32 and x.is_contiguous() and w.is_contiguous() and pool.dtype == torch.bfloat16
     num_pages, n_layers, _, pnkv, page_size, pd = pool.shape
     assert pnkv == nkv and pd == d and w.shape[0] == (nh + 2 * nkv) * d
+    pending = delta is not None or delta_bias is not None or parts is not None
+    assert not (FUSE_NORM and pending)
     if not FUSE_NORM:
         h = torch.empty(x.shape, dtype=w.dtype, device=x.device)
-        add_norm(x, gamma=gamma, beta=beta, eps=eps, kind=kind, out_act=h)
+        add_norm(x, delta=delta, delta_bias=delta_bias, parts=parts, resid_out=x if pending else None, gamma=gamma,
+                 beta=beta, eps=eps, kind=kind, out_act=h)
         return qkv_linear_to_cache(h, w, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv,
                                    d, status, write_kv)
     _check(lib().st_gemm_skinny_norm_qkv(_p(x), _p(gamma), _p(beta), _f(eps), NORM_CODES[kind], _p(w), _p(bias),

@@ -249,19 +249,28 @@ class Attention(Mixer):
         plan = ctx.plan(PagedAttentionPlan.name)
         return plan.n_items == 0 and plan.n_tiles > 0
 
-    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any) -> bool:
-        """x += attention(norm(x)) for a step of a few tokens in three kernels: norm + q|k|v product + bias +
-        cache write; attention; output product + bias + residual sum."""
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any,
+                              pending: Optional[Delta] = None) -> Any:
+        """x <- (x + pending) + attention(norm(x + pending)) for a step of a few tokens in three or four kernels: norm
+        (which adds what is pending) and q|k|v product + bias + cache write; attention; output product + bias +
+        residual sum."""
         if getattr(self.qk_position, "apply_qk", None) is not None or norm.kind not in ops.NORM_CODES:
             return False
-        if not ops.fused_norm_applies(x.shape[0], self.hidden, self.w_qkv):
+        if not ops.fused_norm_applies(x.shape[0], self.hidden, self.w_qkv) or (pending is not None and ops.FUSE_NORM):
             return False
         q = torch.empty((x.shape[0], self.nh * self.d), dtype=self.w_qkv.dtype, device=x.device)
         ops.norm_qkv_linear_to_cache(x, norm.kind, norm.gamma, norm.beta, norm.eps, self.w_qkv, self.b_qkv, q,
                                      cache.pool, cache.layer, ctx.positions, ctx.seq_of_token, ctx.slots,
                                      cache.block_table, self.nh, self.nkv, self.d, ctx.status,
-                                     write_kv=cache.writable)
+                                     write_kv=cache.writable,
+                                     delta=pending.value if pending else None,
+                                     delta_bias=pending.bias if pending else None,
+                                     parts=pending.parts if pending else None)
         o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
+        if (not ops.FUSE_NORM and ops.linear_parts_slices(x.shape[0], self.w_o) > 1
+                and self.w_o.shape[1] > ops.UNCUT_MAX_INNER):
+            # the output product would be cut over k: its slices' sums are left for the next norm kernel
+            return Delta(None, self.b_o, ops.linear_parts(o, self.w_o))
         ops.linear_add(o, self.w_o, self.b_o, x)
         return True
 

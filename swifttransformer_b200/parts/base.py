@@ -19,7 +19,7 @@ Mixer.cache_spec()        -> PagedKVSpec | StateSpec | None
 Mixer.step_plan()         -> StepPlan | None  (host work once per step, see StepPlan)
 Mixer.forward(h, ctx, cache) -> Delta         h: [N, width] activations
 FeedForward.forward(h, ctx)  -> Delta
-Mixer.forward_into_residual(x, norm, ctx, cache), FeedForward.forward_into_residual(x, norm, ctx) -> bool
+Mixer.forward_into_residual(x, norm, ctx, cache, pending), FeedForward.forward_into_residual(x, norm, ctx, pending)
                           optional: the whole sub-layer with its norm and residual sum fused in, in place
 Norm.apply(x, delta, ...)    -> see parts.norm
 PositionEncoding.table()     -> (table, offset) for encodings added to the hidden state
@@ -42,8 +42,12 @@ from ..weights.spec import ParamSpec
 
 @dataclasses.dataclass
 class Delta:
-    value: torch.Tensor                 # [N, width], activation dtype
+    """What a sub-layer leaves to be added to the residual stream: a tensor in the activation dtype, a bias,
+    and/or float32 parts [n, N, width] to be added in order (the slices of k of a product that did not meet
+    in the product's own kernel)."""
+    value: Optional[torch.Tensor]        # [N, width], activation dtype, or None
     bias: Optional[torch.Tensor] = None  # [width] float32
+    parts: Optional[torch.Tensor] = None  # [n, N, width] float32
 
 
 @dataclasses.dataclass(frozen=True)
@@ -136,11 +140,13 @@ class Mixer(Part):
     def forward(self, h: torch.Tensor, ctx: Any, cache: Any) -> Delta:
         raise NotImplementedError
 
-    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any) -> bool:
-        """Optional fast path of a pre-norm block: x <- x + mixer(norm(x)) in place on the float32 residual
-        rows x, with the norm (a parts.norm.Norm: its kind, gain, shift and eps) fused into the mixer's first
-        kernel and the residual sum into its last.  Return False, having changed nothing, when it does not
-        apply to this step; the block then calls ``norm.apply`` and ``forward``."""
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, cache: Any,
+                              pending: Optional[Delta] = None) -> Any:
+        """Optional fast path of a pre-norm block: x <- (x + pending) + mixer(norm(x + pending)) in place on the
+        float32 residual rows x, with the norm (a parts.norm.Norm: its kind, gain, shift and eps) and the sum with
+        ``pending`` (what the sub-layer before left to be added) in the mixer's first kernel and the residual sum
+        in its last.  Returns False, having changed nothing, when it does not apply to this step (the block then
+        calls ``norm.apply`` and ``forward``); True when x is complete; or a Delta that is still to be added to x."""
         return False
 
 
@@ -148,8 +154,9 @@ class FeedForward(Part):
     def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
         raise NotImplementedError
 
-    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any) -> bool:
-        """Optional fast path of a pre-norm block: x <- x + feed_forward(norm(x)) in place (see Mixer)."""
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, pending: Optional[Delta] = None) -> Any:
+        """Optional fast path of a pre-norm block: x <- (x + pending) + feed_forward(norm(x + pending)) in place
+        (see Mixer: False, True, or a Delta still to be added)."""
         return False
 
 

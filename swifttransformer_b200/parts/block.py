@@ -37,6 +37,7 @@ class ResidualStream:
         out = torch.empty((n, self.x.shape[1]), dtype=self.act_dtype, device=self.x.device)
         p = self.pending
         ops.add_norm(self.x, delta=p.value if p else None, delta_bias=p.bias if p else None,
+                     parts=p.parts if p else None,
                      resid_out=self.x if (p is not None and rows is None) else None,
                      kind="none", rows=rows, out_act=out)
         if rows is None:
@@ -63,12 +64,18 @@ class PreNormBlock(Block):
         # result left pending for the next norm kernel to add.
         x, pending = stream.x, stream.pending
         low = stream.act_dtype != torch.float32
-        if not (low and pending is None and self.mixer.forward_into_residual(x, self.norm1, ctx, cache)):
+        done = self.mixer.forward_into_residual(x, self.norm1, ctx, cache, pending) if low else False
+        if done is False:
             h = self.norm1.apply(x, pending, act_dtype=stream.act_dtype)
             pending = self.mixer.forward(h, ctx, cache)
-        if not (low and pending is None and self.feed_forward.forward_into_residual(x, self.norm2, ctx)):
+        else:
+            pending = None if done is True else done
+        done = self.feed_forward.forward_into_residual(x, self.norm2, ctx, pending) if low else False
+        if done is False:
             h = self.norm2.apply(x, pending, act_dtype=stream.act_dtype)
             pending = self.feed_forward.forward(h, ctx)
+        else:
+            pending = None if done is True else done
         stream.pending = pending
         stream.act = None
 

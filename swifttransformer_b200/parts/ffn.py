@@ -44,14 +44,19 @@ class DenseFFN(FeedForward):
         u = ops.linear(h, self.w1, self.b1, self.activation, bias_bf16=self.b1_bf16)
         return Delta(ops.linear(u, self.w2), self.b2)
 
-    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any) -> bool:
-        """x += ffn(norm(x)) for a step of a few tokens in two kernels: norm + fc1 + bias + activation;
-        fc2 + bias + residual sum."""
+    def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, pending: Optional[Delta] = None) -> Any:
+        """x <- (x + pending) + ffn(norm(x + pending)) for a step of a few tokens: norm (which adds what is pending)
+        and fc1 + bias + activation; then fc2 + bias + residual sum in one kernel, or, where that kernel would cut
+        fc2 over k, the slices' sums left as a Delta for the next norm kernel to add."""
         if norm.kind not in ops.NORM_CODES or not ops.fused_norm_applies(x.shape[0], self.hidden, self.w1):
             return False
-        if self.inner % 8:
+        if self.inner % 8 or (pending is not None and ops.FUSE_NORM):
             return False
-        u = ops.norm_linear(x, norm.kind, norm.gamma, norm.beta, norm.eps, self.w1, self.b1, self.activation)
+        u = ops.norm_linear(x, norm.kind, norm.gamma, norm.beta, norm.eps, self.w1, self.b1, self.activation,
+                            delta=pending.value if pending else None, delta_bias=pending.bias if pending else None,
+                            parts=pending.parts if pending else None)
+        if not ops.FUSE_NORM and ops.linear_parts_slices(x.shape[0], self.w2) > 1 and self.inner > ops.UNCUT_MAX_INNER:
+            return Delta(None, self.b2, ops.linear_parts(u, self.w2))
         ops.linear_add(u, self.w2, self.b2, x)
         return True
 

@@ -41,6 +41,7 @@ class Norm(Part):
             x,
             delta=delta.value if delta is not None else None,
             delta_bias=delta.bias if delta is not None else None,
+            parts=delta.parts if delta is not None else None,
             resid_out=x if (update_residual and not normalise_residual and rows is None and delta is not None) else None,
             gamma=self.gamma, beta=self.beta, eps=self.eps, kind=self.kind, rows=rows,
             out_act=out, out_f32=x if (normalise_residual and rows is None) else None)

@@ -38,11 +38,15 @@ def add_positions(x, positions, pos_table, pos_offset, out):
 
 
 def add_norm(x, *, delta=None, delta_bias=None, resid_out=None, gamma=None, beta=None, eps=1e-5,
-             kind="layernorm", rows=None, out_act=None, out_f32=None, act_dtype=None):
+             kind="layernorm", rows=None, out_act=None, out_f32=None, act_dtype=None, parts=None):
     idx = rows.long() if rows is not None else torch.arange(x.shape[0])
     s = x[idx].float()
-    if delta is not None:
-        s = s + delta[idx].float()
+    if delta is not None or parts is not None:
+        d = delta[idx].float() if delta is not None else torch.zeros_like(s)
+        if parts is not None:
+            for p in parts:
+                d = d + p[idx].float()
+        s = s + d
     if delta_bias is not None:
         s = s + delta_bias.float()
     if resid_out is not None:
@@ -108,30 +112,54 @@ SKINNY_MAX_ROWS = 8
 
 
 FUSED_MAX_ROWS = 8
+UNCUT_MAX_INNER = 2048
+FUSE_NORM = False
 
 
 def fused_norm_applies(n_rows, k, w):
     return False        # the CPU runs of the engine take the unfused path
 
 
-def _norm_rows(x, kind, gamma, beta, eps, dtype):
+def _norm_rows(x, kind, gamma, beta, eps, dtype, delta=None, delta_bias=None, parts=None):
     out = torch.empty(x.shape, dtype=dtype)
-    add_norm(x, gamma=gamma, beta=beta, eps=eps, kind=kind, out_act=out)
+    pending = delta is not None or delta_bias is not None or parts is not None
+    add_norm(x, delta=delta, delta_bias=delta_bias, parts=parts, resid_out=x if pending else None, gamma=gamma,
+             beta=beta, eps=eps, kind=kind, out_act=out)
     return out
 
 
-def norm_linear(x, kind, gamma, beta, eps, w, bias=None, act="none", out_dtype=None):
-    return linear(_norm_rows(x, kind, gamma, beta, eps, w.dtype), w, bias, act, out_dtype or w.dtype)
+def norm_linear(x, kind, gamma, beta, eps, w, bias=None, act="none", out_dtype=None, delta=None, delta_bias=None,
+                parts=None):
+    return linear(_norm_rows(x, kind, gamma, beta, eps, w.dtype, delta, delta_bias, parts), w, bias, act,
+                  out_dtype or w.dtype)
 
 
 def linear_add(a, w, bias, x):
     x += linear(a, w, bias, "none", torch.float32)
 
 
+def linear_parts_slices(n_rows, w):
+    return 1            # the CPU runs of the engine do not cut products
+
+
+def linear_parts(a, w, slices=4):
+    """The sums of a @ w.T over `slices` equal ranges of 32-element blocks of the inner dimension, float32
+    [slices, rows, out] (the kernel's cut: blocks of 32 dealt out in equal runs, the last run shorter)."""
+    k = a.shape[1]
+    nkb = (k + 31) // 32
+    per = (nkb + slices - 1) // slices
+    out = torch.zeros(slices, a.shape[0], w.shape[0], dtype=torch.float32)
+    for s in range(slices):
+        lo, hi = min(k, s * per * 32), min(k, (s + 1) * per * 32)
+        if lo < hi:
+            out[s] = (a[:, lo:hi].double() @ w[:, lo:hi].double().T).float()
+    return out
+
+
 def norm_qkv_linear_to_cache(x, kind, gamma, beta, eps, w, bias, q_out, pool, layer, positions, seq_of_token, slots,
-                             block_table, nh, nkv, d, status, write_kv=True):
-    qkv_linear_to_cache(_norm_rows(x, kind, gamma, beta, eps, w.dtype), w, bias, q_out, pool, layer, positions,
-                        seq_of_token, slots, block_table, nh, nkv, d, status, write_kv)
+                             block_table, nh, nkv, d, status, write_kv=True, delta=None, delta_bias=None, parts=None):
+    qkv_linear_to_cache(_norm_rows(x, kind, gamma, beta, eps, w.dtype, delta, delta_bias, parts), w, bias, q_out, pool,
+                        layer, positions, seq_of_token, slots, block_table, nh, nkv, d, status, write_kv)
 
 
 def qkv_linear_to_cache(h, w, bias, q_out, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d,
@@ -283,7 +311,7 @@ def sample(logits, temperatures, top_k, seeds, counters, out=None):
     return res
 
 
-ALL = ["sm_count", "fused_norm_applies", "norm_linear", "linear_add", "norm_qkv_linear_to_cache", "embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
+ALL = ["sm_count", "fused_norm_applies", "norm_linear", "linear_add", "linear_parts_slices", "linear_parts", "norm_qkv_linear_to_cache", "embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain", "gemm_skinny", "gemm_stream_tc", "kernel_status",
        "qkv_linear_to_cache", "qkv_to_cache",
        "attention_plain", "attention_decode_scratch", "decode_warps", "attention_decode", "attention_prefill_tile_rows",
        "attention_prefill", "argmax", "sample", "uniform"]

@@ -622,6 +622,56 @@ def test_linear_add_uncut_with_all_weights_on_chip(shape):
     close(got, ref, torch.float32, "linear_add on chip", rel=2e-5)
 
 
+@pytest.mark.parametrize("shape", [(8, 2048, 8192), (1, 2048, 8192), (5, 4096, 4096), (3, 1000, 2080), (8, 96, 4096)])
+def test_linear_parts_and_the_norm_that_adds_them(shape):
+    """A product cut over k leaves the slices' sums as float parts (no cluster, no bias); the norm kernel behind adds
+    them in slice order with the bias and the residual rows: together they equal x + a . w^T + bias, normalised."""
+    n, m, k = shape
+    a, w, b = rnd((n, k), torch.bfloat16, 195), rnd((m, k), torch.bfloat16, 196, 0.1), rnd((m,), torch.float32, 197)
+    x = rnd((n, m), torch.float32, 198) * 3
+    slices = ops.linear_parts_slices(n, w.to(DEV))
+    assert slices == int(ops.lib().st_gemm_skinny_parts_slices(m, k))
+    if slices == 1:
+        pytest.skip("this product is not cut on this GPU")
+    parts = ops.linear_parts(a.to(DEV), w.to(DEV))
+    assert parts.shape == (slices, n, m) and parts.dtype == torch.float32
+    ref_parts = cpu_ops.linear_parts(a, w, slices)
+    close(parts, ref_parts, torch.float32, "linear_parts", rel=2e-5)
+    gamma, beta = 1 + 0.2 * rnd((m,), torch.float32, 199), 0.3 * rnd((m,), torch.float32, 200)
+    for width_ok in (True,):
+        got_x, got_h = x.to(DEV).clone(), torch.empty((n, m), dtype=torch.bfloat16, device=DEV)
+        ops.add_norm(got_x, parts=parts, delta_bias=b.to(DEV), resid_out=got_x, gamma=gamma.to(DEV), beta=beta.to(DEV),
+                     eps=1e-5, kind="layernorm", out_act=got_h)
+        ref_x, ref_h = x.clone(), torch.empty((n, m), dtype=torch.bfloat16)
+        cpu_ops.add_norm(ref_x, parts=ref_parts, delta_bias=b, resid_out=ref_x, gamma=gamma, beta=beta, eps=1e-5,
+                         kind="layernorm", out_act=ref_h)
+        close(got_x, ref_x, torch.float32, "residual rows with parts", rel=2e-5)
+        close(got_x, x.double() + cpu_ops.linear(a, w, b, "none", torch.float32).double(), torch.float32,
+              "parts add up to the product", rel=3e-5)
+        close(got_h, ref_h, torch.bfloat16, "norm of rows with parts", rel=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [40, 777, 2048, 7168])
+def test_add_norm_with_parts_and_a_delta_and_a_row_gather(dtype, width):
+    """Every form of the norm kernel (row in shared memory, two or four vectors per thread in registers) with float
+    parts beside a delta in the activation type, a bias, and a gather of rows (the final norm of a step)."""
+    n, n_parts = 9, 3
+    x = rnd((n, width), torch.float32, 205) * 2
+    delta, bias = rnd((n, width), dtype, 206), rnd((width,), torch.float32, 207)
+    parts = rnd((n_parts, n, width), torch.float32, 208)
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32)
+    gamma, beta = 1 + 0.2 * rnd((width,), torch.float32, 209), 0.3 * rnd((width,), torch.float32, 210)
+    for kind in ("layernorm", "rmsnorm", "none"):
+        got = torch.empty((3, width), dtype=dtype, device=DEV)
+        ops.add_norm(x.to(DEV), delta=delta.to(DEV), delta_bias=bias.to(DEV), parts=parts.to(DEV), gamma=gamma.to(DEV),
+                     beta=beta.to(DEV), eps=1e-5, kind=kind, rows=rows.to(DEV), out_act=got)
+        ref = torch.empty((3, width), dtype=dtype)
+        cpu_ops.add_norm(x.clone(), delta=delta, delta_bias=bias, parts=parts, gamma=gamma, beta=beta, eps=1e-5, kind=kind,
+                         rows=rows, out_act=ref)
+        close(got, ref, dtype, f"add_norm with parts, {kind}", rel=2e-5 if dtype == torch.float32 else 1e-2)
+
+
 def test_qkv_linear_to_cache_with_all_weights_on_chip():
     """The fused q|k|v product at a size that takes the on-chip variant (6144 features, 1024 inner elements, 7 tokens
     of which one is padding): queries and pages as the plain reference leaves them."""
