@@ -91,12 +91,15 @@ def test_a_long_prompt_whole_in_portions_and_with_a_decoded_tail(big_models, nam
         assert s.cache.free_pages == s.cache.total_pages
 
 
-@pytest.mark.parametrize("dtype,n_requests", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
+@pytest.mark.parametrize("dtype,n_requests", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64), ("bfloat16", 5),
+                                              ("bfloat16", 8), ("bfloat16", 2)])
 @pytest.mark.parametrize("name", list(SIZES))
 def test_many_requests_decoding_together(big_models, name, dtype, n_requests):
-    """16 and 64 requests of 300 to 520 tokens: prompts several to a step, then the last 8 tokens of all of
+    """2 to 64 requests of 300 to 520 tokens: prompts several to a step, then the last 8 tokens of all of
     them together, one by one.  Eight different token sequences (neighbouring requests never share one); every
-    request has pages of its own."""
+    request has pages of its own.  Up to 8 requests the decode steps take the weight-streaming products (weights on
+    chip before their wait, a product cut over k leaving its parts to the next norm; 5 requests run in a step
+    recorded for 8), beyond that the library products."""
     model_dir, cfg, w = big_models(name)
     tail = 8
     lens = [300, 517, 411, 352, 520, 333, 478, 401]
