@@ -23,6 +23,12 @@
 //     block leaves its result in `partial` and the split that arrives last merges them, in split
 //     order (same protocol and layout as attention_decode.cu).
 //
+//   * Optionally the kernel takes the q|k|v product as the library left it (rows of q, k and v features, bias
+//     included) instead of queries: it reads its queries from there, copies the keys and values of this step's own
+//     tokens from those rows into its shared-memory stages (asynchronously, like rows of the cache), and once its own
+//     token's rows have landed writes them from there into their page.  A decode step of more tokens than the
+//     weight-streaming product serves then has no separate cache-write kernel.
+//
 // Rows of a group past the end of the key range are zero-filled, never read, and masked.
 // Same mathematics as src/csrc/kernel/fused_decoding_stage_attention_mha.cu:159-318 in the
 // reference (scalar arithmetic there, one warp per head).
@@ -38,9 +44,18 @@
 // of a warp's five groups one after the other behind them (3.5 us per layer at batch 1).
 template <int DMAX, bool DEEP> struct DmStages { static constexpr int value = DEEP ? 6 : (DMAX == 64 ? 3 : 2); };
 
+// The q|k|v form: `q` is the product [tokens, (nh + 2 nkv) d] (q features, then k, then v; bias included),
+// `q_stride` the elements of one of its rows.  Keys from the request's `start_pos` on are this step's: the token at
+// position p of the request is row t - (pos - p) (a request's tokens of a step are consecutive rows in the order of
+// their positions).  on == 0: `q` holds queries only, [tokens, nh d], and every key is in the cache.
+struct DmQkv {
+    int q_stride, num_pages, write_kv, on;       // on: host side only (which variant is launched)
+};
+
 // head_dim <= DMAX, a multiple of 16; FULL: head_dim == DMAX, known when compiling (no tests on it in the loops)
-template <int DMAX, bool FULL, int DM_WARPS, bool DEEP>
-__global__ void __launch_bounds__(DM_WARPS * 32)
+// QKV: the q|k|v form (a variant of its own, so that the plain form keeps its registers)
+template <int DMAX, bool FULL, int DM_WARPS, bool DEEP, bool QKV>
+__global__ void __launch_bounds__(DM_WARPS * 32, QKV ? (DM_WARPS == 4 ? (DMAX == 64 ? 4 : 3) : (DMAX == 64 ? 2 : 1)) : 0)
 attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, bf16* __restrict__ out,
                             float* __restrict__ partial, const int* __restrict__ items,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -48,7 +63,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             const int* __restrict__ block_table, int max_pages,
                             int n_layers, int layer, int nh, int nkv, int d_arg, int page_size, int page_shift,
                             float scale_log2, int window, int n_splits, int* __restrict__ counters,
-                            int* __restrict__ status) {
+                            int* __restrict__ status, DmQkv qkv) {
     const int d = FULL ? DMAX : d_arg;
     // page_shift: log2(page_size) if that is a power of two, else -1
     constexpr int STAGES = DmStages<DMAX, DEEP>::value;
@@ -78,6 +93,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     // keys below this position were written by earlier steps: they may be read before the wait for the
     // kernel before this one (which writes this step's keys and values); null: none may
     const int old_hi = start_pos ? start_pos[seq] : 0;
+    const int new_lo = QKV ? old_hi : 0x7fffffff;          // keys from here on come from the q|k|v rows of this step
     const int* bt = block_table + (size_t)slot * max_pages;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int hi = pos + 1;
@@ -141,7 +157,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     auto load_group = [&](int i, int stage) {
         const uint32_t dk = my_stages + stage * STAGE_BYTES;
         const int key0 = k_lo + (warp + i * DM_WARPS) * DM_KEYS;
-        if (one_page) {
+        if (one_page && (!QKV || key0 + DM_KEYS <= new_lo)) {
             const int pg = page_shift >= 0 ? key0 >> page_shift : key0 / page_size;
             const int page = s_pages[pg - p_lo];
             const bool page_ok = page >= 0;      // a hole in the block table: zeros instead of an access before the pool
@@ -161,15 +177,21 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             if (ld_row[j] < 0) continue;
             const int key = key0 + ld_row[j];
             bool ok = key < k_hi;
-            const bf16* src = pool;
-            if (ok) {
+            const bf16 *src = pool, *vsrc = pool;
+            if (QKV && ok && key >= new_lo) {    // a key of this step: from its token's row of the product
+                src = q + (size_t)(t - (pos - key)) * qkv.q_stride + (size_t)(nh + kvh) * d + ld_col[j];
+                vsrc = src + (size_t)nkv * d;
+            } else if (ok) {
                 const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
                 const int page = s_pages[pg - p_lo];
                 ok = page >= 0;                  // a hole in the block table: zeros instead of an access before the pool
-                if (ok) src = kbase + (size_t)page * page_stride + (key - pg * page_size) * d + ld_col[j];
+                if (ok) {
+                    src = kbase + (size_t)page * page_stride + (key - pg * page_size) * d + ld_col[j];
+                    vsrc = src + kv_stride;
+                }
             }
             cp_async16_s(dk + ld_off[j], src, ok);
-            cp_async16_s(dk + V_BYTES + ld_off[j], ok ? src + kv_stride : pool, ok);
+            cp_async16_s(dk + V_BYTES + ld_off[j], vsrc, ok);
         }
     };
     // The first stages: groups whose keys all lie below old_hi were written by earlier steps and are asked
@@ -189,7 +211,8 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     const int g = lane >> 2, t4 = lane & 3;
     uint32_t qb[DMAX / 16][2];
     {
-        const bf16* qrow = q + ((size_t)t * nh + h0 + min(g, n_heads - 1)) * d + 2 * t4;
+        const size_t feat = (size_t)(h0 + min(g, n_heads - 1)) * d + 2 * t4;
+        const bf16* qrow = q + (size_t)t * (QKV ? qkv.q_stride : nh * d) + feat;
 #pragma unroll
         for (int kk = 0; kk < DMAX / 16; ++kk) {
             qb[kk][0] = qb[kk][1] = 0u;
@@ -232,6 +255,22 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             }
         }
         const int key0 = k_lo + (warp + i * DM_WARPS) * DM_KEYS;
+        if constexpr (QKV) {
+            // this block's own token's key and value rows have landed with this group: from the stage into their page
+            if (pos >= key0 && pos < key0 + DM_KEYS && qkv.write_kv && blockIdx.y % chunks_per_kv == 0) {
+                const int pg = page_shift >= 0 ? pos >> page_shift : pos / page_size;
+                const int page = s_pages[pg - p_lo];
+                if (page < 0 || page >= qkv.num_pages) {
+                    if (status) *status = 1;
+                } else if (lane < 2 * chunks) {
+                    const int kv = lane >= chunks, c = lane - kv * chunks, r = pos - key0;
+                    const uint4 v = *reinterpret_cast<const uint4*>(
+                        tile_ptr<DMAX>(sKV + (size_t)(warp * STAGES + i % STAGES) * STAGE_ELEMS + kv * DM_KEYS * DMAX, r, c));
+                    bf16* dst = const_cast<bf16*>(kbase) + (size_t)page * page_stride + kv * kv_stride + (pos - pg * page_size) * d + c * 8;
+                    *reinterpret_cast<uint4*>(dst) = v;
+                }
+            }
+        }
         if (key0 + DM_KEYS > k_hi) {       // the range's last group: keys past its end do not count
             if (key0 + g >= k_hi) s_acc[0] = s_acc[1] = -INFINITY;
             if (key0 + g + 8 >= k_hi) s_acc[2] = s_acc[3] = -INFINITY;
@@ -370,14 +409,11 @@ static size_t dm_smem_bytes(int d, int block_pages, int warps) {
 
 ST_EXPORT int st_attention_decode_mma_applies(int d) { return d > 0 && d % 16 == 0 && d <= 128; }
 
-// Same arguments and scratch layout as st_attention_decode, and the number of warps per block (4 or 8);
-// start_pos (per request: the tokens it had in the cache before this step, or null) tells which keys earlier
-// steps wrote, so that their copies can start before the kernel before this one has finished.
-ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out, float* partial, const int* items,
-                                      int n_items, const int* positions, const int* seq_of_token, const int* slots,
-                                      const int* start_pos, const int* block_table, int max_pages, int n_layers,
-                                      int layer, int nh, int nkv, int d, int page_size, float scale, int window,
-                                      int n_splits, int* counters, int warps, int* status, void* stream) {
+static int dm_launch(const void* q, const DmQkv& qkv, const void* pool, void* out, float* partial, const int* items,
+                     int n_items, const int* positions, const int* seq_of_token, const int* slots,
+                     const int* start_pos, const int* block_table, int max_pages, int n_layers,
+                     int layer, int nh, int nkv, int d, int page_size, float scale, int window,
+                     int n_splits, int* counters, int warps, int* status, void* stream) {
     if (n_items <= 0) return 0;
     if (warps != 4 && warps != 8) return ST_ERR_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1 || n_splits > 65535) return ST_ERR_BAD_ARG;
@@ -394,29 +430,30 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
         if (page_size == (1 << b)) page_shift = b;
     int rc;
     // one block per SM at most: the deep ring
-    const bool deep = (long long)n_items * gy * n_splits <= st_sm_count();
-#define LAUNCH_DM(DMAX, FULL, WARPS, DEEP)                                                                           \
+    const bool deep = !qkv.on && (long long)n_items * gy * n_splits <= st_sm_count();
+#define LAUNCH_DM(DMAX, FULL, WARPS, DEEP, QKV)                                                                           \
     do {                                                                                                             \
         const size_t smem = dm_smem_bytes<DMAX, DEEP>(d, st_decode_block_pages(max_pages, page_size, window, n_splits), WARPS); \
         if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;                                                              \
         static bool configured = false;                                                                              \
         if (!configured) {                                                                                           \
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL, WARPS, DEEP>,               \
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<DMAX, FULL, WARPS, DEEP, QKV>,               \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
             if (e != cudaSuccess) return (int)e;                                                                     \
             configured = true;                                                                                       \
         }                                                                                                            \
-        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL, WARPS, DEEP>, grid, dim3(WARPS * 32), \
+        rc = st_launch_pdl("decode_mma", attention_decode_mma_kernel<DMAX, FULL, WARPS, DEEP, QKV>, grid, dim3(WARPS * 32), \
                            smem, s, (const bf16*)q, (const bf16*)pool, (bf16*)out,                                   \
                            n_splits > 1 ? partial : (float*)nullptr, items, positions, seq_of_token, slots,          \
                            start_pos, block_table, max_pages, n_layers, layer, nh, nkv, d, page_size, page_shift, sl2, window,  \
-                           n_splits, counters, status);                                                              \
+                           n_splits, counters, status, qkv);                                                         \
     } while (0)
 #define LAUNCH_DM_W(DMAX, FULL)                                                                                      \
     do {                                                                                                             \
         if (deep && dm_smem_bytes<DMAX, true>(d, st_decode_block_pages(max_pages, page_size, window, n_splits), warps) <= 200 * 1024) { \
-            if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, true); else LAUNCH_DM(DMAX, FULL, 4, true); }                   \
-        else { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, false); else LAUNCH_DM(DMAX, FULL, 4, false); }              \
+            if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, true, false); else LAUNCH_DM(DMAX, FULL, 4, true, false); }     \
+        else if (qkv.on) { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, false, true); else LAUNCH_DM(DMAX, FULL, 4, false, true); } \
+        else { if (warps == 8) LAUNCH_DM(DMAX, FULL, 8, false, false); else LAUNCH_DM(DMAX, FULL, 4, false, false); } \
     } while (0)
     if (d == 64) LAUNCH_DM_W(64, true);
     else if (d < 64) LAUNCH_DM_W(64, false);
@@ -425,4 +462,37 @@ ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out
 #undef LAUNCH_DM_W
 #undef LAUNCH_DM
     return rc;
+}
+
+// Same arguments and scratch layout as st_attention_decode, and the number of warps per block (4 or 8);
+// start_pos (per request: the tokens it had in the cache before this step, or null) tells which keys earlier
+// steps wrote, so that their copies can start before the kernel before this one has finished.
+ST_EXPORT int st_attention_decode_mma(const void* q, const void* pool, void* out, float* partial, const int* items,
+                                      int n_items, const int* positions, const int* seq_of_token, const int* slots,
+                                      const int* start_pos, const int* block_table, int max_pages, int n_layers,
+                                      int layer, int nh, int nkv, int d, int page_size, float scale, int window,
+                                      int n_splits, int* counters, int warps, int* status, void* stream) {
+    const DmQkv none = {};
+    return dm_launch(q, none, pool, out, partial, items, n_items, positions, seq_of_token, slots, start_pos, block_table,
+                     max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window, n_splits, counters, warps, status,
+                     stream);
+}
+
+// The q|k|v form: `qkv` [tokens, (nh + 2 nkv) d] is the fused projection of ALL the step's tokens (bfloat16, bias
+// included), every token of the step is one of the items, and start_pos (required) tells where each request's tokens
+// of this step begin.  The kernel writes each token's key and value rows into its page (write_kv; the pool has
+// num_pages pages) and attends over the cache and the step's own rows.  No other kernel may need this step's keys in
+// the cache (a step with prompt tiles does).
+ST_EXPORT int st_attention_decode_mma_qkv(const void* qkv, void* pool, void* out, float* partial,
+                                          const int* items, int n_items, const int* positions, const int* seq_of_token,
+                                          const int* slots, const int* start_pos, const int* block_table, int max_pages,
+                                          int num_pages, int n_layers, int layer, int nh, int nkv, int d, int page_size,
+                                          float scale, int window, int n_splits, int* counters, int warps, int write_kv,
+                                          int* status, void* stream) {
+    if (!start_pos || !qkv || num_pages <= 0) return ST_ERR_BAD_ARG;
+    if (!aligned16(qkv) || !aligned16(pool)) return ST_ERR_BAD_ARG;
+    const DmQkv form = {(nh + 2 * nkv) * d, num_pages, write_kv ? 1 : 0, 1};
+    return dm_launch(qkv, form, pool, out, partial, items, n_items, positions, seq_of_token, slots, start_pos, block_table,
+                     max_pages, n_layers, layer, nh, nkv, d, page_size, scale, window, n_splits, counters, warps, status,
+                     stream);
 }

@@ -548,6 +548,49 @@ def attention_decode(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch
     return out
 
 
+# Decode steps of more tokens than the weight-streaming product serves: the attention kernel works from the library's
+# q|k|v product and writes the cache itself (False: a cache-write kernel between the two, for measurements).
+DECODE_FROM_PROJECTION = True
+
+
+def attention_decode_qkv_applies(qkv: torch.Tensor, pool: torch.Tensor, n_items: int, nh: int, n_splits: int) -> bool:
+    """Whether ``attention_decode_qkv`` takes this step: bfloat16 on the device, a head size the tensor-core kernel
+    takes, and (with several splits) few enough (token, head) pairs for its arrival counters."""
+    d = pool.shape[-1]
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16
+            and bool(lib().st_attention_decode_mma_applies(d)) and (n_splits == 1 or n_items * nh <= _DECODE_COUNTERS))
+
+
+def attention_decode_qkv(qkv: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, items: Optional[torch.Tensor], n_items: int, positions: torch.Tensor,
+                         seq_of_token: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor,
+                         block_table: torch.Tensor, nh: int, scale: float, window: int = 0, n_splits: int = 1,
+                         partial: Optional[torch.Tensor] = None, warps: int = 4, write_kv: bool = True,
+                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-token attention straight from the fused projection: ``qkv`` [tokens, (nh + 2 nkv) d] holds the q, k and
+    v features of ALL the step's tokens as the product left them (bias included), every token of the step is an item,
+    and ``start_pos`` says where each request's tokens of this step begin.  The kernel writes each token's key and
+    value into its page (``write_kv``) and attends over the cache and the step's own rows: the step needs no
+    cache-write kernel.  Only for steps in which no other kernel reads this step's keys from the cache (no prompt
+    tiles)."""
+    _, n_layers, _, nkv, page_size, d = pool.shape
+    if not attention_decode_qkv_applies(qkv, pool, n_items, nh, n_splits):
+        raise KernelError("attention_decode_qkv: bfloat16, head sizes that are multiples of 16 up to 128")
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * d and out.shape == (qkv.shape[0], nh * d)
+    counters = None
+    if n_splits > 1:
+        need = attention_decode_scratch(n_items, nh, d, n_splits)
+        if partial is None or partial.numel() < need or partial.dtype != torch.float32:
+            raise KernelError(f"attention_decode_qkv: needs {need} floats of scratch for {n_splits} splits")
+        counters = _decode_counters(qkv.device)
+    _check(lib().st_attention_decode_mma_qkv(_p(qkv), _p(pool), _p(out), _p(partial), _p(items), n_items,
+                                             _p(positions), _p(seq_of_token), _p(slots), _p(start_pos),
+                                             _p(block_table), block_table.shape[1], pool.shape[0], n_layers, layer,
+                                             nh, nkv, d, page_size, _f(scale), window, n_splits, _p(counters),
+                                             warps if d <= 64 else 4, int(write_kv), _p(status), _stream()),
+           "attention_decode_qkv")
+    return out
+
+
 def decode_warps(n_items: int, nkv: int, d: int, n_splits: int, max_kv: int) -> int:
     """Warps per block for the tensor-core decode attention.  Eight when the launch is at most two blocks per
     SM and the key ranges are long: a warp's chain of groups is then half as long; with many blocks four are

@@ -231,6 +231,22 @@ class Attention(Mixer):
                                   ctx.start_pos, ctx.slots, cache.block_table, self.nh, self.scale, self.window or 0,
                                   status=ctx.status, q_stride=qkv.shape[1])
             return Delta(ops.linear(o, self.w_o), self.b_o)
+        elif self._decode_from_projection(h, ctx, cache):
+            # single tokens only, more of them than the weight-streaming product serves: the library product adds
+            # the bias in its epilogue, and the attention kernel takes the product as it is, writes each token's
+            # key and value into its page and attends: no cache-write kernel
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv, bias_bf16=self.b_qkv_bf16)
+            plan = ctx.plan(PagedAttentionPlan.name)
+            n_splits = plan.splits(self.nh, self.d)
+            o = torch.empty((h.shape[0], self.nh * self.d), dtype=h.dtype, device=h.device)
+            ops.attention_decode_qkv(qkv, cache.pool, cache.layer, o, plan.items,
+                                     plan.n_items, ctx.positions, ctx.seq_of_token, ctx.slots, ctx.start_pos,
+                                     cache.block_table, self.nh, self.scale, self.window or 0, n_splits,
+                                     ctx.scratch_f32(ops.attention_decode_scratch(plan.n_items, self.nh, self.d, n_splits))
+                                     if n_splits > 1 else None,
+                                     warps=ops.decode_warps(plan.n_items, self.nkv, self.d, n_splits, plan.max_item_kv),
+                                     status=ctx.status)
+            return Delta(ops.linear(o, self.w_o), self.b_o)
         else:
             qkv = ops.linear(h, self.w_qkv)
             ops.qkv_to_cache(qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token,
@@ -238,6 +254,17 @@ class Attention(Mixer):
                              write_kv=cache.writable)
         o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
         return Delta(ops.linear(o, self.w_o), self.b_o)
+
+    def _decode_from_projection(self, h: torch.Tensor, ctx: Any, cache: Any) -> bool:
+        """Whether this step's attention can work from the fused projection itself: every token of the step stands
+        alone (no prompt tiles, whose kernel reads this step's keys from the cache), the layer writes its own cache,
+        the product's epilogue adds the bias exactly (or there is none), and the kernel takes the sizes."""
+        if not (ops.DECODE_FROM_PROJECTION and cache.writable) or (self.bias and self.b_qkv_bf16 is None):
+            return False
+        plan = ctx.plan(PagedAttentionPlan.name)
+        if plan.n_tiles or not plan.n_items:
+            return False
+        return ops.attention_decode_qkv_applies(h, cache.pool, plan.n_items, self.nh, plan.splits(self.nh, self.d))
 
     def _queries_in_place(self, h: torch.Tensor, ctx: Any) -> bool:
         """Whether this step can leave the queries in the fused product: bfloat16, a head size the tile kernels

@@ -239,6 +239,24 @@ def attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_toke
     return out
 
 
+DECODE_FROM_PROJECTION = True
+
+
+def attention_decode_qkv_applies(qkv, pool, n_items, nh, n_splits):
+    return False        # the CPU runs of the engine keep the cache write apart
+
+
+def attention_decode_qkv(qkv, pool, layer, out, items, n_items, positions, seq_of_token, slots, start_pos,
+                         block_table, nh, scale, window=0, n_splits=1, partial=None, warps=4, write_kv=True, status=None):
+    """The cache write of every token of the step, then single-token attention for the items."""
+    nkv, d = pool.shape[3], pool.shape[5]
+    q = torch.zeros(qkv.shape[0], nh * d, dtype=qkv.dtype)
+    st = status if status is not None else torch.zeros(1, dtype=torch.int32)
+    qkv_to_cache(qkv, None, q, pool, layer, positions, seq_of_token, slots, block_table, nh, nkv, d, st, write_kv)
+    return attention_decode(q, pool, layer, out, items, n_items, positions, seq_of_token, slots, block_table, nh,
+                            scale, window)
+
+
 TILE_ROWS = 128
 
 

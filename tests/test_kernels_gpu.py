@@ -250,6 +250,41 @@ def test_attention_decode(shape, window, n_splits, kernel):
     assert torch.equal(early, out)
 
 
+@pytest.mark.parametrize("shape", [sh for sh in ATT_SHAPES if sh[2] % 16 == 0 and sh[2] <= 128])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("n_splits,warps", [(1, 4), (3, 4), (1, 8), (8, 8)])
+def test_attention_decode_from_the_fused_projection(shape, window, n_splits, warps):
+    """The single-token kernel given the q|k|v product instead of queries: it takes this step's keys and values from
+    the product's rows (the pages hold stale values at their places until it writes them: a read from the cache
+    there would show), writes each token's rows into its page exactly as the cache-write kernel would, and skips a
+    padding token.  Requests bring one to three tokens; one starts at position 0."""
+    nh, nkv, d, ps = shape
+    dtype = torch.bfloat16
+    lens, new = [150, 9, 700, 1, 64, 33], [1, 2, 1, 1, 3, 1]
+    pool, bt, slots, t, _, scale, _ = attention_case(dtype, nh, nkv, d, ps, lens, new, 60, window)
+    pos = torch.cat([t["pos"], torch.tensor([-1], dtype=torch.int32)])          # the last token is padding
+    seq = torch.cat([t["seq"], torch.tensor([0], dtype=torch.int32)])
+    n = pos.shape[0]
+    width = (nh + 2 * nkv) * d
+    qkv = rnd((n, width), dtype, 61)
+    bias = None
+    ref_pool, ref_q, st = pool.clone(), torch.zeros(n, nh * d, dtype=dtype), torch.zeros(1, dtype=torch.int32)
+    cpu_ops.qkv_to_cache(qkv, bias, ref_q, ref_pool, 1, pos, seq, slots, bt, nh, nkv, d, st)
+    ref = torch.zeros(n, nh * d, dtype=dtype)
+    cpu_ops.attention_plain(ref_q, ref_pool, 1, ref, pos, seq, slots, bt, nh, scale, window)
+    for write_kv in (True, False):
+        gp, out = pool.to(DEV), torch.full((n, nh * d), 7.0, dtype=dtype, device=DEV)
+        gst = torch.zeros(1, dtype=torch.int32, device=DEV)
+        partial = torch.empty(ops.attention_decode_scratch(n, nh, d, n_splits) + 1, device=DEV)
+        ops.attention_decode_qkv(qkv.to(DEV), gp, 1, out, None, n, pos.to(DEV),
+                                 seq.to(DEV), slots.to(DEV), t["start"].to(DEV), bt.to(DEV), nh, scale, window, n_splits,
+                                 partial, warps=warps, write_kv=write_kv, status=gst)
+        assert int(gst.item()) == 0
+        close(out[:n - 1], ref[:n - 1], dtype, "attention_decode_qkv", rel=1e-2)
+        assert torch.all(out[n - 1] == 7.0), "a padding token must not be written"
+        assert torch.equal(gp.cpu(), ref_pool if write_kv else pool), "the pages after the step"
+
+
 @pytest.mark.parametrize("shape", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
 @pytest.mark.parametrize("kernel", ["tmap", "tma", "tma3", "tc", "mma"])
