@@ -319,6 +319,8 @@ def main():
                 us = {"library": graph_us(lambda i: torch.mm(x, ws[i % copies].t()))}
                 if m <= 128:
                     us["stream_tc"] = graph_us(lambda i: ops.gemm_stream_tc(x, ws[i % copies]))
+                if m > ops.SKINNY_MAX_ROWS and ops.linear_parts_slices(m, ws[0]) > 1:
+                    us["stream_tc_parts"] = graph_us(lambda i: ops.linear_parts(x, ws[i % copies]))
                 if m <= 32:
                     us["skinny"] = graph_us(lambda i: ops.gemm_skinny(x, ws[i % copies]))
                 print(json.dumps({"only": "products", "rows": m, "product": name, "n": n, "k": k,

@@ -356,7 +356,7 @@ static int launch_add_norm(const float* x, const int* rows, const void* delta, c
     if (block > 512) block = 512;
     if (block < 64) block = 64;
     auto kern = vec ? add_norm_kernel<T, true> : add_norm_kernel<T, false>;
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {     // with the kernel's static part past what a kernel may use without asking
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }

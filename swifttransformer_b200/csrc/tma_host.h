@@ -48,6 +48,25 @@ static inline int st_tma_encode_bf16(CUtensorMap* out, const void* base, int ran
     return r == CUDA_SUCCESS ? 0 : -1;
 }
 
+// The same with the strides given: strides[i] is the distance in bytes between consecutive indices of dimension
+// i + 1 (a multiple of 16; dimensions may be listed in any order of their strides, the innermost is contiguous).
+static inline int st_tma_encode_bf16_strided(CUtensorMap* out, const void* base, int rank, const unsigned long long* dims,
+                                             const unsigned long long* strides, const unsigned* box) {
+    st_tma_encode_fn enc = st_tma_encoder();
+    if (!enc || rank < 2 || rank > 3 || box[0] != 64) return -1;
+    cuuint64_t d[3], st[2];
+    cuuint32_t b[3], elem[3] = {1, 1, 1};
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        if (i + 1 < rank) st[i] = strides[i];
+    }
+    const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, st, b,
+                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1;
+}
+
 // The tensor map of a paged key/value pool for the attention kernels fed by TMA: a rank-3 tensor
 // [page x layer x (K|V) x kv_head][position in page][head_dim] with boxes of one page of one head and 64 of its
 // elements.  Encoded once per pool and geometry and kept in a small table (per translation unit).

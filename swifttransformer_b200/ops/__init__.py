@@ -231,7 +231,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return torch.empty((0, m), dtype=out_dtype, device=a.device)
     if n <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0:
         return gemm_skinny(a, w, bias, act, out_dtype)
-    if n <= min(STREAM_TC_MAX_ROWS, 128) and a.shape[1] % 8 == 0:
+    if stream_tc_applies(n, w):
         return gemm_stream_tc(a, w, bias, act, out_dtype)
     if out_dtype == torch.float32:
         y = torch.mm(a, w.t(), out_dtype=torch.float32)
@@ -250,16 +250,25 @@ SKINNY_MAX_ROWS = 8
 SKINNY_KERNEL_MAX_ROWS = 32
 
 
-# Up to this many tokens (and above SKINNY_MAX_ROWS) the tcgen05 weight-streaming kernel serves bfloat16
-# products; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on (it is ahead at every row
-# count: at 64 rows 35 against 90 microseconds for the products of one OPT-1.3B layer).
+# Up to this many tokens (and above SKINNY_MAX_ROWS) the tcgen05 weight-streaming kernel serves the bfloat16
+# products that it runs in one wave of blocks; 0: off, the library product takes over from SKINNY_MAX_ROWS + 1 on.
+# Off: the library is ahead at every row count (OPT-1.3B decode step at batch 16 / 64: 1.42 / 2.33 ms against 1.77 /
+# 2.93 with this kernel; per layer 34 against 44 microseconds at 16 tokens, 35 against 54 at 64).
 STREAM_TC_MAX_ROWS = 0
+
+
+def stream_tc_applies(n_rows: int, w: torch.Tensor) -> bool:
+    """Whether ``linear`` / ``linear_parts`` give a product of n_rows tokens with w [out, in] to the tcgen05
+    weight-streaming kernel: bfloat16 on the device, more tokens than the mma.sync kernel serves, an inner dimension
+    that is a multiple of 64, and few enough features for one block per SM (the output head is not)."""
+    return (w.is_cuda and w.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < n_rows <= min(STREAM_TC_MAX_ROWS, 128)
+            and w.shape[1] % 64 == 0 and bool(lib().st_gemm_stream_tc_one_wave(w.shape[0])))
 
 
 def gemm_stream_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
                    out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """act(a @ w.T + bias) for at most 128 rows of bfloat16 ``a`` on tcgen05 fed by TMA; w is [out, in] with
-    in % 8 == 0.  A wait that expires inside the kernel shows in ``kernel_status``."""
+    in % 64 == 0.  A wait that expires inside the kernel shows in ``kernel_status``."""
     out_dtype = out_dtype or a.dtype
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_stream_tc is a bfloat16 kernel")
@@ -367,24 +376,34 @@ def linear_parts_slices(n_rows: int, w: torch.Tensor) -> int:
     """Into how many slices of k ``linear_parts`` cuts a product with w [out, in] for n_rows tokens (1: it does not
     apply: more than FUSED_MAX_ROWS tokens, weights that are not bfloat16 on the device, an inner dimension that is
     no multiple of 32, or a product that is not cut)."""
-    if not (LINEAR_PARTS and w.is_cuda and w.dtype == torch.bfloat16 and 1 <= n_rows <= FUSED_MAX_ROWS):
+    if not (LINEAR_PARTS and w.is_cuda and w.dtype == torch.bfloat16 and n_rows >= 1):
         return 1
-    return int(lib().st_gemm_skinny_parts_slices(w.shape[0], w.shape[1]))
+    if n_rows <= FUSED_MAX_ROWS:
+        return int(lib().st_gemm_skinny_parts_slices(w.shape[0], w.shape[1]))
+    if stream_tc_applies(n_rows, w):
+        return int(lib().st_gemm_stream_tc_slices(w.shape[0], w.shape[1]))
+    return 1
 
 
 def linear_parts(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """The slices' sums of a @ w.T for at most FUSED_MAX_ROWS bfloat16 rows: float32 [slices, rows, out], to be
-    added in slice order (``add_norm(parts=...)`` does, in the kernel that reads the residual rows anyway).  The
-    result lives in a buffer that the next call for the same sizes overwrites."""
+    """The slices' sums of a @ w.T for bfloat16 rows (as many as ``linear_parts_slices`` answers for with more than
+    one slice): float32 [slices, rows, out], to be added in slice order (``add_norm(parts=...)`` does, in the kernel
+    that reads the residual rows anyway).  Up to FUSED_MAX_ROWS rows the mma.sync kernel, beyond it the tcgen05
+    kernel.  The result lives in a buffer that the next call for the same sizes overwrites."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
     assert a.shape[1] == w.shape[1]
     n, m = a.shape[0], w.shape[0]
     slices = linear_parts_slices(n, w)
-    key = (a.device.index, slices, m)
+    cap = FUSED_MAX_ROWS if n <= FUSED_MAX_ROWS else 128
+    key = (a.device.index, slices, m, cap)
     if key not in _parts_scratch:
-        _parts_scratch[key] = torch.zeros(slices * FUSED_MAX_ROWS * m, dtype=torch.float32, device=a.device)
+        _parts_scratch[key] = torch.zeros(slices * cap * m, dtype=torch.float32, device=a.device)
     parts = _parts_scratch[key][:slices * n * m].view(slices, n, m)
-    _check(lib().st_gemm_skinny_parts(_p(a), _p(w), _p(parts), n, m, a.shape[1], _stream()), "linear_parts")
+    if n <= FUSED_MAX_ROWS:
+        _check(lib().st_gemm_skinny_parts(_p(a), _p(w), _p(parts), n, m, a.shape[1], _stream()), "linear_parts")
+    else:
+        _check(lib().st_gemm_stream_tc_parts(_p(a), _p(w), _p(parts), n, m, a.shape[1],
+                                             _p(_tc_status_word(a.device)), _stream()), "linear_parts")
     return parts
 
 

@@ -230,7 +230,7 @@ class Attention(Mixer):
             ops.attention_prefill(qkv, cache.pool, cache.layer, o, plan.tiles, plan.n_tiles, ctx.q_start,
                                   ctx.start_pos, ctx.slots, cache.block_table, self.nh, self.scale, self.window or 0,
                                   status=ctx.status, q_stride=qkv.shape[1])
-            return Delta(ops.linear(o, self.w_o), self.b_o)
+            return self._project(o)
         elif self._decode_from_projection(h, ctx, cache):
             # single tokens only, more of them than the weight-streaming product serves: the library product adds
             # the bias in its epilogue, and the attention kernel takes the product as it is, writes each token's
@@ -246,13 +246,20 @@ class Attention(Mixer):
                                      if n_splits > 1 else None,
                                      warps=ops.decode_warps(plan.n_items, self.nkv, self.d, n_splits, plan.max_item_kv),
                                      status=ctx.status)
-            return Delta(ops.linear(o, self.w_o), self.b_o)
+            return self._project(o)
         else:
             qkv = ops.linear(h, self.w_qkv)
             ops.qkv_to_cache(qkv, self.b_qkv, q, cache.pool, cache.layer, ctx.positions, ctx.seq_of_token,
                              ctx.slots, cache.block_table, self.nh, self.nkv, self.d, ctx.status,
                              write_kv=cache.writable)
         o = paged_attention(q, cache, ctx, self.nh, self.scale, self.window or 0)
+        return self._project(o)
+
+    def _project(self, o: torch.Tensor) -> Delta:
+        """The output projection, left for the next norm kernel to add: as one matrix, or, where the product for
+        this many tokens is cut over k, as its slices' sums."""
+        if o.shape[0] > ops.SKINNY_MAX_ROWS and ops.linear_parts_slices(o.shape[0], self.w_o) > 1:
+            return Delta(None, self.b_o, ops.linear_parts(o, self.w_o))
         return Delta(ops.linear(o, self.w_o), self.b_o)
 
     def _decode_from_projection(self, h: torch.Tensor, ctx: Any, cache: Any) -> bool:

@@ -42,6 +42,9 @@ class DenseFFN(FeedForward):
 
     def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
         u = ops.linear(h, self.w1, self.b1, self.activation, bias_bf16=self.b1_bf16)
+        if u.shape[0] > ops.SKINNY_MAX_ROWS and ops.linear_parts_slices(u.shape[0], self.w2) > 1:
+            # fc2 for this many tokens is cut over k: its slices' sums are left for the next norm kernel
+            return Delta(None, self.b2, ops.linear_parts(u, self.w2))
         return Delta(ops.linear(u, self.w2), self.b2)
 
     def forward_into_residual(self, x: torch.Tensor, norm: Any, ctx: Any, pending: Optional[Delta] = None) -> Any:

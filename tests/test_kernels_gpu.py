@@ -605,11 +605,13 @@ def test_norm_qkv_product_and_cache_write_in_one_kernel(n, monkeypatch):
     assert changed == int(live.sum()) * 2 * nkv, "one key row and one value row per live token and kv head, nothing else"
 
 
-@pytest.mark.parametrize("shape", [(9, 130, 64), (16, 2048, 2048), (33, 777, 520), (48, 300, 8192), (64, 6144, 2048),
-                                   (100, 1000, 264), (128, 4096, 1024), (12, 50272, 512)])
+@pytest.mark.parametrize("shape", [(9, 130, 64), (16, 2048, 2048), (33, 777, 576), (48, 300, 8192), (64, 6144, 2048),
+                                   (100, 1000, 320), (128, 4096, 1024), (12, 50272, 512)])
 def test_gemm_stream_tc(shape):
     """The tcgen05 + TMA weight-streaming product: every count of tokens up to 128, feature counts that are
-    no multiple of its 128-row tiles, k that is no multiple of its 64-wide stages, with and without k slices."""
+    no multiple of its 64- or 128-row tiles (the last shape takes the 128-row tiles), k that is no multiple of its
+    stages of 256 (128) elements, and more stages of k than its rings hold.  An inner dimension that is no multiple
+    of 64 is refused."""
     n, m, k = shape
     dtype = torch.bfloat16
     a, w, b = rnd((n, k), dtype, 84), rnd((m, k), dtype, 85, 0.1), rnd((m,), torch.float32, 86)
@@ -621,10 +623,50 @@ def test_gemm_stream_tc(shape):
     assert ops.kernel_status(DEV) == 0
     with pytest.raises(ops.KernelError):
         ops.gemm_stream_tc(rnd((129, k), dtype, 87).to(DEV), w.to(DEV))
+    with pytest.raises(ops.KernelError):
+        ops.gemm_stream_tc(rnd((n, k + 8), dtype, 88).to(DEV), rnd((m, k + 8), dtype, 89).to(DEV))
     # a row's result does not depend on the other rows in the batch
     one = ops.gemm_stream_tc(a[n - 1:n].to(DEV).contiguous(), w.to(DEV), b.to(DEV), "none", torch.float32)
     full = ops.gemm_stream_tc(a.to(DEV), w.to(DEV), b.to(DEV), "none", torch.float32)
     assert torch.equal(one[0], full[n - 1])
+
+
+@pytest.mark.parametrize("shape", [(64, 2048, 8192), (9, 2048, 2048), (33, 1000, 2112), (16, 96, 4096),
+                                   (128, 4096, 16384), (48, 130, 576), (20, 12288, 4096)])
+def test_linear_parts_of_the_tcgen05_product_and_the_norm_that_adds_them(shape):
+    """More tokens than the mma.sync kernel serves: the tcgen05 product cut over k leaves its slices' float sums
+    (blocks of their own, no bias), and the norm kernel behind adds them in slice order with the bias and the
+    residual rows."""
+    n, m, k = shape
+    a, w, b = rnd((n, k), torch.bfloat16, 215), rnd((m, k), torch.bfloat16, 216, 0.1), rnd((m,), torch.float32, 217)
+    x = rnd((n, m), torch.float32, 218) * 3
+    slices = int(ops.lib().st_gemm_stream_tc_slices(m, k))
+    stage = 256 if (m + 63) // 64 <= ops.sm_count() else 128       # elements of k per stage: tiles of 64 or 128 rows
+    stages = (k + stage - 1) // stage
+    per = (stages + slices - 1) // slices * stage
+    parts = torch.empty((slices, n, m), dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ga, gw = a.to(DEV), w.to(DEV)
+    rc = ops.lib().st_gemm_stream_tc_parts(ops._p(ga), ops._p(gw), ops._p(parts), n, m, k, ops._p(status), ops._stream())
+    assert rc == 0 and int(status.item()) == 0
+    ref_parts = torch.zeros(slices, n, m)
+    for sl in range(slices):
+        lo, hi = min(k, sl * per), min(k, (sl + 1) * per)
+        if lo < hi:
+            ref_parts[sl] = (a[:, lo:hi].double() @ w[:, lo:hi].double().T).float()
+    close(parts, ref_parts, torch.float32, "parts of the tcgen05 product", rel=2e-5)
+    if ops.linear_parts_slices(n, w.to(DEV)) > 1:             # what the engine calls for this shape: the same parts
+        assert torch.equal(ops.linear_parts(a.to(DEV), w.to(DEV)), parts)
+    gamma, beta = 1 + 0.2 * rnd((m,), torch.float32, 219), 0.3 * rnd((m,), torch.float32, 220)
+    got_x, got_h = x.to(DEV).clone(), torch.empty((n, m), dtype=torch.bfloat16, device=DEV)
+    ops.add_norm(got_x, parts=parts, delta_bias=b.to(DEV), resid_out=got_x, gamma=gamma.to(DEV), beta=beta.to(DEV),
+                 eps=1e-5, kind="layernorm", out_act=got_h)
+    close(got_x, x.double() + cpu_ops.linear(a, w, b, "none", torch.float32).double(), torch.float32,
+          "parts add up to the product", rel=3e-5)
+    ref_x, ref_h = x.clone(), torch.empty((n, m), dtype=torch.bfloat16)
+    cpu_ops.add_norm(ref_x, parts=ref_parts, delta_bias=b, resid_out=ref_x, gamma=gamma, beta=beta, eps=1e-5,
+                     kind="layernorm", out_act=ref_h)
+    close(got_h, ref_h, torch.bfloat16, "norm of rows with parts", rel=1e-2)
 
 
 @pytest.mark.parametrize("shape", [(5, 6144, 2048), (8, 5000, 576), (2, 8192, 1056), (1, 4768, 1024)])
@@ -687,7 +729,7 @@ def test_linear_parts_and_the_norm_that_adds_them(shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [40, 777, 2048, 7168])
+@pytest.mark.parametrize("width", [40, 777, 2048, 7168, 12288])
 def test_add_norm_with_parts_and_a_delta_and_a_row_gather(dtype, width):
     """Every form of the norm kernel (row in shared memory, two or four vectors per thread in registers) with float
     parts beside a delta in the activation type, a bias, and a gather of rows (the final norm of a step)."""
