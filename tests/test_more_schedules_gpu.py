@@ -64,6 +64,50 @@ def test_sixteen_live_requests_replayed(head_models, name, dtype):
 
 
 @pytest.mark.parametrize("name", list(HEADS))
+def test_steps_of_single_tokens_and_short_portions_attend_from_the_projection(head_models, name, monkeypatch):
+    """Twelve requests: prompts in long portions (tiles, the separate cache write), then steps in which every
+    request brings one token or a portion of 2 to 15 (all of them single queries to the attention): more tokens
+    than the weight-streaming product serves, no tiles, so the attention kernel works from the q|k|v product and
+    writes the cache itself.  Keys of the same step, page edges inside a portion, and later steps that read what
+    these wrote all show in the logits."""
+    from swifttransformer_b200 import ops
+    cfg = HEADS[name]["cfg"]
+    calls = []
+    real = ops.attention_decode_qkv
+    monkeypatch.setattr(ops, "attention_decode_qkv", lambda *a, **k: (calls.append(a[0].shape[0]), real(*a, **k))[1])
+    rng = np.random.default_rng(11)
+    reqs = {f"r{i}": helpers.random_tokens(cfg["vocab_size"], int(rng.integers(120, 250)), 700 + i) for i in range(12)}
+    pos = {rid: int(rng.integers(40, 90)) for rid in reqs}
+    steps = [dict(entries=[dict(id=rid, tokens=reqs[rid][:pos[rid]], want=[pos[rid] - 1]) for rid in list(reqs)[a:a + 4]],
+                  end=[]) for a in (0, 4, 8)]
+    live = set(reqs)
+    while live:
+        entries, end = [], []
+        for rid in sorted(live):
+            left = len(reqs[rid]) - pos[rid]
+            n = min(left, int(rng.choice([1, 1, 1, 2, 3, 5, 15])))
+            entries.append(dict(id=rid, tokens=reqs[rid][pos[rid]:pos[rid] + n], want=list(range(n))))
+            pos[rid] += n
+            if pos[rid] == len(reqs[rid]):
+                end.append(rid)
+        live -= set(end)
+        steps.append(dict(entries=entries, end=end))
+    s = trace_session(head_models[name], "bfloat16", helpers.live_token_need(steps), 16, max_requests=12,
+                      max_batch_tokens=1024)
+    got = helpers.replay(s, steps)
+    layers = cfg["num_hidden_layers"]
+    assert len(calls) >= layers * 20 and max(calls) > 8, "the steps of single queries took the kernel under test"
+    # the first wanted row of a request is the last of its prompt; the rest follow position by position
+    for rid, toks in reqs.items():
+        first = len(toks) - got[rid].shape[0]
+        ref = helpers.plain_logits(head_models[name], toks)[first:]
+        bad = helpers.first_bad(got[rid], ref, helpers.TOL["bfloat16"] * np.abs(ref).max())
+        assert bad is None, f"{name}/{rid}: position {first + bad[0]} differs by {bad[1]:.3e}"
+    assert s.cache.free_pages == s.cache.total_pages
+    s.runner.check_status()
+
+
+@pytest.mark.parametrize("name", list(HEADS))
 def test_sixteen_live_requests_generated_bfloat16(head_models, name):
     from swifttransformer_b200.engine.engine import LLMEngine
     from swifttransformer_b200.sampling import SamplingParams
