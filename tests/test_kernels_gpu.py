@@ -699,10 +699,12 @@ def test_linear_add_uncut_with_all_weights_on_chip(shape):
     close(got, ref, torch.float32, "linear_add on chip", rel=2e-5)
 
 
-@pytest.mark.parametrize("shape", [(8, 2048, 8192), (1, 2048, 8192), (5, 4096, 4096), (3, 1000, 2080), (8, 96, 4096)])
+@pytest.mark.parametrize("shape", [(8, 2048, 8192), (1, 2048, 8192), (5, 4096, 4096), (3, 1000, 2080), (8, 96, 4096),
+                                   (7, 1536, 6240), (6, 2000, 4640), (4, 1200, 2240)])
 def test_linear_parts_and_the_norm_that_adds_them(shape):
     """A product cut over k leaves the slices' sums as float parts (no cluster, no bias); the norm kernel behind adds
-    them in slice order with the bias and the residual rows: together they equal x + a . w^T + bias, normalised."""
+    them in slice order with the bias and the residual rows: together they equal x + a . w^T + bias, normalised.
+    The first two shapes are fc2 of OPT-1.3B; the last three have a shorter last slice."""
     n, m, k = shape
     a, w, b = rnd((n, k), torch.bfloat16, 195), rnd((m, k), torch.bfloat16, 196, 0.1), rnd((m,), torch.float32, 197)
     x = rnd((n, m), torch.float32, 198) * 3
