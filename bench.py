@@ -250,6 +250,7 @@ def main():
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
             eng.cache.free_slot(slot)
+        eng.runner.check_status()        # a kernel that gave up a wait or met a hole in a block table raises here
         ms = min(times[2:])
         fl = prefill_flops(cfg, cfg.num_hidden_layers, n)
         return dict(value=n / ms * 1e3, tokens=n, ms=ms, frac=fl / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12))
