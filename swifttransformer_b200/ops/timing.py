@@ -19,7 +19,8 @@ import torch
 
 TIMED = ("embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gather_where_i32", "linear", "gemm_plain",
          "gemm_skinny", "gemm_stream_tc", "norm_linear", "linear_add", "norm_qkv_linear_to_cache", "qkv_linear_to_cache",
-         "qkv_to_cache", "attention_plain", "attention_decode", "attention_prefill", "argmax", "sample")
+         "qkv_to_cache", "attention_plain", "attention_decode", "attention_decode_qkv", "attention_prefill",
+         "linear_parts", "argmax", "sample")
 
 _originals: Dict[str, object] = {}
 _events: List[Tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
