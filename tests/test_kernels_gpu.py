@@ -730,6 +730,35 @@ def test_linear_parts_and_the_norm_that_adds_them(shape):
         close(got_h, ref_h, torch.bfloat16, "norm of rows with parts", rel=1e-2)
 
 
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm", "none"])
+@pytest.mark.parametrize("width", [128, 640, 2048, 2176, 200])
+def test_add_norm_of_many_rows(kind, width):
+    """More rows than the launch has blocks (prompt portions): every block takes several rows, the next row's loads
+    under this row's reductions.  Both uses: residual updated with a normalised copy out (with and without delta,
+    bias, gain and shift), and the residual replaced by the normalised row."""
+    dtype = torch.bfloat16
+    n = 700
+    x = rnd((n, width), torch.float32, 230) + 20.0
+    delta, dbias = rnd((n, width), dtype, 231), rnd((width,), torch.float32, 232)
+    gamma, beta = 1 + rnd((width,), torch.float32, 233, 0.1), rnd((width,), torch.float32, 234, 0.1)
+    dev = lambda t: None if t is None else t.to(DEV)
+    for dl, db, ga, be in ((delta, dbias, gamma, beta), (None, None, gamma, None), (delta, None, None, None)):
+        xr, ref_out = x.clone(), torch.empty(n, width, dtype=dtype)
+        cpu_ops.add_norm(xr, delta=dl, delta_bias=db, resid_out=xr, gamma=ga, beta=be, eps=1e-5, kind=kind, out_act=ref_out)
+        xg, got_out = x.to(DEV), torch.empty(n, width, dtype=dtype, device=DEV)
+        ops.add_norm(xg, delta=dev(dl), delta_bias=dev(db), resid_out=xg, gamma=dev(ga), beta=dev(be), eps=1e-5, kind=kind,
+                     out_act=got_out)
+        close(xg, xr, torch.float32, "residual of many rows", rel=1e-6)
+        close(got_out, ref_out, dtype, f"{kind} of many rows", rel=8e-3)
+    xr, ref_out = x.clone(), torch.empty(n, width, dtype=dtype)
+    cpu_ops.add_norm(xr, delta=delta, delta_bias=dbias, gamma=gamma, beta=beta, eps=1e-5, kind=kind, out_act=ref_out, out_f32=xr)
+    xg, got_out = x.to(DEV), torch.empty(n, width, dtype=dtype, device=DEV)
+    ops.add_norm(xg, delta=dev(delta), delta_bias=dev(dbias), gamma=dev(gamma), beta=dev(beta), eps=1e-5, kind=kind,
+                 out_act=got_out, out_f32=xg)
+    close(xg, xr, torch.float32, "normalised residual of many rows", rel=5e-5)
+    close(got_out, ref_out, dtype, f"{kind} of many rows, normalised residual", rel=8e-3)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [40, 777, 2048, 7168, 12288])
 def test_add_norm_with_parts_and_a_delta_and_a_row_gather(dtype, width):
