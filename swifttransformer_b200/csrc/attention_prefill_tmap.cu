@@ -31,7 +31,7 @@
 #define TP_WG_BYTES (4 * TP_KV_BYTES + TP_Q_BYTES)  // K x2, V x2, P
 #define TP_MRG_FLOATS ((2 + TP_D) * 128)
 #define TP_ALL_BYTES (2 * TP_Q_BYTES + 2 * TP_WG_BYTES + 2 * TP_MRG_FLOATS * 4)
-#define TP_WG_COLS 128                              // S (64 columns), then O (64)
+#define TP_WG_COLS 256                              // S (64 columns), then O (64), then P (32: 64 packed bfloat16)
 
 __device__ __forceinline__ bool tp_wait(uint32_t mbar, uint32_t parity, volatile int* dead) {
     for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
@@ -160,7 +160,7 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
     }
     if (tid < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(tc_smem(&s_tmem)), "r"(256) : "memory");
+                     ::"r"(tc_smem(&s_tmem)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before_sync();
@@ -219,8 +219,8 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
                         tc_fence_after_sync();
 #pragma unroll
                         for (int jj = 0; jj < TC_BN / 16; ++jj)
-                            tc_mma(t_wg + 64, dp + ((jj * 32) >> 4), dv + ((b * TP_KV_BYTES + jj * 2048) >> 4), idesc_o,
-                                   i > 0 || jj > 0);
+                            tc_mma_ts(t_wg + 64, t_wg + 128 + jj * 8, dv + ((b * TP_KV_BYTES + jj * 2048) >> 4), idesc_o,
+                                      i > 0 || jj > 0);
                         tc_commit(mb_o);
                         tc_commit(mb_free + 8 * (2 + b));     // the value buffer may be refilled
                     } else alive = false;
@@ -381,14 +381,9 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
                     tc_st_wait();
                     l_run *= corr;
                 }
-                const uint32_t prow = sP + row * 128;
-#pragma unroll
-                for (int c8 = 0; c8 < TC_BN / 8; ++c8)
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n"
-                                 ::"r"(prow + ((c8 ^ (row & 7)) << 4)), "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]),
-                                   "r"(w[4 * c8 + 3]) : "memory");
+                tc_st32(t_row + 128, reinterpret_cast<const float*>(w));     // P: this row's 64 packed bfloat16 into tensor memory
                 l_run += ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
-                tc_fence_async_smem();
+                tc_st_wait();
                 tc_fence_before_sync();
                 tp_arrive(wg, 1);
             }
@@ -462,7 +457,7 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
     block_sync();
     if (s_dead && tid == 0) atomicExch(status, 3);
     if (tid < 32) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
     }
 }
 
