@@ -16,10 +16,14 @@
 //     cores while the softmax threads still merge and store this pair's result;
 //   * the softmax threads of the two warpgroups (every second key tile each, as before) meet once per pair,
 //     when both have read their last S: the second warpgroup then leaves (max, sum, O) in one of two merge
-//     buffers and goes on, the first combines and stores.
+//     buffers and goes on, the first combines and stores;
+//   * P never goes through shared memory: a softmax thread writes its row of P (64 packed bfloat16) into tensor
+//     memory with tcgen05.st and O += P V takes it from there as its A operand (one instruction and a wait
+//     instead of eight swizzled stores and a proxy fence: 54.0 -> 52.2 us per layer at 2048 tokens, 575 -> 537
+//     at 8192; two P buffers, so that P(i) would not wait for the product of tile i - 1, were slower: 56.4).
 //
-// Mathematics, layouts in shared and tensor memory, the bounded waits and their status codes are those of
-// attention_prefill_tma.cu.  Reference counterparts: src/csrc/kernel/fused_context_stage_attention.cu:82-453
+// Mathematics, the layouts of Q, K and V in shared memory and of S and O in tensor memory, the bounded waits and
+// their status codes are those of attention_prefill_tma.cu.  Reference counterparts: src/csrc/kernel/fused_context_stage_attention.cu:82-453
 // and src/csrc/kernel/xformers_attention.cu:313-393.
 #include "tcgen05.cuh"
 #include "tma_host.h"
@@ -28,7 +32,7 @@
 #define TP_D 64
 #define TP_Q_BYTES (TC_BM * 128)                    // a [128][64] block of bfloat16
 #define TP_KV_BYTES (TC_BN * 128)                   // a [64][64] block
-#define TP_WG_BYTES (4 * TP_KV_BYTES + TP_Q_BYTES)  // K x2, V x2, P
+#define TP_WG_BYTES (4 * TP_KV_BYTES)               // K x2, V x2
 #define TP_MRG_FLOATS ((2 + TP_D) * 128)
 #define TP_ALL_BYTES (2 * TP_Q_BYTES + 2 * TP_WG_BYTES + 2 * TP_MRG_FLOATS * 4)
 #define TP_WG_COLS 256                              // S (64 columns), then O (64), then P (32: 64 packed bfloat16)
@@ -148,7 +152,6 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
     const uint32_t sQ = base;                                            // two query buffers
     const uint32_t sK = sQ + 2 * TP_Q_BYTES + wg * TP_WG_BYTES;          // two key buffers
     const uint32_t sV = sK + 2 * TP_KV_BYTES;                            // two value buffers
-    const uint32_t sP = sV + 2 * TP_KV_BYTES;                            // one [128][64] block
     float* mrg_all = reinterpret_cast<float*>(tp_raw + (base - tc_smem(tp_raw)) + 2 * TP_Q_BYTES + 2 * TP_WG_BYTES);
     const uint32_t mb_s = tc_smem(&s_mbar[wg][0]), mb_o = tc_smem(&s_mbar[wg][1]);
     const uint32_t mb_full = tc_smem(&s_mbar[wg][2]), mb_free = tc_smem(&s_mbar[wg][6]);   // four each, 8 bytes apart
@@ -182,7 +185,7 @@ attention_prefill_tmap_kernel(const __grid_constant__ CUtensorMap kv_map, const 
         bool alive = true;
         const uint32_t idesc_s = tc_idesc(TC_BM, TC_BN, 0, 0);
         const uint32_t idesc_o = tc_idesc(TC_BM, d, 0, 1);
-        const uint64_t dk = tc_desc(sK, 16, 1024), dp = tc_desc(sP, 16, 1024), dv = tc_desc(sV, TP_KV_BYTES, 1024);
+        const uint64_t dk = tc_desc(sK, 16, 1024), dv = tc_desc(sV, TP_KV_BYTES, 1024);
         uint32_t g = 0;              // key tiles of this warpgroup so far, over all pairs: buffer g & 1, phase (g >> 1) & 1
         tp_pair_sync();              // the first pair's queries are in place
         for (int k = 0; have; ++k) {
