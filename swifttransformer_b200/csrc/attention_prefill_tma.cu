@@ -96,8 +96,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     constexpr int d = 64 * DB;
     constexpr uint32_t Q_BLK = TC_BM * 128, KV_BLK = TC_BN * 128;       // bytes of one [rows][64] block
     constexpr uint32_t BUF = DB * KV_BLK;                               // one key or value tile
-    constexpr uint32_t WG_BYTES = 4 * BUF + Q_BLK;                      // K x2, V x2, P
-    constexpr int WG_COLS = 64 + 64 * DB;                               // S, then O
+    constexpr uint32_t WG_BYTES = 4 * BUF + Q_BLK;                      // K x2, V x2, and a [128][64] block that was P's
+    constexpr int WG_COLS = 64 + 64 * DB + 32;                          // S, then O, then P (64 packed bfloat16 per row)
     constexpr uint32_t ALL_BYTES = DB * Q_BLK + NWG * WG_BYTES;
     constexpr int TMEM_COLS = NWG * WG_COLS <= 256 ? 256 : 512;
     static_assert(NWG * WG_COLS <= 512, "tensor memory has 512 columns");
@@ -122,7 +122,6 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
     const uint32_t sQ = base;
     const uint32_t sK = sQ + DB * Q_BLK + wg * WG_BYTES;                 // two key buffers
     const uint32_t sV = sK + 2 * BUF;                                    // two value buffers
-    const uint32_t sP = sV + 2 * BUF;                                    // one [128][64] block
 
     // Blocks start in the order of their linear index, x fastest: the head is x, so that all heads of
     // the longest tile start first (the host lists the tiles longest key range first).
@@ -184,7 +183,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
         const uint32_t idesc_s = tc_idesc(TC_BM, TC_BN, 0, 0);
         const uint32_t idesc_o = tc_idesc(TC_BM, d, 0, 1);
         const uint64_t dq = tc_desc(sQ, 16, 1024), dk = tc_desc(sK, 16, 1024);
-        const uint64_t dp = tc_desc(sP, 16, 1024), dv = tc_desc(sV, KV_BLK, 1024);
+        const uint64_t dv = tc_desc(sV, KV_BLK, 1024);
         // descriptors differ only in the start address (in units of 16 bytes, the low bits)
         auto issue_s = [&](int buf) {
 #pragma unroll
@@ -217,7 +216,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                     tc_fence_after_sync();
 #pragma unroll
                     for (int jj = 0; jj < TC_BN / 16; ++jj)
-                        tc_mma(t_wg + 64, dp + ((jj * 32) >> 4), dv + ((b * BUF + jj * 2048) >> 4), idesc_o, i > 0 || jj > 0);
+                        tc_mma_ts(t_wg + 64, t_wg + 64 + 64 * DB + jj * 8, dv + ((b * BUF + jj * 2048) >> 4), idesc_o, i > 0 || jj > 0);
                     tc_commit(mb_o);
                     tc_commit(mb_free + 8 * (2 + b));     // the value buffer may be refilled
                 } else alive = false;
@@ -389,14 +388,10 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const b
                 l_run *= corr;
             }
             TM_STAMP(4)
-            const uint32_t prow = sP + row * 128;
-#pragma unroll
-            for (int c8 = 0; c8 < TC_BN / 8; ++c8)
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n"
-                             ::"r"(prow + ((c8 ^ (row & 7)) << 4)), "r"(w[4 * c8]), "r"(w[4 * c8 + 1]), "r"(w[4 * c8 + 2]),
-                               "r"(w[4 * c8 + 3]) : "memory");
+            // P stays in tensor memory: this row's 64 packed bfloat16, the A operand of O += P V
+            tc_st32(t_row + 64 + 64 * DB, reinterpret_cast<const float*>(w));
             l_run += ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
-            tc_fence_async_smem();
+            tc_st_wait();
             tc_fence_before_sync();
             tm_arrive(wg, 1);
             TM_STAMP(5)
